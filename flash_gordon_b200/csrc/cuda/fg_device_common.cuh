@@ -1,0 +1,104 @@
+// Device-side building blocks shared by the sampling kernels (sm_100a).
+//
+// Everything here is exact integer / IEEE arithmetic: the orders, the penalty
+// formula and the key mapping must agree bit for bit with the reference's C
+// sampler (src/sampler.c) and argmax order (src/output.c:484-492).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace fgk {
+
+constexpr uint32_t kPaddingId = 0xffffffffu;
+constexpr unsigned kFullMask = 0xffffffffu;
+constexpr int kMaxK = 64;
+
+__device__ __forceinline__ bool is_nonfinite(float v) {
+    return (__float_as_uint(v) & 0x7f800000u) == 0x7f800000u;
+}
+
+// src/sampler.c:75-78 — the sampling order: larger score first, then smaller id.
+__device__ __forceinline__ bool precedes(float a, uint32_t a_id, float b, uint32_t b_id) {
+    return a > b || (a == b && a_id < b_id);
+}
+
+// src/output.c:484-492 / shaders/fg_argmax_reduce.comp:14-24 — the argmax order.
+__device__ __forceinline__ bool argmax_before(float a, uint32_t a_id, float b, uint32_t b_id) {
+    const bool a_pad = a_id == kPaddingId, b_pad = b_id == kPaddingId;
+    if (a_pad || b_pad) return !a_pad && b_pad;
+    const bool a_wild = is_nonfinite(a), b_wild = is_nonfinite(b);
+    if (a_wild || b_wild) return a_wild != b_wild ? a_wild : a_id < b_id;
+    return a > b || (a == b && a_id < b_id);
+}
+
+// src/sampler.c:52-58 for one seen id.  Round-to-nearest intrinsics keep nvcc
+// from contracting frequency*count + presence into a fused multiply-add.
+__device__ __forceinline__ float penalise(float v, uint32_t seen, float presence, float frequency,
+                                          float repetition) {
+    if (repetition != 1.0f) v = v > 0.0f ? __fdiv_rn(v, repetition) : __fmul_rn(v, repetition);
+    const float offset = __fadd_rn(__fmul_rn(frequency, __uint2float_rn(seen)), presence);
+    return __fsub_rn(v, offset);
+}
+
+// Monotone map finite fp32 -> uint32 (larger float, larger key); -0.0 and +0.0
+// share a key because every comparator of the reference's C code treats them as
+// equal and falls through to the id.  Key 0 is below every finite value.
+__device__ __forceinline__ uint32_t float_key(float v) {
+    uint32_t bits = __float_as_uint(v);
+    if (bits == 0x80000000u) bits = 0u;
+    return (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);
+}
+
+// Inverse of float_key for thresholds; key 0 means "below everything".
+__device__ __forceinline__ float key_to_float(uint32_t key) {
+    if (key == 0u) return __uint_as_float(0xff800000u);  // -inf
+    const uint32_t bits = (key & 0x80000000u) ? (key & 0x7fffffffu) : ~key;
+    return __uint_as_float(bits);
+}
+
+// 64-bit selection key: value key in the high word, inverted id in the low word,
+// so "larger key" is exactly `precedes`.
+__device__ __forceinline__ uint64_t select_key(float v, uint32_t id) {
+    return (static_cast<uint64_t>(float_key(v)) << 32) | static_cast<uint64_t>(~id);
+}
+
+__device__ __forceinline__ float bf16_bits_to_float(uint32_t bits16) {
+    return __uint_as_float(bits16 << 16);
+}
+
+__device__ __forceinline__ uint32_t lane_id() { return threadIdx.x & 31u; }
+
+// 128-bit streaming load: read-only path, no L1 allocation (every logit is
+// touched once).
+__device__ __forceinline__ uint4 load_stream_128(const void *p) {
+    uint4 r;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+                 : "l"(p));
+    return r;
+}
+
+// The POD the kernels read; layout of fg_sampler_config (include/fg_sampler.h).
+struct SamplerConfig {
+    float temperature;
+    float top_p;
+    uint32_t top_k;
+    float presence_penalty;
+    float frequency_penalty;
+    float repetition_penalty;
+    float min_p;
+    uint32_t pad_;
+    uint64_t seed;
+};
+static_assert(sizeof(SamplerConfig) == 40, "fg_sampler_config is 40 bytes");
+
+__device__ __forceinline__ bool penalties_active(const SamplerConfig &c) {
+    return c.presence_penalty != 0.0f || c.frequency_penalty != 0.0f ||
+           c.repetition_penalty != 1.0f;
+}
+
+// fg_status values used on the device (include/fg.h).
+constexpr uint32_t kOk = 0u, kErrFormat = 4u, kErrMismatch = 5u, kErrLimit = 8u;
+
+}  // namespace fgk

@@ -1,0 +1,125 @@
+/*
+ * Internal seam between the C17 host layer (csrc/host) and the CUDA
+ * translation units (csrc/cuda).  Plain C types only.  Every fgk_* function
+ * returns a cudaError_t value as int (0 = success) unless stated otherwise;
+ * the host layer turns it into fg_status and a message.  Not installed, not
+ * part of the public ABI.
+ */
+#ifndef FG_B200_KERNELS_H
+#define FG_B200_KERNELS_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#include "fg_sampler.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* dynamic shared memory a streaming CTA may ask for (static part comes on top) */
+#define FGK_STREAM_MAX_DYNAMIC_SMEM (200 * 1024)
+/* dynamic shared memory that still lets four CTAs share one SM */
+#define FGK_STREAM_COMFORT_DYNAMIC_SMEM (44 * 1024)
+
+/* ---- runtime plumbing (fg_runtime.cu) ---- */
+int fgk_device_count(int *count);
+int fgk_set_device(int device);
+int fgk_device_sm_count(int device, int *sm_count);
+int fgk_stream_create(void **stream);
+int fgk_stream_destroy(void *stream);
+int fgk_stream_synchronize(void *stream);
+int fgk_malloc(void **pointer, size_t bytes);
+int fgk_free(void *pointer);
+int fgk_host_alloc(void **pointer, size_t bytes); /* pinned */
+int fgk_host_free(void *pointer);
+int fgk_memset_async(void *pointer, int value, size_t bytes, void *stream);
+int fgk_copy_to_device_async(void *device, const void *host, size_t bytes, void *stream);
+int fgk_copy_to_host_async(void *host, const void *device, size_t bytes, void *stream);
+const char *fgk_error_string(int cuda_error);
+/* 1 when `pointer` is device-accessible memory of the current context's device
+ * (or its provenance cannot be told), 0 when it is plainly host memory. */
+int fgk_pointer_is_device(const void *pointer);
+
+/* ---- outputs shared by the sampling launches ---- */
+typedef struct fgk_select_output {
+    uint32_t *tokens;
+    float *token_logits;
+    uint32_t *row_status;
+    uint64_t *first_error; /* device word: min over failing rows of (row << 8 | status) */
+    uint32_t *dbg_count;
+    uint32_t *dbg_ids;
+    float *dbg_scores;
+    double *dbg_raw;
+    double *dbg_tempered;
+} fgk_select_output;
+
+/* ---- streaming select (fg_stream_kernels.cu) ---- */
+typedef struct fgk_stream_launch {
+    const void *logits;
+    uint32_t dtype; /* 0 fp32, 1 bf16 */
+    uint32_t rows, vocab;
+    uint64_t row_stride;
+    uint32_t vocab_offset, vocab_total;
+    uint32_t splits, split_len;
+    const uint32_t *history_tokens;
+    const uint64_t *history_offsets;
+    uint32_t history_max;
+    const void *configs_device; /* rows x 40 bytes when config_count > 1 */
+    fg_sampler_config config0;
+    uint32_t config_count;
+    uint32_t shard_k;
+    const float *uniforms;
+    float *shard_scores;
+    uint32_t *shard_ids;
+    float *part_scores;
+    uint32_t *part_ids;
+    void *part_meta;
+    uint32_t *tickets;
+    uint32_t bitmap_words;
+    uint32_t count_capacity;
+    fgk_select_output out;
+} fgk_stream_launch;
+
+uint32_t fgk_stream_max_splits(void);
+uint32_t fgk_stream_tile(void);
+uint32_t fgk_stream_threads(void);
+uint64_t fgk_stream_part_meta_bytes(void);
+int fgk_stream_prepare(void);
+int fgk_launch_stream_select(const fgk_stream_launch *launch, void *stream);
+
+typedef struct fgk_merge_launch {
+    const float *scores;
+    const uint32_t *ids;
+    uint32_t rows, shards, k_shard;
+    uint32_t check_spans;
+    uint32_t span_first[16], span_width[16];
+    const void *configs_device;
+    fg_sampler_config config0;
+    uint32_t config_count;
+    const float *uniforms;
+    fgk_select_output out;
+} fgk_merge_launch;
+
+int fgk_launch_merge_select(const fgk_merge_launch *launch, void *stream);
+
+/* ---- device operators (fg_ops_kernels.cu) ---- */
+int fgk_launch_apply_penalties(float *logits, const uint32_t *counts, uint32_t values,
+                               float presence, float frequency, float repetition, void *stream);
+/* scores[i] penalised with seen[i] (already gathered), for fg_sampler_apply_penalties */
+int fgk_launch_apply_penalties_seen(float *scores, const uint32_t *seen, uint32_t values,
+                                    float presence, float frequency, float repetition,
+                                    void *stream);
+int fgk_launch_argmax_reduce(float *out_scores, uint32_t *out_ids, const float *scores,
+                             const uint32_t *ids, uint32_t count, void *stream);
+int fgk_launch_topk_select(float *out_scores, uint32_t *out_ids, const float *scores,
+                           const uint32_t *ids, uint32_t count, uint32_t k, void *stream);
+/* counts += occurrences of history[0..count); *bad (device word) set when an id >= vocab */
+int fgk_launch_history_add(uint32_t *counts, uint32_t vocab, const uint32_t *history,
+                           uint32_t count, uint32_t *bad, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif

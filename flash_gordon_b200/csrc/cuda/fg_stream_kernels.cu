@@ -1,0 +1,719 @@
+// Fused sampling kernels for sm_100a: one pass over the logits in HBM.
+//
+// Grid: (splits, rows).  CTA (s, r) owns columns [s*split_len, (s+1)*split_len)
+// of row r and
+//   1. builds, in shared memory, the part of the row's token history that falls
+//      into its columns: a bitmap of seen ids, a running popcount per bitmap word
+//      and a dense count per seen id (src/output.c:601-617 builds a vocab-wide
+//      count table per session instead);
+//   2. streams its columns with 128-bit loads (next tile prefetched into
+//      registers), applies the penalties of src/sampler.c:46-60 to seen ids in
+//      registers, and keeps every value that can still be among the k best in a
+//      shared-memory candidate list; the list is cut back to k with a radix
+//      select whenever it fills, which also raises the admission threshold;
+//   3. hands its k best to the row's last-arriving CTA (ticket counter), which
+//      merges the splits and runs the select step of src/sampler.c:80-122.
+// Logits are read once; nothing vocabulary-sized is written.
+#include "fg_block_select.cuh"
+#include "fg_kernels.h"
+
+namespace fgk {
+
+constexpr int kThreads = 256;
+constexpr int kElemsPerThread = 16;
+constexpr int kTile = kThreads * kElemsPerThread;  // 4096 logits per CTA iteration
+constexpr int kCandCap = 1024;
+constexpr uint32_t kMaxSplits = kCandCap / kMaxK;  // the merge fits one candidate buffer
+
+struct alignas(16) PartMeta {
+    uint32_t count;         // finite candidates this split kept (<= k)
+    uint32_t wild_id;       // smallest id holding a NaN/Inf (greedy rows), padding if none
+    uint32_t wild_bits;     // its value
+    uint32_t bad_history;   // 0, or the fg_status a broken history earns the row
+};
+
+struct StreamParams {
+    const void *logits;
+    uint64_t row_stride;
+    uint32_t rows, vocab;
+    uint32_t vocab_offset, vocab_total;
+    uint32_t splits, split_len;
+    const uint32_t *history_tokens;
+    const uint64_t *history_offsets;
+    const SamplerConfig *configs;  // device copy when config_count > 1
+    SamplerConfig config0;
+    uint32_t config_count;
+    uint32_t shard_k;               // != 0: write candidates instead of sampling
+    const float *uniforms;
+    float *shard_scores;
+    uint32_t *shard_ids;
+    float *part_scores;             // [rows][splits][64]
+    uint32_t *part_ids;
+    PartMeta *part_meta;            // [rows][splits]
+    uint32_t *tickets;              // [rows], zero between launches
+    uint32_t history_max;           // caller's bound on any row's history length
+    uint32_t bitmap_words;          // shared-memory layout (0: no history structure)
+    uint32_t count_capacity;        // entries of the dense count array (0: counts unused)
+    SelectOutput out;
+};
+
+struct StreamShared {
+    CandidateBuffer<kCandCap> cand;
+    FinishBuffer fin;
+    uint32_t scan[kThreads / 32];
+    uint32_t distinct;
+    uint32_t bad_history;
+    uint32_t wild_id;
+    uint32_t wild_bits;
+    uint32_t is_last;
+};
+
+template <typename T>
+struct Loader;
+
+template <>
+struct Loader<float> {
+    static constexpr int kVectors = 4;        // 4 x (4 fp32) per thread per tile
+    static constexpr int kPerVector = 4;
+    // ragged edge / unaligned row: element-wise, columns past the end read as -inf
+    static __device__ __forceinline__ uint4 load_guarded(const float *p, uint32_t first, uint32_t n) {
+        uint32_t w[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) w[j] = first + j < n ? __float_as_uint(p[first + j]) : 0xff800000u;
+        return make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    static __device__ __forceinline__ void unpack(const uint4 &raw, float *v) {
+        v[0] = __uint_as_float(raw.x);
+        v[1] = __uint_as_float(raw.y);
+        v[2] = __uint_as_float(raw.z);
+        v[3] = __uint_as_float(raw.w);
+    }
+};
+
+template <>
+struct Loader<uint16_t> {                     // bf16 bit patterns
+    static constexpr int kVectors = 2;        // 2 x (8 bf16) per thread per tile
+    static constexpr int kPerVector = 8;
+    static __device__ __forceinline__ uint4 load_guarded(const uint16_t *p, uint32_t first,
+                                                         uint32_t n) {
+        uint32_t w[4];
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+            const uint32_t low = first + 2 * q < n ? p[first + 2 * q] : 0xff80u;
+            const uint32_t high = first + 2 * q + 1 < n ? p[first + 2 * q + 1] : 0xff80u;
+            w[q] = low | (high << 16);
+        }
+        return make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    static __device__ __forceinline__ void unpack(const uint4 &raw, float *v) {
+        v[0] = __uint_as_float(raw.x << 16);
+        v[1] = __uint_as_float(raw.x & 0xffff0000u);
+        v[2] = __uint_as_float(raw.y << 16);
+        v[3] = __uint_as_float(raw.y & 0xffff0000u);
+        v[4] = __uint_as_float(raw.z << 16);
+        v[5] = __uint_as_float(raw.z & 0xffff0000u);
+        v[6] = __uint_as_float(raw.w << 16);
+        v[7] = __uint_as_float(raw.w & 0xffff0000u);
+    }
+};
+
+// Column (relative to the split) of element j of vector u of this thread.
+template <typename T>
+__device__ __forceinline__ uint32_t column_of(uint32_t tile_base, int u, int j) {
+    return tile_base + (u * kThreads + threadIdx.x) * Loader<T>::kPerVector + j;
+}
+
+// Tile -> raw registers.  Full, 16-byte aligned vectors use one 128-bit load;
+// ragged edges and unaligned rows fall back to guarded scalar loads.  Lanes past
+// the end read as -inf and are masked out by the caller.
+template <typename T>
+__device__ __forceinline__ void load_tile(const T *columns, uint32_t tile_base, uint32_t n,
+                                          bool aligned, uint4 (&raw)[Loader<T>::kVectors]) {
+    using L = Loader<T>;
+#pragma unroll
+    for (int u = 0; u < L::kVectors; u++) {
+        const uint32_t first = column_of<T>(tile_base, u, 0);
+        if (aligned && first + L::kPerVector <= n) {
+            raw[u] = load_stream_128(columns + first);
+        } else {
+            raw[u] = L::load_guarded(columns, first, n);
+        }
+    }
+}
+
+// k-th largest of one key per thread (0 = no key), by bitwise search from the
+// top bit; 0 when fewer than k threads hold a key.  All threads call.
+__device__ __forceinline__ uint32_t block_kth_key(uint32_t my_key, uint32_t k) {
+    uint32_t found = 0;
+#pragma unroll 1
+    for (int bit = 31; bit >= 0; bit--) {
+        const uint32_t trial = found | (1u << bit);
+        if ((uint32_t)__syncthreads_count(my_key >= trial) >= k) found = trial;
+    }
+    return found;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads, 4) stream_select_kernel(const StreamParams p) {
+    using L = Loader<T>;
+    extern __shared__ __align__(16) uint32_t dyn_smem[];
+    __shared__ StreamShared sh;
+
+    const uint32_t tid = threadIdx.x;
+    const uint32_t lane = tid & 31u, warp = tid >> 5;
+    const uint32_t split = blockIdx.x, row = blockIdx.y;
+    const SamplerConfig cfg = p.config_count > 1 ? p.configs[row] : p.config0;
+    const bool shard_mode = p.shard_k != 0;
+    const bool greedy = !shard_mode && cfg.temperature == 0.0f;
+    if (!shard_mode && !greedy && cfg.top_k == 0) return;  // rows without a top-k cut use the nucleus kernel
+    const uint32_t k = shard_mode ? p.shard_k : (greedy ? 1u : cfg.top_k);
+
+    const uint32_t lo = split * p.split_len;
+    const uint32_t n = min(p.split_len, p.vocab - lo);
+    const T *columns = static_cast<const T *>(p.logits) + (size_t)row * p.row_stride + lo;
+    const bool aligned = (reinterpret_cast<uintptr_t>(columns) & 15u) == 0;
+
+    // first tile is in flight while the history structure is built
+    uint4 raw[L::kVectors];
+    load_tile<T>(columns, 0, n, aligned, raw);
+
+    if (tid == 0) {
+        sh.cand.count = 0;
+        sh.cand.tau_score = __uint_as_float(0xff800000u);
+        sh.cand.tau_id = kPaddingId;
+        sh.bad_history = 0;
+        sh.wild_id = kPaddingId;
+        sh.wild_bits = 0;
+        sh.distinct = 0;
+    }
+    __syncthreads();
+
+    // ---- 1. history slice -> bitmap / running popcount / dense counts ----
+    uint32_t *bitmap = dyn_smem;
+    uint32_t *running = dyn_smem + p.bitmap_words;
+    uint32_t *dense = dyn_smem + 2 * p.bitmap_words;
+    const uint32_t words = (n + 31u) >> 5;
+    uint32_t history_len = 0;
+    const uint32_t *history = nullptr;
+    if (p.history_tokens != nullptr && p.history_offsets != nullptr) {
+        const uint64_t begin = p.history_offsets[row], end = p.history_offsets[row + 1];
+        history = p.history_tokens + begin;
+        history_len = (uint32_t)(end - begin);
+        // the shared-memory count array was sized from the caller's bound
+        if (end < begin || end - begin > p.history_max) {
+            history_len = 0;
+            if (tid == 0) sh.bad_history = kErrLimit;
+        }
+    }
+    const bool penalise_row = penalties_active(cfg) && p.bitmap_words != 0;
+    const bool seen_any = penalise_row && history_len != 0;
+    const bool with_counts = seen_any && cfg.frequency_penalty != 0.0f && p.count_capacity != 0;
+    if (seen_any) {
+        for (uint32_t w = tid; w < words; w += kThreads) bitmap[w] = 0;
+        __syncthreads();
+        const uint32_t first_global = p.vocab_offset + lo;
+        for (uint32_t i = tid; i < history_len; i += kThreads) {
+            const uint32_t token = history[i];
+            if (token >= p.vocab_total) sh.bad_history = kErrFormat;
+            const uint32_t local = token - first_global;  // wraps for ids below the split
+            if (local < n) {
+                const uint32_t bit = 1u << (local & 31u);
+                if ((bitmap[local >> 5] & bit) == 0) atomicOr(&bitmap[local >> 5], bit);
+            }
+        }
+        __syncthreads();
+        if (with_counts) {
+            // exclusive running popcount per word: each thread owns a contiguous run
+            const uint32_t per = (words + kThreads - 1) / kThreads;
+            const uint32_t w0 = min(tid * per, words), w1 = min(w0 + per, words);
+            uint32_t mine = 0;
+            for (uint32_t w = w0; w < w1; w++) mine += __popc(bitmap[w]);
+            uint32_t incl = mine;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const uint32_t up = __shfl_up_sync(kFullMask, incl, d);
+                if (lane >= (uint32_t)d) incl += up;
+            }
+            if (lane == 31) sh.scan[warp] = incl;
+            __syncthreads();
+            uint32_t before = incl - mine;
+            for (uint32_t q = 0; q < warp; q++) before += sh.scan[q];
+            if (tid == kThreads - 1) sh.distinct = before + mine;
+            for (uint32_t w = w0; w < w1; w++) {
+                running[w] = before;
+                before += __popc(bitmap[w]);
+            }
+            __syncthreads();
+            // the host sizes count_capacity >= min(history_max, split_len) >= distinct
+            const uint32_t distinct = min(sh.distinct, p.count_capacity);
+            for (uint32_t i = tid; i < distinct; i += kThreads) dense[i] = 0;
+            __syncthreads();
+            for (uint32_t i = tid; i < history_len; i += kThreads) {
+                const uint32_t local = history[i] - first_global;
+                if (local < n) {
+                    const uint32_t word = bitmap[local >> 5];
+                    const uint32_t at =
+                        running[local >> 5] + __popc(word & ((1u << (local & 31u)) - 1u));
+                    if (at < p.count_capacity) atomicAdd(&dense[at], 1u);
+                }
+            }
+        }
+    }
+    __syncthreads();
+
+    // ---- 2. stream the columns ----
+    const uint32_t tiles = (n + kTile - 1) / kTile;
+    uint32_t wild_id = kPaddingId, wild_bits = 0;
+    float tau = __uint_as_float(0xff800000u);
+    for (uint32_t t = 0; t < tiles; t++) {
+        const uint32_t tile_base = t * kTile;
+        float v[kElemsPerThread];
+#pragma unroll
+        for (int u = 0; u < L::kVectors; u++) L::unpack(raw[u], &v[u * L::kPerVector]);
+        if (t + 1 < tiles) load_tile<T>(columns, tile_base + kTile, n, aligned, raw);
+
+        if (seen_any) {
+#pragma unroll
+            for (int u = 0; u < L::kVectors; u++) {
+                const uint32_t first = column_of<T>(tile_base, u, 0);
+                if (first >= n) continue;
+                const uint32_t word = bitmap[first >> 5];
+                const uint32_t bits = (word >> (first & 31u)) & ((1u << L::kPerVector) - 1u);
+                if (bits == 0) continue;
+#pragma unroll
+                for (int j = 0; j < L::kPerVector; j++) {
+                    if (bits & (1u << j)) {
+                        uint32_t seen = 1;
+                        if (with_counts) {
+                            const uint32_t below = (1u << ((first & 31u) + j)) - 1u;
+                            seen = dense[min(running[first >> 5] + __popc(word & below),
+                                             p.count_capacity - 1)];
+                        }
+                        v[u * L::kPerVector + j] =
+                            penalise(v[u * L::kPerVector + j], seen, cfg.presence_penalty,
+                                     cfg.frequency_penalty, cfg.repetition_penalty);
+                    }
+                }
+            }
+        }
+
+        // which of my 16 values exist, are finite, and can still make the top k
+        const bool ragged = tile_base + kTile > n;
+        uint32_t pending = 0;
+        if (t == 0) {
+            // First tile: a valid lower bound for the k-th best is the k-th largest of
+            // the per-thread maxima (k distinct elements are at least that large).
+            float best = __uint_as_float(0xff800000u);
+            uint32_t have = 0;
+#pragma unroll
+            for (int e = 0; e < kElemsPerThread; e++) {
+                const bool exists =
+                    !ragged || column_of<T>(tile_base, e / L::kPerVector, e % L::kPerVector) < n;
+                if (exists && !is_nonfinite(v[e])) {
+                    best = fmaxf(best, v[e]);
+                    have = 1;
+                }
+            }
+            tau = key_to_float(block_kth_key(have ? float_key(best) : 0u, k));
+        }
+#pragma unroll
+        for (int e = 0; e < kElemsPerThread; e++) {
+            const bool exists =
+                !ragged || column_of<T>(tile_base, e / L::kPerVector, e % L::kPerVector) < n;
+            const bool wild = is_nonfinite(v[e]);
+            if (greedy && exists && wild) {
+                const uint32_t id =
+                    p.vocab_offset + lo + column_of<T>(tile_base, e / L::kPerVector, e % L::kPerVector);
+                if (id < wild_id) {
+                    wild_id = id;
+                    wild_bits = __float_as_uint(v[e]);
+                }
+            }
+            // ties with the bound can only matter inside the tile that produced it:
+            // later columns carry larger ids and lose the tie
+            const bool pass = t == 0 ? v[e] >= tau : v[e] > tau;
+            if (exists && !wild && pass) pending |= 1u << e;
+        }
+
+        // append; when the list overflows, cut it back to k and retry what is left
+        for (;;) {
+            bool trouble = false;
+            if (__any_sync(kFullMask, pending != 0)) {
+#pragma unroll
+                for (int e = 0; e < kElemsPerThread; e++) {
+                    const bool mine = (pending >> e) & 1u;
+                    const unsigned votes = __ballot_sync(kFullMask, mine);
+                    if (votes == 0) continue;
+                    const int leader = __ffs(votes) - 1;
+                    uint32_t base = 0;
+                    if ((int)lane == leader) {
+                        base = atomicAdd(&sh.cand.count, (uint32_t)__popc(votes));
+                        // ask for a cut well before the list is full: it also lifts tau
+                        if (base + __popc(votes) > kCandCap / 2) trouble = true;
+                    }
+                    base = __shfl_sync(kFullMask, base, leader);
+                    if (mine) {
+                        const uint32_t slot = base + __popc(votes & ((1u << lane) - 1u));
+                        if (slot < kCandCap) {
+                            sh.cand.score[slot] = v[e];
+                            sh.cand.id[slot] = p.vocab_offset + lo +
+                                               column_of<T>(tile_base, e / L::kPerVector,
+                                                            e % L::kPerVector);
+                            pending &= ~(1u << e);
+                        } else {
+                            trouble = true;
+                        }
+                    }
+                }
+            }
+            if (!__syncthreads_or(trouble)) break;
+            const uint32_t held = min(sh.cand.count, (uint32_t)kCandCap);
+            __syncthreads();  // everyone has read count before compact rewrites it
+            compact_topk<kThreads, kCandCap>(sh.cand, held, k);
+            if (held <= k && tid == 0) sh.cand.count = held;  // (cannot happen: held > cap/2 > k)
+            tau = sh.cand.tau_score;
+            const uint32_t tau_id = sh.cand.tau_id;
+            bool left = false;
+#pragma unroll
+            for (int e = 0; e < kElemsPerThread; e++) {
+                if ((pending >> e) & 1u) {
+                    const uint32_t id = p.vocab_offset + lo +
+                                        column_of<T>(tile_base, e / L::kPerVector, e % L::kPerVector);
+                    if (precedes(v[e], id, tau, tau_id)) left = true;
+                    else pending &= ~(1u << e);
+                }
+            }
+            if (!__syncthreads_or(left)) break;
+        }
+    }
+
+    // ---- 3. this split's k best ----
+    __syncthreads();
+    uint32_t held = min(sh.cand.count, (uint32_t)kCandCap);
+    __syncthreads();
+    held = compact_topk<kThreads, kCandCap>(sh.cand, held, k);
+    if (greedy && wild_id != kPaddingId) atomicMin(&sh.wild_id, wild_id);
+    __syncthreads();
+    if (greedy && wild_id != kPaddingId && wild_id == sh.wild_id) sh.wild_bits = wild_bits;
+    __syncthreads();
+
+    uint32_t bad_history = sh.bad_history;
+    uint32_t row_wild_id = sh.wild_id, row_wild_bits = sh.wild_bits;
+
+    if (p.splits > 1) {
+        const size_t slot = (size_t)row * p.splits + split;
+        if (tid < kMaxK) {
+            p.part_scores[slot * kMaxK + tid] = tid < held ? sh.cand.score[tid] : 0.0f;
+            p.part_ids[slot * kMaxK + tid] = tid < held ? sh.cand.id[tid] : kPaddingId;
+        }
+        if (tid == 0) {
+            PartMeta meta;
+            meta.count = held;
+            meta.wild_id = row_wild_id;
+            meta.wild_bits = row_wild_bits;
+            meta.bad_history = bad_history;
+            p.part_meta[slot] = meta;
+        }
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) sh.is_last = atomicAdd(&p.tickets[row], 1u) == p.splits - 1 ? 1u : 0u;
+        __syncthreads();
+        if (!sh.is_last) return;
+        __threadfence();
+        if (tid == 0) {
+            p.tickets[row] = 0;  // ready for the next launch
+            sh.cand.count = 0;
+        }
+        // gather every split's survivors into the candidate buffer
+        uint32_t total = 0;
+        bad_history = 0;
+        row_wild_id = kPaddingId;
+        row_wild_bits = 0;
+        for (uint32_t s = 0; s < p.splits; s++) {
+            const size_t from = (size_t)row * p.splits + s;
+            const uint4 packed = __ldcg(reinterpret_cast<const uint4 *>(&p.part_meta[from]));
+            PartMeta meta;
+            meta.count = packed.x;
+            meta.wild_id = packed.y;
+            meta.wild_bits = packed.z;
+            meta.bad_history = packed.w;
+            if (tid < meta.count) {
+                sh.cand.score[total + tid] = __ldcg(&p.part_scores[from * kMaxK + tid]);
+                sh.cand.id[total + tid] = __ldcg(&p.part_ids[from * kMaxK + tid]);
+            }
+            total += meta.count;
+            if (meta.bad_history) bad_history = meta.bad_history;
+            if (meta.wild_id < row_wild_id) {
+                row_wild_id = meta.wild_id;
+                row_wild_bits = meta.wild_bits;
+            }
+        }
+        __syncthreads();
+        if (tid == 0) sh.cand.count = total;
+        __syncthreads();
+        held = compact_topk<kThreads, kCandCap>(sh.cand, total, k);
+    }
+
+    // ---- 4. row result ----
+    if (shard_mode) {
+        sort_candidates(sh.cand, sh.fin, held);
+        if (tid < k) {
+            const size_t at = (size_t)row * k + tid;
+            const bool live = tid < held && !bad_history;
+            p.shard_scores[at] = live ? sh.fin.score[tid] : __uint_as_float(0xff800000u);
+            p.shard_ids[at] = live ? sh.fin.id[tid] : kPaddingId;
+        }
+        if (tid == 0) {
+            p.out.row_status[row] = bad_history;
+            if (bad_history)
+                atomicMin(p.out.first_error, ((unsigned long long)row << 8) | bad_history);
+        }
+        return;
+    }
+    if (bad_history) {  // "history token ... is outside vocabulary", src/output.c:610-612
+        if (tid == 0) {
+            report_row(p.out, row, bad_history, kPaddingId, 0.0f);
+            if (p.out.dbg_count) p.out.dbg_count[row] = 0;
+        }
+        return;
+    }
+    if (greedy) {
+        if (tid == 0) {
+            uint32_t status = kOk, token;
+            float logit;
+            if (row_wild_id != kPaddingId) {
+                // a NaN/Inf beats every finite logit in the argmax order and is then
+                // rejected: src/output.c:593 (no penalties) / 737-739 (penalised)
+                status = penalties_active(cfg) ? kErrFormat : kErrMismatch;
+                token = row_wild_id;
+                logit = __uint_as_float(row_wild_bits);
+            } else if (held == 0) {
+                status = kErrMismatch;
+                token = kPaddingId;
+                logit = 0.0f;
+            } else {
+                token = sh.cand.id[0];
+                logit = sh.cand.score[0];
+            }
+            report_row(p.out, row, status, token, logit);
+            if (p.out.dbg_count) {
+                const bool ok = status == kOk;
+                p.out.dbg_count[row] = ok ? 1u : 0u;
+                if (p.out.dbg_ids) p.out.dbg_ids[(size_t)row * kMaxK] = ok ? token : kPaddingId;
+                if (p.out.dbg_scores) p.out.dbg_scores[(size_t)row * kMaxK] = ok ? logit : 0.0f;
+            }
+        }
+        return;
+    }
+    sort_candidates(sh.cand, sh.fin, held);
+    if (warp == 0) finish_select(sh.fin, held, cfg, p.uniforms[row], row, p.out);
+}
+
+// ---------------------------------------------------------------- merge kernel
+//
+// One CTA per row over `shards` blocks of k_shard candidates each (the layout an
+// all-gather leaves: [shard][row][k_shard]); also serves fg_sampler_select
+// (one row, one shard, count candidates).  Range check and fold follow
+// worker_output_split_combine, src/runtime.c:2437-2466.
+
+struct MergeParams {
+    const float *scores;
+    const uint32_t *ids;
+    uint32_t rows, shards, k_shard;
+    uint32_t check_spans;           // sharded merge: range-check ids, a NaN/Inf finalist is an error
+    uint32_t span_first[16], span_width[16];
+    const SamplerConfig *configs;
+    SamplerConfig config0;
+    uint32_t config_count;
+    const float *uniforms;
+    SelectOutput out;
+};
+
+__global__ void __launch_bounds__(kThreads) merge_select_kernel(const MergeParams p) {
+    __shared__ StreamShared sh;
+    const uint32_t tid = threadIdx.x, row = blockIdx.x;
+    const SamplerConfig cfg = p.config_count > 1 ? p.configs[row] : p.config0;
+    const bool greedy = cfg.temperature == 0.0f;
+    const uint32_t k = greedy ? 1u : cfg.top_k;
+    if (tid == 0) {
+        sh.cand.count = 0;
+        sh.bad_history = 0;
+        sh.wild_id = kPaddingId;
+        sh.wild_bits = 0;
+    }
+    __syncthreads();
+    const uint32_t total = p.shards * p.k_shard;  // <= kCandCap, checked by the host
+    for (uint32_t i = tid; i < total; i += kThreads) {
+        const uint32_t shard = i / p.k_shard, within = i % p.k_shard;
+        const size_t at = ((size_t)shard * p.rows + row) * p.k_shard + within;
+        const float score = p.scores[at];
+        const uint32_t id = p.ids[at];
+        if (id == kPaddingId && p.check_spans) continue;  // padding of a short shard
+        if (p.check_spans && (id < p.span_first[shard] || id - p.span_first[shard] >= p.span_width[shard]))
+            sh.bad_history = 1;  // id outside its shard's span
+        if (is_nonfinite(score)) {
+            if (greedy && p.check_spans) atomicMin(&sh.wild_id, id);
+            continue;  // the select step drops non-finite candidates, src/sampler.c:89
+        }
+        const uint32_t slot = atomicAdd(&sh.cand.count, 1u);
+        sh.cand.score[slot] = score;
+        sh.cand.id[slot] = id;
+    }
+    __syncthreads();
+    if (greedy && sh.wild_id != kPaddingId) {
+        for (uint32_t i = tid; i < total; i += kThreads) {
+            const uint32_t shard = i / p.k_shard, within = i % p.k_shard;
+            const size_t at = ((size_t)shard * p.rows + row) * p.k_shard + within;
+            if (p.ids[at] == sh.wild_id && is_nonfinite(p.scores[at]))
+                sh.wild_bits = __float_as_uint(p.scores[at]);
+        }
+    }
+    __syncthreads();
+    if (sh.bad_history) {
+        if (tid == 0) {
+            report_row(p.out, row, kErrMismatch, kPaddingId, 0.0f);
+            if (p.out.dbg_count) p.out.dbg_count[row] = 0;
+        }
+        return;
+    }
+    uint32_t held = sh.cand.count;
+    __syncthreads();
+    held = compact_topk<kThreads, kCandCap>(sh.cand, held, k);
+    if (greedy) {
+        if (tid == 0) {
+            uint32_t status = kOk, token = kPaddingId;
+            float logit = 0.0f;
+            if (sh.wild_id != kPaddingId) {
+                status = kErrMismatch;  // "invalid combined output finalist", runtime.c:2461-2463
+                token = sh.wild_id;
+                logit = __uint_as_float(sh.wild_bits);
+            } else if (held == 0) {
+                status = p.check_spans ? kErrMismatch : kErrFormat;
+            } else {
+                token = sh.cand.id[0];
+                logit = sh.cand.score[0];
+            }
+            report_row(p.out, row, status, token, logit);
+            if (p.out.dbg_count) {
+                const bool ok = status == kOk;
+                p.out.dbg_count[row] = ok ? 1u : 0u;
+                if (p.out.dbg_ids) p.out.dbg_ids[(size_t)row * kMaxK] = ok ? token : kPaddingId;
+                if (p.out.dbg_scores) p.out.dbg_scores[(size_t)row * kMaxK] = ok ? logit : 0.0f;
+            }
+        }
+        return;
+    }
+    sort_candidates(sh.cand, sh.fin, held);
+    if (tid < 32) finish_select(sh.fin, held, cfg, p.uniforms ? p.uniforms[row] : 0.0f, row, p.out);
+}
+
+}  // namespace fgk
+
+// ------------------------------------------------------------------ launchers
+
+using namespace fgk;
+
+static SelectOutput make_output(const fgk_select_output *o) {
+    SelectOutput out;
+    out.tokens = o->tokens;
+    out.token_logits = o->token_logits;
+    out.row_status = o->row_status;
+    out.first_error = reinterpret_cast<unsigned long long *>(o->first_error);
+    out.dbg_count = o->dbg_count;
+    out.dbg_ids = o->dbg_ids;
+    out.dbg_scores = o->dbg_scores;
+    out.dbg_raw = o->dbg_raw;
+    out.dbg_tempered = o->dbg_tempered;
+    return out;
+}
+
+static SamplerConfig to_device_config(const fg_sampler_config *c) {
+    SamplerConfig d;
+    d.temperature = c->temperature;
+    d.top_p = c->top_p;
+    d.top_k = c->top_k;
+    d.presence_penalty = c->presence_penalty;
+    d.frequency_penalty = c->frequency_penalty;
+    d.repetition_penalty = c->repetition_penalty;
+    d.min_p = c->min_p;
+    d.pad_ = 0;
+    d.seed = c->seed;
+    return d;
+}
+
+extern "C" uint32_t fgk_stream_max_splits(void) { return kMaxSplits; }
+extern "C" uint32_t fgk_stream_tile(void) { return kTile; }
+extern "C" uint32_t fgk_stream_threads(void) { return kThreads; }
+extern "C" uint64_t fgk_stream_part_meta_bytes(void) { return sizeof(PartMeta); }
+
+extern "C" int fgk_stream_prepare(void) {
+    // opt in to the large dynamic shared-memory carve-out once per process
+    cudaError_t e = cudaFuncSetAttribute(stream_select_kernel<float>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         FGK_STREAM_MAX_DYNAMIC_SMEM);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(stream_select_kernel<uint16_t>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 FGK_STREAM_MAX_DYNAMIC_SMEM);
+    return (int)e;
+}
+
+extern "C" int fgk_launch_stream_select(const fgk_stream_launch *l, void *stream) {
+    StreamParams p;
+    p.logits = l->logits;
+    p.row_stride = l->row_stride;
+    p.rows = l->rows;
+    p.vocab = l->vocab;
+    p.vocab_offset = l->vocab_offset;
+    p.vocab_total = l->vocab_total;
+    p.splits = l->splits;
+    p.split_len = l->split_len;
+    p.history_tokens = l->history_tokens;
+    p.history_offsets = l->history_offsets;
+    p.configs = reinterpret_cast<const SamplerConfig *>(l->configs_device);
+    p.config0 = to_device_config(&l->config0);
+    p.config_count = l->config_count;
+    p.shard_k = l->shard_k;
+    p.uniforms = l->uniforms;
+    p.shard_scores = l->shard_scores;
+    p.shard_ids = l->shard_ids;
+    p.part_scores = l->part_scores;
+    p.part_ids = l->part_ids;
+    p.part_meta = reinterpret_cast<PartMeta *>(l->part_meta);
+    p.tickets = l->tickets;
+    p.history_max = l->history_max;
+    p.bitmap_words = l->bitmap_words;
+    p.count_capacity = l->count_capacity;
+    p.out = make_output(&l->out);
+    const dim3 grid(l->splits, l->rows);
+    // bitmap, then (only when counts are kept) running popcounts and dense counts
+    const size_t dynamic =
+        ((size_t)(l->count_capacity ? 2 : 1) * l->bitmap_words + l->count_capacity) * sizeof(uint32_t);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (l->dtype == 1u)
+        stream_select_kernel<uint16_t><<<grid, kThreads, dynamic, s>>>(p);
+    else
+        stream_select_kernel<float><<<grid, kThreads, dynamic, s>>>(p);
+    return (int)cudaGetLastError();
+}
+
+extern "C" int fgk_launch_merge_select(const fgk_merge_launch *l, void *stream) {
+    MergeParams p;
+    p.scores = l->scores;
+    p.ids = l->ids;
+    p.rows = l->rows;
+    p.shards = l->shards;
+    p.k_shard = l->k_shard;
+    p.check_spans = l->check_spans;
+    for (int i = 0; i < 16; i++) {
+        p.span_first[i] = l->span_first[i];
+        p.span_width[i] = l->span_width[i];
+    }
+    p.configs = reinterpret_cast<const SamplerConfig *>(l->configs_device);
+    p.config0 = to_device_config(&l->config0);
+    p.config_count = l->config_count;
+    p.uniforms = l->uniforms;
+    p.out = make_output(&l->out);
+    merge_select_kernel<<<l->rows, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
+    return (int)cudaGetLastError();
+}

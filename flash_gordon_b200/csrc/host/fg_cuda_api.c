@@ -1,0 +1,771 @@
+/*
+ * Context, tensors and the device-operator / batched entry points of
+ * fg_cuda_sampler.h.  This layer is C17: it validates arguments with the
+ * reference's rules (src/vk.c:1808-1824, 2237-2256, 2260; src/output.c:601-628,
+ * 702-755), plans the launch and calls the CUDA translation units through
+ * fg_kernels.h.  It performs no sampling arithmetic itself.
+ */
+#include "fg_host_internal.h"
+
+#include <math.h>
+#include <stdlib.h>
+#include <string.h>
+
+/* ------------------------------------------------------------------ helpers */
+
+fg_status fg_cuda_fail(fg_error *err, int cuda_error, const char *what) {
+    /* cudaErrorMemoryAllocation = 2; no device / no driver = 100 / 35 / 3 */
+    fg_status status = FG_ERR_IO;
+    if (cuda_error == 2) status = FG_ERR_OOM;
+    else if (cuda_error == 100 || cuda_error == 35 || cuda_error == 3 || cuda_error == 101 ||
+             cuda_error == 999)
+        status = FG_ERR_UNAVAILABLE;
+    fg_error_set(err, status, "%s failed: %s (cuda error %d)", what, fgk_error_string(cuda_error),
+                 cuda_error);
+    return status;
+}
+
+fg_status fg_cuda_enter(fg_cuda_context *context, fg_error *err) {
+    const int e = fgk_set_device(context->device);
+    return e ? fg_cuda_fail(err, e, "selecting the CUDA device") : FG_OK;
+}
+
+fg_status fg_cuda_reserve(void **buffer, size_t *have, size_t want, bool zero,
+                          fg_cuda_context *context, fg_error *err) {
+    if (*have >= want && *buffer) return FG_OK;
+    /* growing discards the old contents; wait for work that may still read them */
+    int e = fgk_stream_synchronize(context->stream);
+    if (e) return fg_cuda_fail(err, e, "draining the stream");
+    if (*buffer) fgk_free(*buffer);
+    *buffer = NULL;
+    *have = 0;
+    size_t rounded = (size_t)fg_align_up_u64(want + want / 4u, 256u);
+    e = fgk_malloc(buffer, rounded);
+    if (e) return fg_cuda_fail(err, e, "allocating device scratch");
+    if (zero) {
+        e = fgk_memset_async(*buffer, 0, rounded, context->stream);
+        if (e) return fg_cuda_fail(err, e, "clearing device scratch");
+    }
+    *have = rounded;
+    return FG_OK;
+}
+
+fg_status fg_cuda_reserve_pinned(fg_cuda_context *context, size_t want, fg_error *err) {
+    if (context->pinned_bytes >= want && context->pinned) return FG_OK;
+    int e = fgk_stream_synchronize(context->stream);
+    if (e) return fg_cuda_fail(err, e, "draining the stream");
+    if (context->pinned) fgk_host_free(context->pinned);
+    context->pinned = NULL;
+    context->pinned_bytes = 0;
+    size_t rounded = (size_t)fg_align_up_u64(want + want / 4u, 4096u);
+    e = fgk_host_alloc(&context->pinned, rounded);
+    if (e) return fg_cuda_fail(err, e, "allocating pinned host memory");
+    context->pinned_bytes = rounded;
+    return FG_OK;
+}
+
+/* ------------------------------------------------------------------ context */
+
+fg_status fg_cuda_context_create(int device, fg_cuda_context **out, fg_error *err) {
+    if (!out || device < 0) {
+        fg_error_set(err, FG_ERR_ARGUMENT, "invalid CUDA context arguments");
+        return FG_ERR_ARGUMENT;
+    }
+    *out = NULL;
+    int count = 0;
+    int e = fgk_device_count(&count);
+    if (e || count <= 0) {
+        fg_error_set(err, FG_ERR_UNAVAILABLE, "no usable CUDA device: %s",
+                     e ? fgk_error_string(e) : "device count is zero");
+        return FG_ERR_UNAVAILABLE;
+    }
+    if (device >= count) {
+        fg_error_set(err, FG_ERR_ARGUMENT, "CUDA device %d does not exist (%d present)", device, count);
+        return FG_ERR_ARGUMENT;
+    }
+    fg_cuda_context *c = calloc(1, sizeof(*c));
+    if (!c) {
+        fg_error_set(err, FG_ERR_OOM, "out of host memory");
+        return FG_ERR_OOM;
+    }
+    c->device = device;
+    int sms = 0;
+    e = fgk_set_device(device);
+    if (!e) e = fgk_device_sm_count(device, &sms);
+    if (!e) e = fgk_stream_create(&c->own_stream);
+    if (!e) e = fgk_stream_prepare();
+    if (!e) e = fgk_malloc((void **)&c->first_error, 256u);
+    if (e) {
+        fg_status status = fg_cuda_fail(err, e, "opening the CUDA context");
+        fg_cuda_context_destroy(c);
+        return status;
+    }
+    c->stream = c->own_stream;
+    c->sm_count = (uint32_t)sms;
+    *out = c;
+    return FG_OK;
+}
+
+void fg_cuda_context_destroy(fg_cuda_context *c) {
+    if (!c) return;
+    if (fgk_set_device(c->device) == 0) {
+        if (c->stream) fgk_stream_synchronize(c->stream);
+        if (c->parts) fgk_free(c->parts);
+        if (c->tickets) fgk_free(c->tickets);
+        if (c->configs) fgk_free(c->configs);
+        if (c->first_error) fgk_free(c->first_error);
+        if (c->staging) fgk_free(c->staging);
+        if (c->pinned) fgk_host_free(c->pinned);
+        if (c->own_stream) fgk_stream_destroy(c->own_stream);
+    }
+    free(c);
+}
+
+fg_status fg_cuda_context_set_stream(fg_cuda_context *c, void *cuda_stream, fg_error *err) {
+    if (!c) {
+        fg_error_set(err, FG_ERR_ARGUMENT, "invalid CUDA context");
+        return FG_ERR_ARGUMENT;
+    }
+    fg_status status = fg_cuda_enter(c, err);
+    if (status != FG_OK) return status;
+    int e = fgk_stream_synchronize(c->stream); /* scratch is shared between the two streams */
+    if (e) return fg_cuda_fail(err, e, "draining the stream");
+    c->stream = cuda_stream ? cuda_stream : c->own_stream;
+    return FG_OK;
+}
+
+void *fg_cuda_context_stream(const fg_cuda_context *c) { return c ? c->stream : NULL; }
+int fg_cuda_context_device(const fg_cuda_context *c) { return c ? c->device : -1; }
+uint32_t fg_cuda_context_sm_count(const fg_cuda_context *c) { return c ? c->sm_count : 0u; }
+uint64_t fg_cuda_context_launches(const fg_cuda_context *c) { return c ? c->launches : 0u; }
+uint64_t fg_cuda_context_scratch_bytes(const fg_cuda_context *c) { return c ? c->last_scratch_bytes : 0u; }
+
+fg_status fg_cuda_context_set_splits(fg_cuda_context *c, uint32_t splits, fg_error *err) {
+    if (!c || splits > fgk_stream_max_splits()) {
+        fg_error_set(err, FG_ERR_ARGUMENT, "invalid split count");
+        return FG_ERR_ARGUMENT;
+    }
+    c->forced_splits = splits;
+    return FG_OK;
+}
+
+fg_status fg_cuda_begin(fg_cuda_context *c, fg_error *err) {
+    if (!c || c->batch_active) {
+        fg_error_set(err, FG_ERR_ARGUMENT, "invalid CUDA batch begin");
+        return FG_ERR_ARGUMENT;
+    }
+    fg_status status = fg_cuda_enter(c, err);
+    if (status == FG_OK) c->batch_active = true;
+    return status;
+}
+
+fg_status fg_cuda_end(fg_cuda_context *c, fg_error *err) {
+    if (!c || !c->batch_active) {
+        fg_error_set(err, FG_ERR_ARGUMENT, "invalid CUDA batch end");
+        return FG_ERR_ARGUMENT;
+    }
+    c->batch_active = false;
+    fg_status status = fg_cuda_enter(c, err);
+    if (status != FG_OK) return status;
+    const int e = fgk_stream_synchronize(c->stream);
+    return e ? fg_cuda_fail(err, e, "waiting for the CUDA batch") : FG_OK;
+}
+
+bool fg_cuda_batch_active(const fg_cuda_context *c) { return c && c->batch_active; }
+
+/* ------------------------------------------------------------------ tensors */
+
+fg_status fg_cuda_tensor_create(fg_cuda_context *c, uint64_t bytes, fg_cuda_tensor **out,
+                                fg_error *err) {
+    if (!c || !bytes || !out) {
+        fg_error_set(err, FG_ERR_ARGUMENT, "invalid CUDA tensor arguments");
+        return FG_ERR_ARGUMENT;
+    }
+    *out = NULL;
+    fg_status status = fg_cuda_enter(c, err);
+    if (status != FG_OK) return status;
+    fg_cuda_tensor *t = calloc(1, sizeof(*t));
+    if (!t) {
+        fg_error_set(err, FG_ERR_OOM, "out of host memory");
+        return FG_ERR_OOM;
+    }
+    /* round the allocation so 128-bit accesses near the end stay inside it */
+    int e = fgk_malloc((void **)&t->base, (size_t)fg_align_up_u64(bytes, 256u));
+    if (!e) e = fgk_memset_async(t->base, 0, (size_t)fg_align_up_u64(bytes, 256u), c->stream);
+    if (e) {
+        status = fg_cuda_fail(err, e, "allocating a CUDA tensor");
+        if (t->base) fgk_free(t->base);
+        free(t);
+        return status;
+    }
+    t->context = c;
+    t->bytes = bytes;
+    t->owns = true;
+    *out = t;
+    return FG_OK;
+}
+
+fg_status fg_cuda_tensor_view(fg_cuda_tensor *base, uint64_t offset, uint64_t bytes,
+                              fg_cuda_tensor **out, fg_error *err) {
+    if (!base || !out || !bytes || offset > base->bytes || bytes > base->bytes - offset) {
+        fg_error_set(err, FG_ERR_ARGUMENT, "invalid CUDA tensor view");
+        return FG_ERR_ARGUMENT;
+    }
+    fg_cuda_tensor *t = calloc(1, sizeof(*t));
+    if (!t) {
+        fg_error_set(err, FG_ERR_OOM, "out of host memory");
+        return FG_ERR_OOM;
+    }
+    t->context = base->context;
+    t->base = base->base + offset;
+    t->bytes = bytes;
+    t->owns = false;
+    *out = t;
+    return FG_OK;
+}
+
+fg_status fg_cuda_tensor_wrap(fg_cuda_context *c, void *device_pointer, uint64_t bytes,
+                              fg_cuda_tensor **out, fg_error *err) {
+    if (!c || !device_pointer || !bytes || !out) {
+        fg_error_set(err, FG_ERR_ARGUMENT, "invalid CUDA tensor wrap");
+        return FG_ERR_ARGUMENT;
+    }
+    fg_cuda_tensor *t = calloc(1, sizeof(*t));
+    if (!t) {
+        fg_error_set(err, FG_ERR_OOM, "out of host memory");
+        return FG_ERR_OOM;
+    }
+    t->context = c;
+    t->base = device_pointer;
+    t->bytes = bytes;
+    t->owns = false;
+    *out = t;
+    return FG_OK;
+}
+
+void fg_cuda_tensor_destroy(fg_cuda_tensor *t) {
+    if (!t) return;
+    if (t->owns && t->base && fgk_set_device(t->context->device) == 0) {
+        fgk_stream_synchronize(t->context->stream);
+        fgk_free(t->base);
+    }
+    free(t);
+}
+
+uint64_t fg_cuda_tensor_bytes(const fg_cuda_tensor *t) { return t ? t->bytes : 0u; }
+void *fg_cuda_tensor_device_pointer(const fg_cuda_tensor *t) { return t ? t->base : NULL; }
+
+static bool tensor_range(const fg_cuda_tensor *t, uint64_t offset, uint64_t bytes) {
+    return t && offset <= t->bytes && bytes <= t->bytes - offset;
+}
+
+fg_status fg_cuda_tensor_write(fg_cuda_tensor *t, uint64_t offset, const void *data, uint64_t bytes,
+                               fg_error *err) {
+    if (!tensor_range(t, offset, bytes) || (bytes && !data)) {
+        fg_error_set(err, FG_ERR_ARGUMENT, "invalid CUDA tensor write");
+        return FG_ERR_ARGUMENT;
+    }
+    if (!bytes) return FG_OK;
+    fg_status status = fg_cuda_enter(t->context, err);
+    if (status != FG_OK) return status;
+    int e = fgk_copy_to_device_async(t->base + offset, data, (size_t)bytes, t->context->stream);
+    /* the caller may reuse `data` at once */
+    if (!e) e = fgk_stream_synchronize(t->context->stream);
+    return e ? fg_cuda_fail(err, e, "writing a CUDA tensor") : FG_OK;
+}
+
+fg_status fg_cuda_tensor_read(const fg_cuda_tensor *t, uint64_t offset, void *data, uint64_t bytes,
+                              fg_error *err) {
+    if (!tensor_range(t, offset, bytes) || (bytes && !data)) {
+        fg_error_set(err, FG_ERR_ARGUMENT, "invalid CUDA tensor read");
+        return FG_ERR_ARGUMENT;
+    }
+    if (!bytes) return FG_OK;
+    fg_status status = fg_cuda_enter(t->context, err);
+    if (status != FG_OK) return status;
+    int e = fgk_copy_to_host_async(data, t->base + offset, (size_t)bytes, t->context->stream);
+    if (!e) e = fgk_stream_synchronize(t->context->stream);
+    return e ? fg_cuda_fail(err, e, "reading a CUDA tensor") : FG_OK;
+}
+
+/* --------------------------------------------------------- device operators */
+
+static bool on_context(const fg_cuda_context *c, const fg_cuda_tensor *t) {
+    return t && t->context == c;
+}
+
+fg_status fg_cuda_apply_penalties(fg_cuda_context *c, fg_cuda_tensor *logits,
+                                  const fg_cuda_tensor *counts, uint32_t values,
+                                  float presence_penalty, float frequency_penalty,
+                                  float repetition_penalty, fg_error *err) {
+    /* src/vk.c:1812-1819 */
+    if (!c || !values || !on_context(c, logits) || !on_context(c, counts) ||
+        !tensor_range(logits, 0, (uint64_t)values * 4u) ||
+        !tensor_range(counts, 0, (uint64_t)values * 4u) || !isfinite(presence_penalty) ||
+        !isfinite(frequency_penalty) || !isfinite(repetition_penalty) ||
+        repetition_penalty <= 0.0f) {
+        fg_error_set(err, FG_ERR_ARGUMENT, "invalid vocabulary penalty dispatch");
+        return FG_ERR_ARGUMENT;
+    }
+    fg_status status = fg_cuda_enter(c, err);
+    if (status != FG_OK) return status;
+    const int e = fgk_launch_apply_penalties((float *)logits->base, (const uint32_t *)counts->base,
+                                             values, presence_penalty, frequency_penalty,
+                                             repetition_penalty, c->stream);
+    c->launches++;
+    return e ? fg_cuda_fail(err, e, "penalty kernel") : FG_OK;
+}
+
+fg_status fg_cuda_argmax_reduce(fg_cuda_context *c, fg_cuda_tensor *out_scores,
+                                fg_cuda_tensor *out_ids, const fg_cuda_tensor *in_scores,
+                                const fg_cuda_tensor *in_ids, uint32_t count,
+                                uint32_t *output_count, fg_error *err) {
+    const uint32_t groups = (uint32_t)(((uint64_t)count + 4095u) / 4096u);
+    /* src/vk.c:2260 */
+    if (!c || !count || !output_count || !tensor_range(in_scores, 0, (uint64_t)count * 4u) ||
+        (in_ids && !tensor_range(in_ids, 0, (uint64_t)count * 4u)) ||
+        !tensor_range(out_scores, 0, (uint64_t)groups * 4u) ||
+        !tensor_range(out_ids, 0, (uint64_t)groups * 4u)) {
+        fg_error_set(err, FG_ERR_ARGUMENT, "invalid argmax reduction dispatch");
+        return FG_ERR_ARGUMENT;
+    }
+    fg_status status = fg_cuda_enter(c, err);
+    if (status != FG_OK) return status;
+    const int e = fgk_launch_argmax_reduce((float *)out_scores->base, (uint32_t *)out_ids->base,
+                                           (const float *)in_scores->base,
+                                           in_ids ? (const uint32_t *)in_ids->base : NULL, count,
+                                           c->stream);
+    c->launches++;
+    if (e) return fg_cuda_fail(err, e, "argmax kernel");
+    *output_count = groups;
+    return FG_OK;
+}
+
+fg_status fg_cuda_topk_select(fg_cuda_context *c, fg_cuda_tensor *out_scores,
+                              fg_cuda_tensor *out_ids, const fg_cuda_tensor *in_scores,
+                              const fg_cuda_tensor *in_ids, uint32_t count, uint32_t k,
+                              uint32_t *output_count, fg_error *err) {
+    const uint64_t groups = ((uint64_t)count + 1023u) / 1024u;
+    const uint64_t produced = groups * k;
+    /* src/vk.c:2240-2249 */
+    if (!c || !count || k < 1u || k > 64u || !output_count || produced > UINT32_MAX ||
+        !tensor_range(in_scores, 0, (uint64_t)count * 4u) ||
+        (in_ids && !tensor_range(in_ids, 0, (uint64_t)count * 4u)) ||
+        !tensor_range(out_scores, 0, produced * 4u) || !tensor_range(out_ids, 0, produced * 4u)) {
+        fg_error_set(err, FG_ERR_ARGUMENT, "invalid generation top-k selection dispatch");
+        return FG_ERR_ARGUMENT;
+    }
+    fg_status status = fg_cuda_enter(c, err);
+    if (status != FG_OK) return status;
+    const int e = fgk_launch_topk_select((float *)out_scores->base, (uint32_t *)out_ids->base,
+                                         (const float *)in_scores->base,
+                                         in_ids ? (const uint32_t *)in_ids->base : NULL, count, k,
+                                         c->stream);
+    c->launches++;
+    if (e) return fg_cuda_fail(err, e, "top-k kernel");
+    *output_count = (uint32_t)produced;
+    return FG_OK;
+}
+
+fg_status fg_cuda_history_reset(fg_cuda_context *c, fg_cuda_tensor *counts, uint32_t vocab,
+                                const uint32_t *history, uint32_t count, fg_error *err) {
+    /* src/output.c:604-606 */
+    if (!c || !vocab || !on_context(c, counts) || !tensor_range(counts, 0, (uint64_t)vocab * 4u) ||
+        count > FG_NATIVE_CONTEXT || (count && !history)) {
+        fg_error_set(err, FG_ERR_ARGUMENT, "invalid output history");
+        return FG_ERR_ARGUMENT;
+    }
+    fg_status status = fg_cuda_enter(c, err);
+    if (status != FG_OK) return status;
+    const size_t bytes = (size_t)count * 4u;
+    status = fg_cuda_reserve(&c->staging, &c->staging_bytes, bytes + 64u, false, c, err);
+    if (status != FG_OK) return status;
+    uint32_t *bad = (uint32_t *)c->staging;
+    uint32_t *tokens = (uint32_t *)((unsigned char *)c->staging + 64u);
+    const uint32_t none = UINT32_MAX;
+    int e = fgk_memset_async(counts->base, 0, (size_t)vocab * 4u, c->stream);
+    if (!e) e = fgk_copy_to_device_async(bad, &none, 4u, c->stream);
+    if (!e && count) e = fgk_copy_to_device_async(tokens, history, bytes, c->stream);
+    if (!e && count) {
+        e = fgk_launch_history_add((uint32_t *)counts->base, vocab, tokens, count, bad, c->stream);
+        c->launches++;
+    }
+    uint32_t first_bad = UINT32_MAX;
+    if (!e) e = fgk_copy_to_host_async(&first_bad, bad, 4u, c->stream);
+    if (!e) e = fgk_stream_synchronize(c->stream);
+    if (e) return fg_cuda_fail(err, e, "history kernel");
+    if (first_bad != UINT32_MAX) {
+        fg_error_set(err, FG_ERR_FORMAT, "history token %u is outside vocabulary", first_bad);
+        return FG_ERR_FORMAT;
+    }
+    return FG_OK;
+}
+
+fg_status fg_cuda_history_increment(fg_cuda_context *c, fg_cuda_tensor *counts, uint32_t vocab,
+                                    uint32_t token, fg_error *err) {
+    /* src/output.c:621-622 */
+    if (!c || !on_context(c, counts) || !tensor_range(counts, 0, (uint64_t)vocab * 4u) ||
+        token >= vocab) {
+        fg_error_set(err, FG_ERR_ARGUMENT, "invalid output history token");
+        return FG_ERR_ARGUMENT;
+    }
+    fg_status status = fg_cuda_enter(c, err);
+    if (status != FG_OK) return status;
+    status = fg_cuda_reserve(&c->staging, &c->staging_bytes, 128u, false, c, err);
+    if (status != FG_OK) return status;
+    uint32_t *bad = (uint32_t *)c->staging;
+    uint32_t *slot = (uint32_t *)((unsigned char *)c->staging + 64u);
+    int e = fgk_copy_to_device_async(slot, &token, 4u, c->stream);
+    if (!e) {
+        e = fgk_launch_history_add((uint32_t *)counts->base, vocab, slot, 1u, bad, c->stream);
+        c->launches++;
+    }
+    return e ? fg_cuda_fail(err, e, "history kernel") : FG_OK;
+}
+
+/* ------------------------------------------------------------ fused batched */
+
+typedef struct stream_plan {
+    uint32_t splits, split_len, bitmap_words, count_capacity;
+    size_t dynamic_smem;
+} stream_plan;
+
+/* Picks how many CTAs share a row.  More splits fill the SMs when rows are few
+ * and smooth the last wave when they are many; fewer splits amortise the
+ * per-CTA history set-up.  Results do not depend on the choice. */
+static bool plan_stream(const fg_cuda_context *c, uint32_t rows, uint32_t vocab,
+                        uint32_t history_max, bool penalties, bool counts, stream_plan *plan) {
+    const uint32_t max_splits = fgk_stream_max_splits();
+    const uint32_t tile = fgk_stream_tile();
+    const double slots = (double)c->sm_count * 4.0;
+    double best_score = -1.0;
+    stream_plan best = {0};
+    for (uint32_t want = 1; want <= max_splits; want++) {
+        if (c->forced_splits && want != c->forced_splits) continue;
+        uint32_t len = (vocab + want - 1u) / want;
+        len = (len + 127u) & ~127u;
+        const uint32_t splits = (vocab + len - 1u) / len;
+        if (splits != want && !(c->forced_splits && want == c->forced_splits)) continue;
+        stream_plan p;
+        p.splits = splits;
+        p.split_len = len;
+        p.bitmap_words = penalties ? (len + 31u) / 32u : 0u;
+        p.count_capacity = (penalties && counts) ? (history_max < len ? history_max : len) : 0u;
+        if (p.count_capacity == 0u && penalties && counts) p.count_capacity = 1u;
+        p.dynamic_smem = ((size_t)(p.count_capacity ? 2u : 1u) * p.bitmap_words + p.count_capacity) * 4u;
+        if (p.dynamic_smem > FGK_STREAM_MAX_DYNAMIC_SMEM) continue;
+        const double units = (double)rows * splits;
+        const double waves = ceil(units / slots);
+        double score = units / (waves * slots);
+        if (p.dynamic_smem > FGK_STREAM_COMFORT_DYNAMIC_SMEM) score *= 0.6;
+        if (len < 2u * tile && splits > 1u) score *= 0.85;
+        if (score > best_score + 0.03) {
+            best_score = score;
+            best = p;
+        }
+    }
+    if (best_score < 0.0) return false;
+    *plan = best;
+    return true;
+}
+
+typedef struct batch_traits {
+    bool penalties, counts, sampled, nucleus, topk_rows;
+} batch_traits;
+
+static fg_status check_batch(const fg_cuda_context *c, const fg_cuda_sample_args *a, bool shard,
+                             batch_traits *traits, fg_error *err) {
+    if (!c || !a || !a->logits || !a->rows || !a->vocab || a->row_stride < a->vocab ||
+        (a->dtype != FG_CUDA_F32 && a->dtype != FG_CUDA_BF16) || !a->configs ||
+        (a->config_count != 1u && a->config_count != a->rows) || !a->row_status ||
+        (!shard && (!a->tokens || !a->token_logits)) ||
+        ((a->history_tokens == NULL) != (a->history_offsets == NULL)) ||
+        a->history_max > FG_NATIVE_CONTEXT) {
+        fg_error_set(err, FG_ERR_ARGUMENT, "invalid batched sampling arguments");
+        return FG_ERR_ARGUMENT;
+    }
+    memset(traits, 0, sizeof(*traits));
+    const bool allow = (a->flags & FG_CUDA_SAMPLE_ALLOW_NO_TOPK) != 0u && !shard;
+    for (uint32_t i = 0; i < a->config_count; i++) {
+        const fg_sampler_config *cfg = &a->configs[i];
+        if (!fg_cuda_config_ok(cfg, allow)) {
+            fg_error_set(err, FG_ERR_ARGUMENT, "invalid sampler controls");
+            return FG_ERR_ARGUMENT;
+        }
+        if (fg_sampler_penalties_active(cfg)) traits->penalties = true;
+        if (cfg->frequency_penalty != 0.0f) traits->counts = true;
+        if (cfg->temperature != 0.0f) {
+            traits->sampled = true;
+            if (cfg->top_k == 0u) traits->nucleus = true;
+            else traits->topk_rows = true;
+        } else {
+            traits->topk_rows = true;
+        }
+    }
+    if (shard) traits->topk_rows = true;
+    if (traits->sampled && !shard && !a->uniforms) {
+        fg_error_set(err, FG_ERR_ARGUMENT, "sampled rows need one uniform draw each");
+        return FG_ERR_ARGUMENT;
+    }
+    if (!a->history_tokens || a->history_max == 0u) traits->penalties = traits->counts = false;
+    return FG_OK;
+}
+
+static void fill_output(fgk_select_output *out, const fg_cuda_context *c,
+                        const fg_cuda_sample_args *a) {
+    memset(out, 0, sizeof(*out));
+    out->tokens = a->tokens;
+    out->token_logits = a->token_logits;
+    out->row_status = a->row_status;
+    out->first_error = c->first_error;
+    if (a->debug) {
+        out->dbg_count = a->debug->candidate_count;
+        out->dbg_ids = a->debug->candidate_ids;
+        out->dbg_scores = a->debug->candidate_scores;
+        out->dbg_raw = a->debug->raw_probability;
+        out->dbg_tempered = a->debug->tempered_probability;
+    }
+}
+
+/* Uploads per-row configs when they differ; *device is NULL for a shared config. */
+static fg_status upload_configs(fg_cuda_context *c, const fg_cuda_sample_args *a,
+                                const void **device, fg_error *err) {
+    *device = NULL;
+    if (a->config_count == 1u) return FG_OK;
+    const size_t bytes = (size_t)a->config_count * sizeof(fg_sampler_config);
+    fg_status status = fg_cuda_reserve(&c->configs, &c->configs_bytes, bytes, false, c, err);
+    if (status != FG_OK) return status;
+    const int e = fgk_copy_to_device_async(c->configs, a->configs, bytes, c->stream);
+    if (e) return fg_cuda_fail(err, e, "uploading sampler configs");
+    *device = c->configs;
+    return FG_OK;
+}
+
+/* Waits for the stream and turns the device's first-error word into a status. */
+static fg_status collect_status(fg_cuda_context *c, fg_error *err) {
+    uint64_t word = UINT64_MAX;
+    int e = fgk_copy_to_host_async(&word, c->first_error, 8u, c->stream);
+    if (!e) e = fgk_stream_synchronize(c->stream);
+    if (e) return fg_cuda_fail(err, e, "sampling kernels");
+    if (word == UINT64_MAX) return FG_OK;
+    const fg_status status = (fg_status)(word & 0xffu);
+    const uint64_t row = word >> 8;
+    const char *why = "row failed";
+    if (status == FG_ERR_FORMAT) why = "no finite candidate, invalid penalized finalist, softmax failure or history token outside vocabulary";
+    else if (status == FG_ERR_MISMATCH) why = "invalid output finalist";
+    else if (status == FG_ERR_LIMIT) why = "history longer than history_max";
+    fg_error_set(err, status, "row %llu: %s", (unsigned long long)row, why);
+    return status;
+}
+
+static fg_status run_stream(fg_cuda_context *c, const fg_cuda_sample_args *a,
+                            const batch_traits *traits, uint32_t vocab_offset,
+                            uint32_t vocab_total, uint32_t shard_k, float *shard_scores,
+                            uint32_t *shard_ids, fg_error *err) {
+    stream_plan plan;
+    if (!plan_stream(c, a->rows, a->vocab, a->history_max, traits->penalties, traits->counts, &plan)) {
+        fg_error_set(err, FG_ERR_LIMIT, "history structure does not fit shared memory");
+        return FG_ERR_LIMIT;
+    }
+    fg_status status = FG_OK;
+    const size_t slots = (size_t)a->rows * plan.splits;
+    const size_t meta_bytes = (size_t)fgk_stream_part_meta_bytes();
+    const size_t part_bytes = plan.splits > 1u ? slots * (64u * 8u + meta_bytes) : 0u;
+    if (part_bytes) status = fg_cuda_reserve(&c->parts, &c->parts_bytes, part_bytes, false, c, err);
+    if (status == FG_OK)
+        status = fg_cuda_reserve((void **)&c->tickets, &c->tickets_bytes, (size_t)a->rows * 4u, true, c, err);
+    const void *configs_device = NULL;
+    if (status == FG_OK) status = upload_configs(c, a, &configs_device, err);
+    if (status != FG_OK) return status;
+    c->last_scratch_bytes = part_bytes + (size_t)a->rows * 4u +
+                            (a->config_count > 1u ? (size_t)a->rows * sizeof(fg_sampler_config) : 0u);
+
+    fgk_stream_launch l;
+    memset(&l, 0, sizeof(l));
+    l.logits = a->logits;
+    l.dtype = a->dtype;
+    l.rows = a->rows;
+    l.vocab = a->vocab;
+    l.row_stride = a->row_stride;
+    l.vocab_offset = vocab_offset;
+    l.vocab_total = vocab_total;
+    l.splits = plan.splits;
+    l.split_len = plan.split_len;
+    l.history_tokens = traits->penalties ? a->history_tokens : NULL;
+    l.history_offsets = traits->penalties ? a->history_offsets : NULL;
+    l.history_max = a->history_max;
+    l.configs_device = configs_device;
+    l.config0 = a->configs[0];
+    l.config_count = a->config_count;
+    l.shard_k = shard_k;
+    l.uniforms = a->uniforms;
+    l.shard_scores = shard_scores;
+    l.shard_ids = shard_ids;
+    if (part_bytes) {
+        unsigned char *base = c->parts;
+        l.part_scores = (float *)base;
+        l.part_ids = (uint32_t *)(base + slots * 64u * 4u);
+        l.part_meta = base + slots * 64u * 8u;
+    }
+    l.tickets = c->tickets;
+    l.bitmap_words = plan.bitmap_words;
+    l.count_capacity = plan.count_capacity;
+    fill_output(&l.out, c, a);
+    const int e = fgk_launch_stream_select(&l, c->stream);
+    c->launches++;
+    return e ? fg_cuda_fail(err, e, "streaming select kernel") : FG_OK;
+}
+
+static fg_status arm_first_error(fg_cuda_context *c, fg_error *err) {
+    const int e = fgk_memset_async(c->first_error, 0xff, 8u, c->stream);
+    return e ? fg_cuda_fail(err, e, "arming the error word") : FG_OK;
+}
+
+fg_status fg_cuda_sample_batch(fg_cuda_context *c, const fg_cuda_sample_args *a, fg_error *err) {
+    batch_traits traits;
+    fg_status status = check_batch(c, a, false, &traits, err);
+    if (status != FG_OK) return status;
+    if (traits.nucleus) {
+        fg_error_set(err, FG_ERR_UNAVAILABLE, "sampling without a top-k cut is not built yet");
+        return FG_ERR_UNAVAILABLE;
+    }
+    status = fg_cuda_enter(c, err);
+    if (status == FG_OK) status = arm_first_error(c, err);
+    if (status == FG_OK && traits.topk_rows)
+        status = run_stream(c, a, &traits, 0u, a->vocab, 0u, NULL, NULL, err);
+    if (status != FG_OK || (a->flags & FG_CUDA_SAMPLE_ASYNC)) return status;
+    return collect_status(c, err);
+}
+
+fg_status fg_cuda_shard_topk(fg_cuda_context *c, const fg_cuda_sample_args *a, uint32_t vocab_offset,
+                             uint32_t vocab_total, uint32_t k_shard, float *candidate_scores,
+                             uint32_t *candidate_ids, fg_error *err) {
+    batch_traits traits;
+    fg_status status = check_batch(c, a, true, &traits, err);
+    if (status != FG_OK) return status;
+    if (k_shard < 1u || k_shard > 64u || !candidate_scores || !candidate_ids ||
+        (uint64_t)vocab_offset + a->vocab > vocab_total) {
+        fg_error_set(err, FG_ERR_ARGUMENT, "invalid vocabulary shard arguments");
+        return FG_ERR_ARGUMENT;
+    }
+    status = fg_cuda_enter(c, err);
+    if (status == FG_OK) status = arm_first_error(c, err);
+    if (status == FG_OK)
+        status = run_stream(c, a, &traits, vocab_offset, vocab_total, k_shard, candidate_scores,
+                            candidate_ids, err);
+    if (status != FG_OK || (a->flags & FG_CUDA_SAMPLE_ASYNC)) return status;
+    return collect_status(c, err);
+}
+
+fg_status fg_cuda_merge_select(fg_cuda_context *c, const fg_cuda_sample_args *a,
+                               const float *candidate_scores, const uint32_t *candidate_ids,
+                               uint32_t shards, uint32_t k_shard, const uint32_t *shard_first,
+                               const uint32_t *shard_width, fg_error *err) {
+    if (!c || !a || !a->rows || !a->configs || (a->config_count != 1u && a->config_count != a->rows) ||
+        !a->tokens || !a->token_logits || !a->row_status || !candidate_scores || !candidate_ids ||
+        !shards || shards > 16u || k_shard < 1u || k_shard > 64u || !shard_first || !shard_width) {
+        fg_error_set(err, FG_ERR_ARGUMENT, "invalid shard merge arguments");
+        return FG_ERR_ARGUMENT;
+    }
+    bool sampled = false;
+    for (uint32_t i = 0; i < a->config_count; i++) {
+        if (!fg_cuda_config_ok(&a->configs[i], false)) {
+            fg_error_set(err, FG_ERR_ARGUMENT, "invalid sampler controls");
+            return FG_ERR_ARGUMENT;
+        }
+        if (a->configs[i].temperature != 0.0f) {
+            sampled = true;
+            /* the union of shard top-k lists holds the global top-k only up to k_shard */
+            if (a->configs[i].top_k > k_shard) {
+                fg_error_set(err, FG_ERR_ARGUMENT, "top_k %u exceeds the %u candidates each shard sent",
+                             a->configs[i].top_k, k_shard);
+                return FG_ERR_ARGUMENT;
+            }
+        }
+    }
+    if (sampled && !a->uniforms) {
+        fg_error_set(err, FG_ERR_ARGUMENT, "sampled rows need one uniform draw each");
+        return FG_ERR_ARGUMENT;
+    }
+    fg_status status = fg_cuda_enter(c, err);
+    if (status == FG_OK) status = arm_first_error(c, err);
+    const void *configs_device = NULL;
+    if (status == FG_OK) status = upload_configs(c, a, &configs_device, err);
+    if (status != FG_OK) return status;
+    fgk_merge_launch l;
+    memset(&l, 0, sizeof(l));
+    l.scores = candidate_scores;
+    l.ids = candidate_ids;
+    l.rows = a->rows;
+    l.shards = shards;
+    l.k_shard = k_shard;
+    l.check_spans = 1u;
+    for (uint32_t s = 0; s < shards; s++) {
+        l.span_first[s] = shard_first[s];
+        l.span_width[s] = shard_width[s];
+    }
+    l.configs_device = configs_device;
+    l.config0 = a->configs[0];
+    l.config_count = a->config_count;
+    l.uniforms = a->uniforms;
+    fill_output(&l.out, c, a);
+    const int e = fgk_launch_merge_select(&l, c->stream);
+    c->launches++;
+    if (e) return fg_cuda_fail(err, e, "merge kernel");
+    if (a->flags & FG_CUDA_SAMPLE_ASYNC) return FG_OK;
+    return collect_status(c, err);
+}
+
+/* Host-buffer form: stage in, sample, stage out. */
+fg_status fg_cuda_sample_batch_host(fg_cuda_context *c, const fg_cuda_sample_args *h, fg_error *err) {
+    batch_traits traits;
+    fg_status status = check_batch(c, h, false, &traits, err);
+    if (status != FG_OK) return status;
+    if (h->debug) {
+        fg_error_set(err, FG_ERR_ARGUMENT, "the host entry point takes no debug dump");
+        return FG_ERR_ARGUMENT;
+    }
+    status = fg_cuda_enter(c, err);
+    if (status != FG_OK) return status;
+    const size_t element = h->dtype == FG_CUDA_BF16 ? 2u : 4u;
+    const size_t logits_bytes = ((size_t)(h->rows - 1u) * h->row_stride + h->vocab) * element;
+    uint64_t history_total = 0;
+    if (h->history_offsets) history_total = h->history_offsets[h->rows];
+    const size_t offsets_bytes = h->history_offsets ? ((size_t)h->rows + 1u) * 8u : 0u;
+    const size_t tokens_bytes = (size_t)history_total * 4u;
+    const size_t rows4 = (size_t)h->rows * 4u;
+    size_t at = 0;
+#define CARVE(name, bytes) const size_t name = at; at = (size_t)fg_align_up_u64(at + (bytes), 256u)
+    CARVE(at_logits, logits_bytes);
+    CARVE(at_offsets, offsets_bytes);
+    CARVE(at_history, tokens_bytes);
+    CARVE(at_uniforms, rows4);
+    CARVE(at_tokens, rows4);
+    CARVE(at_token_logits, rows4);
+    CARVE(at_status, rows4);
+#undef CARVE
+    status = fg_cuda_reserve(&c->staging, &c->staging_bytes, at, false, c, err);
+    if (status != FG_OK) return status;
+    unsigned char *d = c->staging;
+    int e = fgk_copy_to_device_async(d + at_logits, h->logits, logits_bytes, c->stream);
+    if (!e && offsets_bytes) e = fgk_copy_to_device_async(d + at_offsets, h->history_offsets, offsets_bytes, c->stream);
+    if (!e && tokens_bytes) e = fgk_copy_to_device_async(d + at_history, h->history_tokens, tokens_bytes, c->stream);
+    if (!e && h->uniforms) e = fgk_copy_to_device_async(d + at_uniforms, h->uniforms, rows4, c->stream);
+    if (e) return fg_cuda_fail(err, e, "copying sampling inputs to the device");
+    fg_cuda_sample_args a = *h;
+    a.logits = d + at_logits;
+    a.history_offsets = offsets_bytes ? (const uint64_t *)(d + at_offsets) : NULL;
+    a.history_tokens = offsets_bytes ? (const uint32_t *)(d + at_history) : NULL;
+    a.uniforms = h->uniforms ? (const float *)(d + at_uniforms) : NULL;
+    a.tokens = (uint32_t *)(d + at_tokens);
+    a.token_logits = (float *)(d + at_token_logits);
+    a.row_status = (uint32_t *)(d + at_status);
+    a.flags = h->flags | FG_CUDA_SAMPLE_ASYNC;
+    status = fg_cuda_sample_batch(c, &a, err);
+    if (status != FG_OK) return status;
+    e = fgk_copy_to_host_async(h->tokens, a.tokens, rows4, c->stream);
+    if (!e) e = fgk_copy_to_host_async(h->token_logits, a.token_logits, rows4, c->stream);
+    if (!e) e = fgk_copy_to_host_async(h->row_status, a.row_status, rows4, c->stream);
+    if (e) return fg_cuda_fail(err, e, "copying sampling results to the host");
+    return collect_status(c, err);
+}

@@ -1,0 +1,54 @@
+/* Shared between the host translation units; not installed. */
+#ifndef FG_B200_HOST_INTERNAL_H
+#define FG_B200_HOST_INTERNAL_H
+
+#include "fg_cuda_sampler.h"
+#include "../cuda/fg_kernels.h"
+
+struct fg_cuda_context {
+    int device;
+    void *own_stream;
+    void *stream;
+    uint32_t sm_count;
+    bool batch_active;
+    uint64_t launches;
+    uint32_t forced_splits;
+
+    /* device scratch, grown on demand and then reused (no allocation on a warm call) */
+    void *parts;            /* candidate hand-off between the splits of a row */
+    size_t parts_bytes;
+    uint32_t *tickets;      /* one arrival counter per row, zero between launches */
+    size_t tickets_bytes;
+    void *configs;          /* per-row configs when they differ */
+    size_t configs_bytes;
+    uint64_t *first_error;  /* one device word */
+    void *staging;          /* host-entry inputs and outputs */
+    size_t staging_bytes;
+    void *pinned;           /* pinned host bounce buffer */
+    size_t pinned_bytes;
+    uint64_t last_scratch_bytes;
+};
+
+struct fg_cuda_tensor {
+    fg_cuda_context *context;
+    unsigned char *base;
+    uint64_t bytes;
+    bool owns;
+};
+
+/* cudaError_t (as int) -> fg_status with a message naming `what`. */
+fg_status fg_cuda_fail(fg_error *err, int cuda_error, const char *what);
+/* Makes the context's device current; FG_ERR_UNAVAILABLE on failure. */
+fg_status fg_cuda_enter(fg_cuda_context *context, fg_error *err);
+/* Grow-only device buffer. */
+fg_status fg_cuda_reserve(void **buffer, size_t *have, size_t want, bool zero,
+                          fg_cuda_context *context, fg_error *err);
+fg_status fg_cuda_reserve_pinned(fg_cuda_context *context, size_t want, fg_error *err);
+/* Process-wide context used by the host-pointer fg_sampler_* entry points. */
+fg_status fg_cuda_default_context(fg_cuda_context **out, fg_error *err);
+void fg_cuda_default_lock(void);
+void fg_cuda_default_unlock(void);
+/* fg_sampler_config_validate with the optional "top_k == 0" extension. */
+bool fg_cuda_config_ok(const fg_sampler_config *config, bool allow_no_topk);
+
+#endif

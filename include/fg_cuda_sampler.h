@@ -1,0 +1,242 @@
+/*
+ * CUDA (sm_100a) sampling operators behind a C ABI.
+ *
+ * Three groups of entry points:
+ *
+ *   1. Context and tensors.  A context binds one GPU and one stream and owns
+ *      the scratch the kernels need; a tensor is a byte range of device memory
+ *      (owned, a view of another tensor, or wrapped caller memory).  They stand
+ *      in for the reference's fg_vk_context / fg_vk_tensor
+ *      (include/fg_vk.h:6-8, 89-90, 147-148, 206-224).
+ *
+ *   2. Device operators with the argument meaning and error behaviour of the
+ *      reference's Vulkan wrappers (src/vk.c:1808-1824, 2237-2256, 2260) plus
+ *      the history table of the output executor (src/output.c:601-628).
+ *
+ *   3. Fused batched sampling: one call turns `rows` rows of vocabulary logits
+ *      into `rows` token ids (penalties, greedy argmax or top-k / top-p /
+ *      temperature selection), reading each logit from HBM once.  The
+ *      reference does this one row per call in fg_output_sample
+ *      (src/output.c:702-755); the per-row result is the same.
+ *
+ * Conventions: every function returns fg_status; `err` may be NULL; the
+ * library never frees or retains caller memory; a context is used by one
+ * thread at a time.  Work is enqueued on the context's stream; calls that hand
+ * data back to the host (tensor_read, fg_cuda_end, the *_host entry and the
+ * synchronous form of fg_cuda_sample_batch) wait for it.
+ */
+#ifndef FG_B200_CUDA_SAMPLER_H
+#define FG_B200_CUDA_SAMPLER_H
+
+#include "fg.h"
+#include "fg_sampler.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct fg_cuda_context fg_cuda_context;
+typedef struct fg_cuda_tensor fg_cuda_tensor;
+
+/* ------------------------------------------------------------------ context */
+
+/* Opens `device`, creates the context's stream and scratch.  Stands in for
+ * fg_vk_open (include/fg_vk.h:89).  FG_ERR_UNAVAILABLE when no CUDA device or
+ * driver is usable. */
+fg_status fg_cuda_context_create(int device, fg_cuda_context **out, fg_error *err);
+/* Stands in for fg_vk_close (include/fg_vk.h:90).  NULL is ignored. */
+void fg_cuda_context_destroy(fg_cuda_context *context);
+/* Run on a stream the caller owns (a cudaStream_t passed as void*); NULL
+ * returns to the context's own stream.  No reference counterpart: Vulkan
+ * queues are owned by the reference's context. */
+fg_status fg_cuda_context_set_stream(fg_cuda_context *context, void *cuda_stream, fg_error *err);
+/* The cudaStream_t work is enqueued on. */
+void *fg_cuda_context_stream(const fg_cuda_context *context);
+int fg_cuda_context_device(const fg_cuda_context *context);
+/* Number of streaming multiprocessors of the bound GPU (grid sizing, reports). */
+uint32_t fg_cuda_context_sm_count(const fg_cuda_context *context);
+/* Kernels launched by this context since creation (bench bookkeeping). */
+uint64_t fg_cuda_context_launches(const fg_cuda_context *context);
+/* Tuning knob, no reference counterpart: how many CTAs share one row in the
+ * fused path (0 = chosen per call from rows, vocabulary and SM count; at most
+ * 16).  Results never depend on it. */
+fg_status fg_cuda_context_set_splits(fg_cuda_context *context, uint32_t splits, fg_error *err);
+/* fg_vk_begin / fg_vk_end (include/fg_vk.h:147-148): the reference records
+ * dispatches into one submission and waits on its fence at `end`.  Here begin
+ * only marks the batch; end waits for the stream and surfaces device errors. */
+fg_status fg_cuda_begin(fg_cuda_context *context, fg_error *err);
+fg_status fg_cuda_end(fg_cuda_context *context, fg_error *err);
+bool fg_cuda_batch_active(const fg_cuda_context *context);
+
+/* ------------------------------------------------------------------ tensors */
+
+/* fg_vk_tensor_create (include/fg_vk.h:206): `bytes` of zero-filled device memory. */
+fg_status fg_cuda_tensor_create(fg_cuda_context *context, uint64_t bytes,
+                                fg_cuda_tensor **out, fg_error *err);
+/* fg_vk_tensor_view (include/fg_vk.h:208): a window into `base`; never owns memory. */
+fg_status fg_cuda_tensor_view(fg_cuda_tensor *base, uint64_t offset, uint64_t bytes,
+                              fg_cuda_tensor **out, fg_error *err);
+/* Wrap device memory the caller allocated (e.g. the output of an lm_head GEMM).
+ * No reference counterpart: its tensors are always context allocations. */
+fg_status fg_cuda_tensor_wrap(fg_cuda_context *context, void *device_pointer, uint64_t bytes,
+                              fg_cuda_tensor **out, fg_error *err);
+/* fg_vk_tensor_destroy (include/fg_vk.h:212). */
+void fg_cuda_tensor_destroy(fg_cuda_tensor *tensor);
+/* fg_vk_tensor_bytes (include/fg_vk.h:213). */
+uint64_t fg_cuda_tensor_bytes(const fg_cuda_tensor *tensor);
+/* Device address; plays the part of fg_vk_tensor_map (include/fg_vk.h:217) for
+ * code that hands the memory to other CUDA work.  Not host-dereferenceable. */
+void *fg_cuda_tensor_device_pointer(const fg_cuda_tensor *tensor);
+/* fg_vk_tensor_write / fg_vk_tensor_read (include/fg_vk.h:221-224): host <-> device
+ * copies ordered with the context's stream; read waits for completion. */
+fg_status fg_cuda_tensor_write(fg_cuda_tensor *tensor, uint64_t offset, const void *data,
+                               uint64_t bytes, fg_error *err);
+fg_status fg_cuda_tensor_read(const fg_cuda_tensor *tensor, uint64_t offset, void *data,
+                              uint64_t bytes, fg_error *err);
+
+/* --------------------------------------------------------- device operators */
+
+/* fg_vk_apply_penalties (src/vk.c:1808-1824) + shaders/fg_apply_penalties.comp.
+ * In place over logits[0..values): ids whose count is zero are untouched; the
+ * others get  v = (v > 0 ? v / repetition : v * repetition)  when repetition
+ * != 1, then  v - (frequency * (float)count + presence),  each step rounded to
+ * fp32 with no fused multiply-add (the association of src/sampler.c:46-60). */
+fg_status fg_cuda_apply_penalties(fg_cuda_context *context, fg_cuda_tensor *logits,
+                                  const fg_cuda_tensor *counts, uint32_t values,
+                                  float presence_penalty, float frequency_penalty,
+                                  float repetition_penalty, fg_error *err);
+
+/* fg_vk_argmax_reduce (src/vk.c:2260) + shaders/fg_argmax_reduce.comp.  One
+ * (score, id) winner per 4096-element tile under the reference's total order
+ * (padding id 0xffffffff loses; a non-finite score beats a finite one; then
+ * larger score; then smaller id).  *output_count = ceil(count / 4096).
+ * in_ids == NULL means ids are 0..count-1 (the reference materialises that
+ * table, src/output.c:526-528; here it is never read from memory). */
+fg_status fg_cuda_argmax_reduce(fg_cuda_context *context, fg_cuda_tensor *out_scores,
+                                fg_cuda_tensor *out_ids, const fg_cuda_tensor *in_scores,
+                                const fg_cuda_tensor *in_ids, uint32_t count,
+                                uint32_t *output_count, fg_error *err);
+
+/* fg_vk_topk_select (src/vk.c:2237-2256) + shaders/fg_topk_select*.comp.  The k
+ * best finite (score, id) pairs of every 1024-element tile, ordered inside the
+ * tile by (score descending, id ascending); missing entries are padded with
+ * (-inf, 0xffffffff).  1 <= k <= 64.  *output_count = ceil(count / 1024) * k.
+ * in_ids == NULL means ids are 0..count-1. */
+fg_status fg_cuda_topk_select(fg_cuda_context *context, fg_cuda_tensor *out_scores,
+                              fg_cuda_tensor *out_ids, const fg_cuda_tensor *in_scores,
+                              const fg_cuda_tensor *in_ids, uint32_t count, uint32_t k,
+                              uint32_t *output_count, fg_error *err);
+
+/* fg_output_history_reset (src/output.c:601-617) for a device-resident table:
+ * counts[0..vocab) = occurrences of each id in history[0..count) (host
+ * pointer), saturating at UINT32_MAX.  count <= FG_NATIVE_CONTEXT; an id
+ * >= vocab yields FG_ERR_FORMAT. */
+fg_status fg_cuda_history_reset(fg_cuda_context *context, fg_cuda_tensor *counts,
+                                uint32_t vocab, const uint32_t *history, uint32_t count,
+                                fg_error *err);
+/* fg_output_history_increment (src/output.c:619-628). */
+fg_status fg_cuda_history_increment(fg_cuda_context *context, fg_cuda_tensor *counts,
+                                    uint32_t vocab, uint32_t token, fg_error *err);
+
+/* ------------------------------------------------------------ fused batched */
+
+typedef enum fg_cuda_dtype {
+    FG_CUDA_F32  = 0,
+    FG_CUDA_BF16 = 1   /* widened exactly to fp32 before any arithmetic */
+} fg_cuda_dtype;
+
+/* Bits of fg_cuda_sample_args.flags. */
+#define FG_CUDA_SAMPLE_ASYNC     1u  /* enqueue only; caller reads row_status itself       */
+#define FG_CUDA_SAMPLE_ALLOW_NO_TOPK 2u /* top_k == 0 means "no top-k cut" (top-p over all) */
+
+/* Optional per-row dump of the final candidate list (device pointers, each
+ * rows * 64 entries except count: rows).  Entries are in sampling order
+ * (score descending, id ascending).  probabilities are the doubles the select
+ * step used, rounded to fp64 storage: raw = exp(s_i - s_0) / sum over the
+ * top-k set, tempered = w_i / temp_sum over the top-p survivors (0 beyond). */
+typedef struct fg_cuda_sample_debug {
+    uint32_t *candidate_count;
+    uint32_t *candidate_ids;
+    float    *candidate_scores;
+    double   *raw_probability;
+    double   *tempered_probability;
+} fg_cuda_sample_debug;
+
+/* One batched sampling call.  Device pointers unless marked HOST. */
+typedef struct fg_cuda_sample_args {
+    const void     *logits;          /* rows x row_stride elements of `dtype`               */
+    uint32_t        dtype;           /* fg_cuda_dtype                                         */
+    uint32_t        rows;
+    uint32_t        vocab;           /* logits per row that are read                          */
+    uint32_t        flags;
+    uint64_t        row_stride;      /* elements between row starts, >= vocab                 */
+    const uint32_t *history_tokens;  /* CSR payload; NULL when no row has history             */
+    const uint64_t *history_offsets; /* rows + 1 entries; row r owns [off[r], off[r+1])       */
+    uint32_t        history_max;     /* HOST-known upper bound of any row's history length    */
+    uint32_t        config_count;    /* 1 (shared by all rows) or rows                        */
+    const fg_sampler_config *configs;/* HOST pointer                                          */
+    const float    *uniforms;        /* rows; one U[0,1) draw per row (unused by greedy rows) */
+    uint32_t       *tokens;          /* out, rows                                             */
+    float          *token_logits;    /* out, rows: penalised raw logit of the pick            */
+    uint32_t       *row_status;      /* out, rows: fg_status per row                          */
+    const fg_cuda_sample_debug *debug; /* HOST pointer to the struct; may be NULL             */
+} fg_cuda_sample_args;
+
+/* Per row: A. history -> counts (src/output.c:601-617); B. penalties
+ * (src/sampler.c:46-60); C. temperature == 0: argmax under the reference's
+ * total order, a non-finite winner is an error (FG_ERR_FORMAT with penalties
+ * active, FG_ERR_MISMATCH without; src/output.c:593, 737-739); temperature > 0:
+ * the top_k best finite logits (score descending, id ascending), then top-p on
+ * the untempered softmax of that set, then temperature softmax and inverse CDF
+ * with the row's uniform (src/sampler.c:80-122).
+ * Configs are validated like fg_sampler_config_validate; with
+ * FG_CUDA_SAMPLE_ALLOW_NO_TOPK, top_k == 0 is also accepted.
+ * Returns the status of the lowest failing row (FG_OK when all rows are OK);
+ * with FG_CUDA_SAMPLE_ASYNC returns after enqueueing. */
+fg_status fg_cuda_sample_batch(fg_cuda_context *context, const fg_cuda_sample_args *args,
+                               fg_error *err);
+
+/* Same call with every buffer in HOST memory: copies inputs to the device,
+ * samples, copies tokens / token_logits / row_status back.  This is what a
+ * reference-shaped caller (logits produced elsewhere, token needed on the
+ * host) binds; `debug` must be NULL. */
+fg_status fg_cuda_sample_batch_host(fg_cuda_context *context, const fg_cuda_sample_args *host_args,
+                                    fg_error *err);
+
+/* Vocabulary-sharded sampling, step 1 (per GPU).  The logits are columns
+ * [vocab_offset, vocab_offset + args->vocab) of a vocab_total-wide head;
+ * history ids are global and only those inside the shard are applied.  Writes
+ * the shard's k_shard best finite (score, global id) pairs per row, padded
+ * with (-inf, 0xffffffff), into candidate_scores / candidate_ids
+ * (rows x k_shard, device).  The reference's analogue is the split head's
+ * per-slice argmax partial (src/output.c:320-344, ids pre-offset by
+ * first_row); here the partial carries k_shard entries instead of one.
+ * tokens / token_logits / uniforms of `args` are ignored. */
+fg_status fg_cuda_shard_topk(fg_cuda_context *context, const fg_cuda_sample_args *args,
+                             uint32_t vocab_offset, uint32_t vocab_total, uint32_t k_shard,
+                             float *candidate_scores, uint32_t *candidate_ids, fg_error *err);
+
+/* Step 2, after the exchange: every row has `shards` blocks of k_shard
+ * candidates, laid out [shard][row][k_shard] (the order an all-gather leaves
+ * them in).  Each candidate id must lie inside its shard's span
+ * [shard_first[s], shard_first[s] + shard_width[s]) (HOST arrays), else the
+ * row fails with FG_ERR_MISMATCH — the check of worker_output_split_combine
+ * (src/runtime.c:2437-2466).  Then the merged set is sampled exactly as in
+ * fg_cuda_sample_batch (greedy rows: fold under the argmax total order).
+ * Uses configs / uniforms / tokens / token_logits / row_status / debug /
+ * rows / flags of `args`. */
+fg_status fg_cuda_merge_select(fg_cuda_context *context, const fg_cuda_sample_args *args,
+                               const float *candidate_scores, const uint32_t *candidate_ids,
+                               uint32_t shards, uint32_t k_shard,
+                               const uint32_t *shard_first, const uint32_t *shard_width,
+                               fg_error *err);
+
+/* Bytes of context scratch the last fg_cuda_sample_batch / shard_topk used
+ * (reports and tests). */
+uint64_t fg_cuda_context_scratch_bytes(const fg_cuda_context *context);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* FG_B200_CUDA_SAMPLER_H */
