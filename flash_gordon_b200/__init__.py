@@ -123,6 +123,7 @@ def load_library() -> ctypes.CDLL:
         "fg_cuda_context_create": (c_int, [c_int, POINTER(P), E]),
         "fg_cuda_context_destroy": (None, [P]),
         "fg_cuda_context_set_stream": (c_int, [P, P, E]),
+        "fg_cuda_context_reset_stream": (c_int, [P, E]),
         "fg_cuda_context_stream": (P, [P]),
         "fg_cuda_context_device": (c_int, [P]),
         "fg_cuda_context_sm_count": (u32, [P]),

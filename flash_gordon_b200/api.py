@@ -276,6 +276,26 @@ class Context:
             raise FgStatusError(status, err.text())
         return SampleResult(out[0], out[1], out[2], status, err.text(), dbg)
 
+    def prepared_sample(self, logits, configs, uniforms, history_tokens, history_offsets,
+                        history_max, out, allow_no_topk: bool = False, asynchronous: bool = True):
+        """Builds the argument block once; the returned callable re-issues the same
+        fg_cuda_sample_batch call (decode loops call it once per step)."""
+        flags = (FG_CUDA_SAMPLE_ASYNC if asynchronous else 0) | \
+                (FG_CUDA_SAMPLE_ALLOW_NO_TOPK if allow_no_topk else 0)
+        args, keep = self._args(logits, configs, uniforms, history_tokens, history_offsets,
+                                history_max, None, flags, out, None)
+        err = FgError()
+        call, handle, args_ref, err_ref = self.lib.fg_cuda_sample_batch, self.handle, byref(args), byref(err)
+
+        def issue() -> int:
+            status = call(handle, args_ref, err_ref)
+            if status != FG_OK:
+                raise FgStatusError(status, err.text())
+            return status
+
+        issue.keepalive = (args, keep, err, logits, uniforms, history_tokens, history_offsets, out)
+        return issue
+
     def sample_batch_host(self, logits: torch.Tensor, configs, uniforms: torch.Tensor | None,
                           history_tokens: torch.Tensor | None, history_offsets: torch.Tensor | None,
                           history_max: int, out=None, allow_no_topk: bool = False) -> SampleResult:

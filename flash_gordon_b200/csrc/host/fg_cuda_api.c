@@ -130,8 +130,12 @@ fg_status fg_cuda_context_set_stream(fg_cuda_context *c, void *cuda_stream, fg_e
     if (status != FG_OK) return status;
     int e = fgk_stream_synchronize(c->stream); /* scratch is shared between the two streams */
     if (e) return fg_cuda_fail(err, e, "draining the stream");
-    c->stream = cuda_stream ? cuda_stream : c->own_stream;
+    c->stream = cuda_stream;
     return FG_OK;
+}
+
+fg_status fg_cuda_context_reset_stream(fg_cuda_context *c, fg_error *err) {
+    return fg_cuda_context_set_stream(c, c ? c->own_stream : NULL, err);
 }
 
 void *fg_cuda_context_stream(const fg_cuda_context *c) { return c ? c->stream : NULL; }

@@ -46,10 +46,12 @@ typedef struct fg_cuda_tensor fg_cuda_tensor;
 fg_status fg_cuda_context_create(int device, fg_cuda_context **out, fg_error *err);
 /* Stands in for fg_vk_close (include/fg_vk.h:90).  NULL is ignored. */
 void fg_cuda_context_destroy(fg_cuda_context *context);
-/* Run on a stream the caller owns (a cudaStream_t passed as void*); NULL
- * returns to the context's own stream.  No reference counterpart: Vulkan
- * queues are owned by the reference's context. */
+/* Run on a stream the caller owns (a cudaStream_t passed as void*; NULL is the
+ * CUDA default stream).  No reference counterpart: Vulkan queues are owned by
+ * the reference's context. */
 fg_status fg_cuda_context_set_stream(fg_cuda_context *context, void *cuda_stream, fg_error *err);
+/* Back to the stream the context created for itself. */
+fg_status fg_cuda_context_reset_stream(fg_cuda_context *context, fg_error *err);
 /* The cudaStream_t work is enqueued on. */
 void *fg_cuda_context_stream(const fg_cuda_context *context);
 int fg_cuda_context_device(const fg_cuda_context *context);
