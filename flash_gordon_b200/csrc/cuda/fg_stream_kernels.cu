@@ -14,10 +14,16 @@
 //   3. hands its k best to the row's last-arriving CTA (ticket counter), which
 //      merges the splits and runs the select step of src/sampler.c:80-122.
 // Logits are read once; nothing vocabulary-sized is written.
+#include <type_traits>
+
 #include "fg_block_select.cuh"
 #include "fg_kernels.h"
 
 namespace fgk {
+
+#ifndef FGK_STREAM_MIN_CTAS
+#define FGK_STREAM_MIN_CTAS 3
+#endif
 
 constexpr int kThreads = 256;
 constexpr int kElemsPerThread = 16;
@@ -63,6 +69,7 @@ struct StreamShared {
     uint32_t scan[kThreads / 32];
     uint32_t distinct;
     uint32_t bad_history;
+    unsigned long long wild_key;  // greedy rows: min over NaN/Inf of (id << 32 | value bits)
     uint32_t wild_id;
     uint32_t wild_bits;
     uint32_t is_last;
@@ -153,8 +160,129 @@ __device__ __forceinline__ uint32_t block_kth_key(uint32_t my_key, uint32_t k) {
     return found;
 }
 
+// Sixteen logits of one thread, passed by value into the rarely taken paths so the
+// hot loop keeps them in registers.
+struct Values16 {
+    float v[kElemsPerThread];
+};
+
+// Per-element look at one thread's values: which ones are finite and can still make
+// the top k (bit e of the result), and, for greedy rows, the smallest id holding a
+// NaN/Inf (merged into sh.wild_key as id << 32 | value bits).  `inclusive` admits
+// ties with the bound: they can only matter inside the tile that produced the bound,
+// because later columns carry larger ids and lose the tie.
 template <typename T>
-__global__ void __launch_bounds__(kThreads, 4) stream_select_kernel(const StreamParams p) {
+__device__ __forceinline__ uint32_t classify(const Values16 &x, uint32_t tile_base, uint32_t n,
+                                             float tau, bool inclusive, bool greedy,
+                                             uint32_t id_base, unsigned long long *wild_key) {
+    using L = Loader<T>;
+    uint32_t pending = 0;
+#pragma unroll
+    for (int e = 0; e < kElemsPerThread; e++) {
+        const uint32_t column = column_of<T>(tile_base, e / L::kPerVector, e % L::kPerVector);
+        if (column >= n) continue;
+        const bool wild = is_nonfinite(x.v[e]);
+        if (wild) {
+            if (greedy)
+                atomicMin(wild_key, ((unsigned long long)(id_base + column) << 32) |
+                                        __float_as_uint(x.v[e]));
+            continue;
+        }
+        if (inclusive ? x.v[e] >= tau : x.v[e] > tau) pending |= 1u << e;
+    }
+    return pending;
+}
+
+// Appends the pending values of a warp to the candidate list (one shared-memory
+// atomic per element position and warp).  Stored bits are cleared from `pending`;
+// returns true when the list is past half full or a value found no slot.
+template <typename T>
+__device__ __forceinline__ bool append_pending(CandidateBuffer<kCandCap> &cand, const Values16 &x,
+                                               uint32_t &pending, uint32_t tile_base,
+                                               uint32_t id_base) {
+    using L = Loader<T>;
+    const uint32_t lane = lane_id();
+    bool trouble = false;
+#pragma unroll
+    for (int e = 0; e < kElemsPerThread; e++) {
+        const bool mine = (pending >> e) & 1u;
+        const unsigned votes = __ballot_sync(kFullMask, mine);
+        if (votes == 0) continue;
+        const int leader = __ffs(votes) - 1;
+        uint32_t base = 0;
+        if ((int)lane == leader) {
+            base = atomicAdd(&cand.count, (uint32_t)__popc(votes));
+            // ask for a cut well before the list is full: it also lifts the bound
+            if (base + __popc(votes) > kCandCap / 2) trouble = true;
+        }
+        base = __shfl_sync(kFullMask, base, leader);
+        if (mine) {
+            const uint32_t slot = base + __popc(votes & ((1u << lane) - 1u));
+            if (slot < kCandCap) {
+                cand.score[slot] = x.v[e];
+                cand.id[slot] =
+                    id_base + column_of<T>(tile_base, e / L::kPerVector, e % L::kPerVector);
+                pending &= ~(1u << e);
+            } else {
+                trouble = true;
+            }
+        }
+    }
+    return trouble;
+}
+
+// Warp-level slow path of a tile: some lane holds a value above the bound (or, on a
+// greedy row, a NaN/Inf), or the tile is one that looks at every element anyway.  Returns this thread's leftovers and whether the
+// block must cut the list.
+template <typename T>
+__device__ __noinline__ uint32_t tile_slow_path(CandidateBuffer<kCandCap> &cand, Values16 x,
+                                                uint32_t tile_base, uint32_t n, float tau,
+                                                bool inclusive, bool greedy, uint32_t id_base,
+                                                unsigned long long *wild_key, bool *trouble) {
+    uint32_t pending = classify<T>(x, tile_base, n, tau, inclusive, greedy, id_base, wild_key);
+    *trouble = false;
+    if (__any_sync(kFullMask, pending != 0))
+        *trouble = append_pending<T>(cand, x, pending, tile_base, id_base);
+    return pending;
+}
+
+// Block-level: the list is (nearly) full.  Cut it back to the k best, which lifts
+// the bound, drop leftovers that no longer qualify, and store the rest; repeat until
+// nothing is left over.  Every thread of the CTA calls this together.  Returns the
+// new bound.
+template <typename T>
+__device__ __noinline__ float resolve_overflow(CandidateBuffer<kCandCap> &cand, Values16 x,
+                                               uint32_t pending, uint32_t tile_base, uint32_t k,
+                                               uint32_t id_base) {
+    using L = Loader<T>;
+    float tau;
+    for (;;) {
+        const uint32_t held = min(cand.count, (uint32_t)kCandCap);
+        __syncthreads();  // everyone has read count before the cut rewrites it
+        compact_topk<kThreads, kCandCap>(cand, held, k);
+        tau = cand.tau_score;
+        const uint32_t tau_id = cand.tau_id;
+        bool left = false;
+#pragma unroll
+        for (int e = 0; e < kElemsPerThread; e++) {
+            if ((pending >> e) & 1u) {
+                const uint32_t id =
+                    id_base + column_of<T>(tile_base, e / L::kPerVector, e % L::kPerVector);
+                if (precedes(x.v[e], id, tau, tau_id)) left = true;
+                else pending &= ~(1u << e);
+            }
+        }
+        if (!__syncthreads_or(left)) break;
+        bool trouble = false;
+        if (__any_sync(kFullMask, pending != 0))
+            trouble = append_pending<T>(cand, x, pending, tile_base, id_base);
+        if (!__syncthreads_or(trouble)) break;
+    }
+    return tau;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads, FGK_STREAM_MIN_CTAS) stream_select_kernel(const StreamParams p) {
     using L = Loader<T>;
     extern __shared__ __align__(16) uint32_t dyn_smem[];
     __shared__ StreamShared sh;
@@ -182,8 +310,7 @@ __global__ void __launch_bounds__(kThreads, 4) stream_select_kernel(const Stream
         sh.cand.tau_score = __uint_as_float(0xff800000u);
         sh.cand.tau_id = kPaddingId;
         sh.bad_history = 0;
-        sh.wild_id = kPaddingId;
-        sh.wild_bits = 0;
+        sh.wild_key = ~0ull;
         sh.distinct = 0;
     }
     __syncthreads();
@@ -257,58 +384,91 @@ __global__ void __launch_bounds__(kThreads, 4) stream_select_kernel(const Stream
                     if (at < p.count_capacity) atomicAdd(&dense[at], 1u);
                 }
             }
+            __syncthreads();
+            // counts -> the offset each seen id is charged, once per row instead of per use
+            for (uint32_t i = tid; i < distinct; i += kThreads)
+                dense[i] = __float_as_uint(
+                    penalty_offset(dense[i], cfg.presence_penalty, cfg.frequency_penalty));
         }
     }
     __syncthreads();
+    const Repetition repetition = make_repetition(cfg.repetition_penalty);
+    // without a count array frequency is +-0 and the product does not depend on the count
+    const float flat_offset = penalty_offset(1u, cfg.presence_penalty, cfg.frequency_penalty);
 
     // ---- 2. stream the columns ----
+    // Tiles 1 .. full-1 of a 16-byte aligned row take the fast path: loads at constant
+    // offsets from one running pointer, one bitmap word per vector, one compare per
+    // vector.  Tile 0 (it sets the admission bound), a ragged last tile and unaligned
+    // rows look at every element.  The two kinds live in separate loops so the hot one
+    // stays small.
     const uint32_t tiles = (n + kTile - 1) / kTile;
-    uint32_t wild_id = kPaddingId, wild_bits = 0;
+    const uint32_t full_tiles = aligned ? n / kTile : 0;
+    const uint32_t id_base = p.vocab_offset + lo;
+    const uint4 *fast_source = reinterpret_cast<const uint4 *>(columns) + tid;
+    constexpr uint32_t kTileVectors = kTile / L::kPerVector;  // 128-bit vectors per tile
+    // this thread's vector u sits in bitmap word (tile_base / 32) + u * kWordsPerStep +
+    // word_lane, at bit bit_lane
+    constexpr uint32_t kWordsPerStep = kThreads * L::kPerVector / 32;
+    const uint32_t word_lane = tid * L::kPerVector / 32;
+    const uint32_t bit_lane = (tid * L::kPerVector) & 31u;
     float tau = __uint_as_float(0xff800000u);
-    for (uint32_t t = 0; t < tiles; t++) {
-        const uint32_t tile_base = t * kTile;
-        float v[kElemsPerThread];
-#pragma unroll
-        for (int u = 0; u < L::kVectors; u++) L::unpack(raw[u], &v[u * L::kPerVector]);
-        if (t + 1 < tiles) load_tile<T>(columns, tile_base + kTile, n, aligned, raw);
 
+    // one tile: penalise seen ids in registers, pick out what may still make the top k
+    auto process = [&](auto fast_tag, uint32_t t, float (&v)[kElemsPerThread]) {
+        constexpr bool fast = decltype(fast_tag)::value;
+        const uint32_t tile_base = t * kTile;
         if (seen_any) {
+            const uint32_t *words_here = bitmap + (tile_base >> 5) + word_lane;
+            const uint32_t *running_here = running + (tile_base >> 5) + word_lane;
 #pragma unroll
             for (int u = 0; u < L::kVectors; u++) {
-                const uint32_t first = column_of<T>(tile_base, u, 0);
-                if (first >= n) continue;
-                const uint32_t word = bitmap[first >> 5];
-                const uint32_t bits = (word >> (first & 31u)) & ((1u << L::kPerVector) - 1u);
+                if (!fast && column_of<T>(tile_base, u, 0) >= n) continue;
+                const uint32_t word = words_here[u * kWordsPerStep];
+                const uint32_t bits = (word >> bit_lane) & ((1u << L::kPerVector) - 1u);
                 if (bits == 0) continue;
 #pragma unroll
                 for (int j = 0; j < L::kPerVector; j++) {
                     if (bits & (1u << j)) {
-                        uint32_t seen = 1;
+                        float offset = flat_offset;
                         if (with_counts) {
-                            const uint32_t below = (1u << ((first & 31u) + j)) - 1u;
-                            seen = dense[min(running[first >> 5] + __popc(word & below),
-                                             p.count_capacity - 1)];
+                            const uint32_t below = (1u << (bit_lane + j)) - 1u;
+                            offset = __uint_as_float(
+                                dense[min(running_here[u * kWordsPerStep] + __popc(word & below),
+                                          p.count_capacity - 1)]);
                         }
                         v[u * L::kPerVector + j] =
-                            penalise(v[u * L::kPerVector + j], seen, cfg.presence_penalty,
-                                     cfg.frequency_penalty, cfg.repetition_penalty);
+                            penalise_with_offset(v[u * L::kPerVector + j], offset, repetition);
                     }
                 }
             }
         }
-
-        // which of my 16 values exist, are finite, and can still make the top k
-        const bool ragged = tile_base + kTile > n;
-        uint32_t pending = 0;
-        if (t == 0) {
-            // First tile: a valid lower bound for the k-th best is the k-th largest of
-            // the per-thread maxima (k distinct elements are at least that large).
+        bool look = !fast;  // does any lane of this warp have to look at single elements?
+        if (fast) {
+            bool hot = false;  // a value above the bound (NaN never compares above)
+#pragma unroll
+            for (int u = 0; u < L::kVectors; u++) {
+                float top = v[u * L::kPerVector];
+#pragma unroll
+                for (int j = 1; j < L::kPerVector; j++) top = fmaxf(top, v[u * L::kPerVector + j]);
+                hot = hot || top > tau;
+            }
+            if (greedy) {  // the argmax order must see NaN and both infinities
+                uint32_t widest = 0;
+#pragma unroll
+                for (int e = 0; e < kElemsPerThread; e++)
+                    widest = max(widest, __float_as_uint(v[e]) & 0x7fffffffu);
+                hot = hot || widest >= 0x7f800000u;
+            }
+            look = __any_sync(kFullMask, hot);
+        } else if (t == 0) {
+            // A valid lower bound for the k-th best: the k-th largest of the per-thread
+            // maxima (k distinct elements are at least that large).
             float best = __uint_as_float(0xff800000u);
             uint32_t have = 0;
 #pragma unroll
             for (int e = 0; e < kElemsPerThread; e++) {
-                const bool exists =
-                    !ragged || column_of<T>(tile_base, e / L::kPerVector, e % L::kPerVector) < n;
+                const bool exists = column_of<T>(tile_base, e / L::kPerVector, e % L::kPerVector) < n;
                 if (exists && !is_nonfinite(v[e])) {
                     best = fmaxf(best, v[e]);
                     have = 1;
@@ -316,75 +476,54 @@ __global__ void __launch_bounds__(kThreads, 4) stream_select_kernel(const Stream
             }
             tau = key_to_float(block_kth_key(have ? float_key(best) : 0u, k));
         }
+        uint32_t pending = 0;
+        bool trouble = false;
+        if (look) {  // rare on the fast path: the values travel by value, off the hot registers
+            Values16 x;
 #pragma unroll
-        for (int e = 0; e < kElemsPerThread; e++) {
-            const bool exists =
-                !ragged || column_of<T>(tile_base, e / L::kPerVector, e % L::kPerVector) < n;
-            const bool wild = is_nonfinite(v[e]);
-            if (greedy && exists && wild) {
-                const uint32_t id =
-                    p.vocab_offset + lo + column_of<T>(tile_base, e / L::kPerVector, e % L::kPerVector);
-                if (id < wild_id) {
-                    wild_id = id;
-                    wild_bits = __float_as_uint(v[e]);
-                }
-            }
-            // ties with the bound can only matter inside the tile that produced it:
-            // later columns carry larger ids and lose the tie
-            const bool pass = t == 0 ? v[e] >= tau : v[e] > tau;
-            if (exists && !wild && pass) pending |= 1u << e;
+            for (int e = 0; e < kElemsPerThread; e++) x.v[e] = v[e];
+            pending = tile_slow_path<T>(sh.cand, x, tile_base, n, tau, t == 0, greedy, id_base,
+                                        &sh.wild_key, &trouble);
         }
+        // one barrier per tile: does anybody need the list cut back?
+        if (__syncthreads_or(trouble)) {
+            Values16 x;
+#pragma unroll
+            for (int e = 0; e < kElemsPerThread; e++) x.v[e] = v[e];
+            tau = resolve_overflow<T>(sh.cand, x, pending, tile_base, k, id_base);
+        }
+    };
 
-        // append; when the list overflows, cut it back to k and retry what is left
-        for (;;) {
-            bool trouble = false;
-            if (__any_sync(kFullMask, pending != 0)) {
+    {
+        float v[kElemsPerThread];
 #pragma unroll
-                for (int e = 0; e < kElemsPerThread; e++) {
-                    const bool mine = (pending >> e) & 1u;
-                    const unsigned votes = __ballot_sync(kFullMask, mine);
-                    if (votes == 0) continue;
-                    const int leader = __ffs(votes) - 1;
-                    uint32_t base = 0;
-                    if ((int)lane == leader) {
-                        base = atomicAdd(&sh.cand.count, (uint32_t)__popc(votes));
-                        // ask for a cut well before the list is full: it also lifts tau
-                        if (base + __popc(votes) > kCandCap / 2) trouble = true;
-                    }
-                    base = __shfl_sync(kFullMask, base, leader);
-                    if (mine) {
-                        const uint32_t slot = base + __popc(votes & ((1u << lane) - 1u));
-                        if (slot < kCandCap) {
-                            sh.cand.score[slot] = v[e];
-                            sh.cand.id[slot] = p.vocab_offset + lo +
-                                               column_of<T>(tile_base, e / L::kPerVector,
-                                                            e % L::kPerVector);
-                            pending &= ~(1u << e);
-                        } else {
-                            trouble = true;
-                        }
-                    }
-                }
-            }
-            if (!__syncthreads_or(trouble)) break;
-            const uint32_t held = min(sh.cand.count, (uint32_t)kCandCap);
-            __syncthreads();  // everyone has read count before compact rewrites it
-            compact_topk<kThreads, kCandCap>(sh.cand, held, k);
-            if (held <= k && tid == 0) sh.cand.count = held;  // (cannot happen: held > cap/2 > k)
-            tau = sh.cand.tau_score;
-            const uint32_t tau_id = sh.cand.tau_id;
-            bool left = false;
+        for (int u = 0; u < L::kVectors; u++) L::unpack(raw[u], &v[u * L::kPerVector]);
+        if (1 < full_tiles) {
 #pragma unroll
-            for (int e = 0; e < kElemsPerThread; e++) {
-                if ((pending >> e) & 1u) {
-                    const uint32_t id = p.vocab_offset + lo +
-                                        column_of<T>(tile_base, e / L::kPerVector, e % L::kPerVector);
-                    if (precedes(v[e], id, tau, tau_id)) left = true;
-                    else pending &= ~(1u << e);
-                }
-            }
-            if (!__syncthreads_or(left)) break;
+            for (int u = 0; u < L::kVectors; u++)
+                raw[u] = load_stream_128(fast_source + kTileVectors + u * kThreads);
         }
+        process(std::false_type{}, 0, v);
+    }
+    for (uint32_t t = 1; t < full_tiles; t++) {
+        float v[kElemsPerThread];
+#pragma unroll
+        for (int u = 0; u < L::kVectors; u++) L::unpack(raw[u], &v[u * L::kPerVector]);
+        if (t + 1 < full_tiles) {
+            const uint4 *next = fast_source + (size_t)(t + 1) * kTileVectors;
+#pragma unroll
+            for (int u = 0; u < L::kVectors; u++) raw[u] = load_stream_128(next + u * kThreads);
+        }
+        process(std::true_type{}, t, v);
+    }
+    // what the fast loop did not cover: the ragged end of an aligned row, or every
+    // further tile of an unaligned one (loaded without prefetch)
+    for (uint32_t t = full_tiles > 1 ? full_tiles : 1; t < tiles; t++) {
+        load_tile<T>(columns, t * kTile, n, aligned, raw);
+        float v[kElemsPerThread];
+#pragma unroll
+        for (int u = 0; u < L::kVectors; u++) L::unpack(raw[u], &v[u * L::kPerVector]);
+        process(std::false_type{}, t, v);
     }
 
     // ---- 3. this split's k best ----
@@ -392,13 +531,11 @@ __global__ void __launch_bounds__(kThreads, 4) stream_select_kernel(const Stream
     uint32_t held = min(sh.cand.count, (uint32_t)kCandCap);
     __syncthreads();
     held = compact_topk<kThreads, kCandCap>(sh.cand, held, k);
-    if (greedy && wild_id != kPaddingId) atomicMin(&sh.wild_id, wild_id);
-    __syncthreads();
-    if (greedy && wild_id != kPaddingId && wild_id == sh.wild_id) sh.wild_bits = wild_bits;
     __syncthreads();
 
     uint32_t bad_history = sh.bad_history;
-    uint32_t row_wild_id = sh.wild_id, row_wild_bits = sh.wild_bits;
+    uint32_t row_wild_id = (uint32_t)(sh.wild_key >> 32);  // padding id when nothing was seen
+    uint32_t row_wild_bits = (uint32_t)sh.wild_key;
 
     if (p.splits > 1) {
         const size_t slot = (size_t)row * p.splits + split;
