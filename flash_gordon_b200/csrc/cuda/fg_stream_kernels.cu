@@ -281,41 +281,20 @@ __device__ __noinline__ float resolve_overflow(CandidateBuffer<kCandCap> &cand, 
     return tau;
 }
 
-template <typename T>
-__global__ void __launch_bounds__(kThreads, FGK_STREAM_MIN_CTAS) stream_select_kernel(const StreamParams p) {
-    using L = Loader<T>;
-    extern __shared__ __align__(16) uint32_t dyn_smem[];
-    __shared__ StreamShared sh;
+// Flags build_history hands back.
+constexpr uint32_t kSeenAny = 1u;      // the row has penalties and history inside this split
+constexpr uint32_t kWithCounts = 2u;   // ... and a frequency penalty, so counts are kept
 
-    const uint32_t tid = threadIdx.x;
-    const uint32_t lane = tid & 31u, warp = tid >> 5;
-    const uint32_t split = blockIdx.x, row = blockIdx.y;
-    const SamplerConfig cfg = p.config_count > 1 ? p.configs[row] : p.config0;
-    const bool shard_mode = p.shard_k != 0;
-    const bool greedy = !shard_mode && cfg.temperature == 0.0f;
-    if (!shard_mode && !greedy && cfg.top_k == 0) return;  // rows without a top-k cut use the nucleus kernel
-    const uint32_t k = shard_mode ? p.shard_k : (greedy ? 1u : cfg.top_k);
-
-    const uint32_t lo = split * p.split_len;
-    const uint32_t n = min(p.split_len, p.vocab - lo);
-    const T *columns = static_cast<const T *>(p.logits) + (size_t)row * p.row_stride + lo;
-    const bool aligned = (reinterpret_cast<uintptr_t>(columns) & 15u) == 0;
-
-    // first tile is in flight while the history structure is built
-    uint4 raw[L::kVectors];
-    load_tile<T>(columns, 0, n, aligned, raw);
-
-    if (tid == 0) {
-        sh.cand.count = 0;
-        sh.cand.tau_score = __uint_as_float(0xff800000u);
-        sh.cand.tau_id = kPaddingId;
-        sh.bad_history = 0;
-        sh.wild_key = ~0ull;
-        sh.distinct = 0;
-    }
-    __syncthreads();
-
-    // ---- 1. history slice -> bitmap / running popcount / dense counts ----
+// Phase 1, once per CTA: the part of the row's token history that falls into
+// columns [lo, lo + n) becomes a bitmap of seen columns, an exclusive running
+// popcount per bitmap word and, per seen column, the offset
+// frequency * count + presence it will be charged (src/output.c:601-617 keeps a
+// vocabulary-wide count table per session instead).  Kept out of line so its
+// registers do not weigh on the streaming loop.
+__device__ __noinline__ uint32_t build_history(const StreamParams &p, StreamShared &sh,
+                                               uint32_t *dyn_smem, uint32_t row, uint32_t lo,
+                                               uint32_t n, const SamplerConfig &cfg) {
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     uint32_t *bitmap = dyn_smem;
     uint32_t *running = dyn_smem + p.bitmap_words;
     uint32_t *dense = dyn_smem + 2 * p.bitmap_words;
@@ -332,201 +311,147 @@ __global__ void __launch_bounds__(kThreads, FGK_STREAM_MIN_CTAS) stream_select_k
             if (tid == 0) sh.bad_history = kErrLimit;
         }
     }
-    const bool penalise_row = penalties_active(cfg) && p.bitmap_words != 0;
-    const bool seen_any = penalise_row && history_len != 0;
+    const bool seen_any = penalties_active(cfg) && p.bitmap_words != 0 && history_len != 0;
     const bool with_counts = seen_any && cfg.frequency_penalty != 0.0f && p.count_capacity != 0;
-    if (seen_any) {
-        for (uint32_t w = tid; w < words; w += kThreads) bitmap[w] = 0;
-        __syncthreads();
-        const uint32_t first_global = p.vocab_offset + lo;
-        for (uint32_t i = tid; i < history_len; i += kThreads) {
-            const uint32_t token = history[i];
-            if (token >= p.vocab_total) sh.bad_history = kErrFormat;
-            const uint32_t local = token - first_global;  // wraps for ids below the split
-            if (local < n) {
-                const uint32_t bit = 1u << (local & 31u);
-                if ((bitmap[local >> 5] & bit) == 0) atomicOr(&bitmap[local >> 5], bit);
-            }
-        }
-        __syncthreads();
-        if (with_counts) {
-            // exclusive running popcount per word: each thread owns a contiguous run
-            const uint32_t per = (words + kThreads - 1) / kThreads;
-            const uint32_t w0 = min(tid * per, words), w1 = min(w0 + per, words);
-            uint32_t mine = 0;
-            for (uint32_t w = w0; w < w1; w++) mine += __popc(bitmap[w]);
-            uint32_t incl = mine;
-#pragma unroll
-            for (int d = 1; d < 32; d <<= 1) {
-                const uint32_t up = __shfl_up_sync(kFullMask, incl, d);
-                if (lane >= (uint32_t)d) incl += up;
-            }
-            if (lane == 31) sh.scan[warp] = incl;
-            __syncthreads();
-            uint32_t before = incl - mine;
-            for (uint32_t q = 0; q < warp; q++) before += sh.scan[q];
-            if (tid == kThreads - 1) sh.distinct = before + mine;
-            for (uint32_t w = w0; w < w1; w++) {
-                running[w] = before;
-                before += __popc(bitmap[w]);
-            }
-            __syncthreads();
-            // the host sizes count_capacity >= min(history_max, split_len) >= distinct
-            const uint32_t distinct = min(sh.distinct, p.count_capacity);
-            for (uint32_t i = tid; i < distinct; i += kThreads) dense[i] = 0;
-            __syncthreads();
-            for (uint32_t i = tid; i < history_len; i += kThreads) {
-                const uint32_t local = history[i] - first_global;
-                if (local < n) {
-                    const uint32_t word = bitmap[local >> 5];
-                    const uint32_t at =
-                        running[local >> 5] + __popc(word & ((1u << (local & 31u)) - 1u));
-                    if (at < p.count_capacity) atomicAdd(&dense[at], 1u);
-                }
-            }
-            __syncthreads();
-            // counts -> the offset each seen id is charged, once per row instead of per use
-            for (uint32_t i = tid; i < distinct; i += kThreads)
-                dense[i] = __float_as_uint(
-                    penalty_offset(dense[i], cfg.presence_penalty, cfg.frequency_penalty));
+    if (!seen_any) return 0;
+
+    for (uint32_t w = tid; w < words; w += kThreads) bitmap[w] = 0;
+    __syncthreads();
+    const uint32_t first_global = p.vocab_offset + lo;
+    for (uint32_t i = tid; i < history_len; i += kThreads) {
+        const uint32_t token = history[i];
+        if (token >= p.vocab_total) sh.bad_history = kErrFormat;
+        const uint32_t local = token - first_global;  // wraps for ids below the split
+        if (local < n) {
+            const uint32_t bit = 1u << (local & 31u);
+            if ((bitmap[local >> 5] & bit) == 0) atomicOr(&bitmap[local >> 5], bit);
         }
     }
     __syncthreads();
-    const Repetition repetition = make_repetition(cfg.repetition_penalty);
-    // without a count array frequency is +-0 and the product does not depend on the count
-    const float flat_offset = penalty_offset(1u, cfg.presence_penalty, cfg.frequency_penalty);
+    if (!with_counts) return kSeenAny;
 
-    // ---- 2. stream the columns ----
-    // Tiles 1 .. full-1 of a 16-byte aligned row take the fast path: loads at constant
-    // offsets from one running pointer, one bitmap word per vector, one compare per
-    // vector.  Tile 0 (it sets the admission bound), a ragged last tile and unaligned
-    // rows look at every element.  The two kinds live in separate loops so the hot one
-    // stays small.
-    const uint32_t tiles = (n + kTile - 1) / kTile;
-    const uint32_t full_tiles = aligned ? n / kTile : 0;
-    const uint32_t id_base = p.vocab_offset + lo;
-    const uint4 *fast_source = reinterpret_cast<const uint4 *>(columns) + tid;
-    constexpr uint32_t kTileVectors = kTile / L::kPerVector;  // 128-bit vectors per tile
-    // this thread's vector u sits in bitmap word (tile_base / 32) + u * kWordsPerStep +
-    // word_lane, at bit bit_lane
-    constexpr uint32_t kWordsPerStep = kThreads * L::kPerVector / 32;
-    const uint32_t word_lane = tid * L::kPerVector / 32;
-    const uint32_t bit_lane = (tid * L::kPerVector) & 31u;
-    float tau = __uint_as_float(0xff800000u);
-
-    // one tile: penalise seen ids in registers, pick out what may still make the top k
-    auto process = [&](auto fast_tag, uint32_t t, float (&v)[kElemsPerThread]) {
-        constexpr bool fast = decltype(fast_tag)::value;
-        const uint32_t tile_base = t * kTile;
-        if (seen_any) {
-            const uint32_t *words_here = bitmap + (tile_base >> 5) + word_lane;
-            const uint32_t *running_here = running + (tile_base >> 5) + word_lane;
+    // exclusive running popcount per word: each thread owns a contiguous run of words
+    const uint32_t per = (words + kThreads - 1) / kThreads;
+    const uint32_t w0 = min(tid * per, words), w1 = min(w0 + per, words);
+    uint32_t mine = 0;
+    for (uint32_t w = w0; w < w1; w++) mine += __popc(bitmap[w]);
+    uint32_t incl = mine;
 #pragma unroll
-            for (int u = 0; u < L::kVectors; u++) {
-                if (!fast && column_of<T>(tile_base, u, 0) >= n) continue;
-                const uint32_t word = words_here[u * kWordsPerStep];
-                const uint32_t bits = (word >> bit_lane) & ((1u << L::kPerVector) - 1u);
-                if (bits == 0) continue;
-#pragma unroll
-                for (int j = 0; j < L::kPerVector; j++) {
-                    if (bits & (1u << j)) {
-                        float offset = flat_offset;
-                        if (with_counts) {
-                            const uint32_t below = (1u << (bit_lane + j)) - 1u;
-                            offset = __uint_as_float(
-                                dense[min(running_here[u * kWordsPerStep] + __popc(word & below),
-                                          p.count_capacity - 1)]);
-                        }
-                        v[u * L::kPerVector + j] =
-                            penalise_with_offset(v[u * L::kPerVector + j], offset, repetition);
-                    }
-                }
-            }
-        }
-        bool look = !fast;  // does any lane of this warp have to look at single elements?
-        if (fast) {
-            bool hot = false;  // a value above the bound (NaN never compares above)
-#pragma unroll
-            for (int u = 0; u < L::kVectors; u++) {
-                float top = v[u * L::kPerVector];
-#pragma unroll
-                for (int j = 1; j < L::kPerVector; j++) top = fmaxf(top, v[u * L::kPerVector + j]);
-                hot = hot || top > tau;
-            }
-            if (greedy) {  // the argmax order must see NaN and both infinities
-                uint32_t widest = 0;
-#pragma unroll
-                for (int e = 0; e < kElemsPerThread; e++)
-                    widest = max(widest, __float_as_uint(v[e]) & 0x7fffffffu);
-                hot = hot || widest >= 0x7f800000u;
-            }
-            look = __any_sync(kFullMask, hot);
-        } else if (t == 0) {
-            // A valid lower bound for the k-th best: the k-th largest of the per-thread
-            // maxima (k distinct elements are at least that large).
-            float best = __uint_as_float(0xff800000u);
-            uint32_t have = 0;
-#pragma unroll
-            for (int e = 0; e < kElemsPerThread; e++) {
-                const bool exists = column_of<T>(tile_base, e / L::kPerVector, e % L::kPerVector) < n;
-                if (exists && !is_nonfinite(v[e])) {
-                    best = fmaxf(best, v[e]);
-                    have = 1;
-                }
-            }
-            tau = key_to_float(block_kth_key(have ? float_key(best) : 0u, k));
-        }
-        uint32_t pending = 0;
-        bool trouble = false;
-        if (look) {  // rare on the fast path: the values travel by value, off the hot registers
-            Values16 x;
-#pragma unroll
-            for (int e = 0; e < kElemsPerThread; e++) x.v[e] = v[e];
-            pending = tile_slow_path<T>(sh.cand, x, tile_base, n, tau, t == 0, greedy, id_base,
-                                        &sh.wild_key, &trouble);
-        }
-        // one barrier per tile: does anybody need the list cut back?
-        if (__syncthreads_or(trouble)) {
-            Values16 x;
-#pragma unroll
-            for (int e = 0; e < kElemsPerThread; e++) x.v[e] = v[e];
-            tau = resolve_overflow<T>(sh.cand, x, pending, tile_base, k, id_base);
-        }
-    };
-
-    {
-        float v[kElemsPerThread];
-#pragma unroll
-        for (int u = 0; u < L::kVectors; u++) L::unpack(raw[u], &v[u * L::kPerVector]);
-        if (1 < full_tiles) {
-#pragma unroll
-            for (int u = 0; u < L::kVectors; u++)
-                raw[u] = load_stream_128(fast_source + kTileVectors + u * kThreads);
-        }
-        process(std::false_type{}, 0, v);
+    for (int d = 1; d < 32; d <<= 1) {
+        const uint32_t up = __shfl_up_sync(kFullMask, incl, d);
+        if (lane >= (uint32_t)d) incl += up;
     }
-    for (uint32_t t = 1; t < full_tiles; t++) {
-        float v[kElemsPerThread];
-#pragma unroll
-        for (int u = 0; u < L::kVectors; u++) L::unpack(raw[u], &v[u * L::kPerVector]);
-        if (t + 1 < full_tiles) {
-            const uint4 *next = fast_source + (size_t)(t + 1) * kTileVectors;
-#pragma unroll
-            for (int u = 0; u < L::kVectors; u++) raw[u] = load_stream_128(next + u * kThreads);
+    if (lane == 31) sh.scan[warp] = incl;
+    __syncthreads();
+    uint32_t before = incl - mine;
+    for (uint32_t q = 0; q < warp; q++) before += sh.scan[q];
+    if (tid == kThreads - 1) sh.distinct = before + mine;
+    for (uint32_t w = w0; w < w1; w++) {
+        running[w] = before;
+        before += __popc(bitmap[w]);
+    }
+    __syncthreads();
+    // the host sizes count_capacity >= min(history_max, split_len) >= distinct
+    const uint32_t distinct = min(sh.distinct, p.count_capacity);
+    for (uint32_t i = tid; i < distinct; i += kThreads) dense[i] = 0;
+    __syncthreads();
+    for (uint32_t i = tid; i < history_len; i += kThreads) {
+        const uint32_t local = history[i] - first_global;
+        if (local < n) {
+            const uint32_t word = bitmap[local >> 5];
+            const uint32_t at = running[local >> 5] + __popc(word & ((1u << (local & 31u)) - 1u));
+            if (at < p.count_capacity) atomicAdd(&dense[at], 1u);
         }
-        process(std::true_type{}, t, v);
     }
-    // what the fast loop did not cover: the ragged end of an aligned row, or every
-    // further tile of an unaligned one (loaded without prefetch)
-    for (uint32_t t = full_tiles > 1 ? full_tiles : 1; t < tiles; t++) {
-        load_tile<T>(columns, t * kTile, n, aligned, raw);
-        float v[kElemsPerThread];
-#pragma unroll
-        for (int u = 0; u < L::kVectors; u++) L::unpack(raw[u], &v[u * L::kPerVector]);
-        process(std::false_type{}, t, v);
-    }
+    __syncthreads();
+    // counts -> the offset each seen id is charged, once per row instead of per use
+    for (uint32_t i = tid; i < distinct; i += kThreads)
+        dense[i] = __float_as_uint(
+            penalty_offset(dense[i], cfg.presence_penalty, cfg.frequency_penalty));
+    __syncthreads();
+    return kSeenAny | kWithCounts;
+}
 
-    // ---- 3. this split's k best ----
+// What the tile routines need to know about the row; a few registers.
+struct RowState {
+    uint32_t n;          // columns in this split
+    uint32_t id_base;    // global id of column 0
+    uint32_t k;
+    uint32_t flags;      // kSeenAny | kWithCounts
+    bool greedy;
+    bool aligned;
+    float flat_offset;   // offset when counts are not kept (frequency is +-0)
+    Repetition repetition;
+};
+
+// One tile looked at element by element: tile 0 (it sets the admission bound), the
+// ragged last tile, and every tile of a row that is not 16-byte aligned.  Loads its
+// own data; out of line, so its sixteen values may live on the stack.  Every thread
+// of the CTA calls it.  Returns the new bound.
+template <typename T>
+__device__ __noinline__ float careful_tile(const StreamParams &p, StreamShared &sh,
+                                           uint32_t *dyn_smem, const T *columns, uint32_t t,
+                                           const RowState &row, float tau) {
+    using L = Loader<T>;
+    const uint32_t tile_base = t * kTile;
+    uint4 raw[L::kVectors];
+    load_tile<T>(columns, tile_base, row.n, row.aligned, raw);
+    Values16 x;
+#pragma unroll
+    for (int u = 0; u < L::kVectors; u++) L::unpack(raw[u], &x.v[u * L::kPerVector]);
+    if (row.flags & kSeenAny) {
+        const uint32_t *bitmap = dyn_smem;
+        const uint32_t *running = dyn_smem + p.bitmap_words;
+        const uint32_t *dense = dyn_smem + 2 * p.bitmap_words;
+#pragma unroll
+        for (int e = 0; e < kElemsPerThread; e++) {
+            const uint32_t column = column_of<T>(tile_base, e / L::kPerVector, e % L::kPerVector);
+            if (column >= row.n) continue;
+            const uint32_t word = bitmap[column >> 5];
+            if (((word >> (column & 31u)) & 1u) == 0) continue;
+            float offset = row.flat_offset;
+            if (row.flags & kWithCounts) {
+                const uint32_t at =
+                    running[column >> 5] + __popc(word & ((1u << (column & 31u)) - 1u));
+                offset = __uint_as_float(dense[min(at, p.count_capacity - 1)]);
+            }
+            x.v[e] = penalise_with_offset(x.v[e], offset, row.repetition);
+        }
+    }
+    if (t == 0) {
+        // A valid lower bound for the k-th best: the k-th largest of the per-thread
+        // maxima (k distinct elements are at least that large).
+        float best = __uint_as_float(0xff800000u);
+        uint32_t have = 0;
+#pragma unroll
+        for (int e = 0; e < kElemsPerThread; e++) {
+            const bool exists =
+                column_of<T>(tile_base, e / L::kPerVector, e % L::kPerVector) < row.n;
+            if (exists && !is_nonfinite(x.v[e])) {
+                best = fmaxf(best, x.v[e]);
+                have = 1;
+            }
+        }
+        tau = key_to_float(block_kth_key(have ? float_key(best) : 0u, row.k));
+    }
+    uint32_t pending = classify<T>(x, tile_base, row.n, tau, t == 0, row.greedy, row.id_base,
+                                   &sh.wild_key);
+    bool trouble = false;
+    if (__any_sync(kFullMask, pending != 0))
+        trouble = append_pending<T>(sh.cand, x, pending, tile_base, row.id_base);
+    if (__syncthreads_or(trouble))
+        tau = resolve_overflow<T>(sh.cand, x, pending, tile_base, row.k, row.id_base);
+    return tau;
+}
+
+// Phases 3 and 4, once per CTA: cut the list to this split's k best; with several
+// splits per row hand them to the row's last-arriving CTA, which merges all splits;
+// then write the row's result (shard candidates, greedy winner, or the select step
+// of src/sampler.c:80-122).  Every thread of the CTA calls it.
+__device__ __noinline__ void finish_split(const StreamParams &p, StreamShared &sh, uint32_t row,
+                                          uint32_t split, uint32_t k, bool greedy,
+                                          bool shard_mode, const SamplerConfig &cfg) {
+    const uint32_t tid = threadIdx.x;
     __syncthreads();
     uint32_t held = min(sh.cand.count, (uint32_t)kCandCap);
     __syncthreads();
@@ -534,8 +459,8 @@ __global__ void __launch_bounds__(kThreads, FGK_STREAM_MIN_CTAS) stream_select_k
     __syncthreads();
 
     uint32_t bad_history = sh.bad_history;
-    uint32_t row_wild_id = (uint32_t)(sh.wild_key >> 32);  // padding id when nothing was seen
-    uint32_t row_wild_bits = (uint32_t)sh.wild_key;
+    uint32_t wild_id = (uint32_t)(sh.wild_key >> 32);  // the padding id when nothing was seen
+    uint32_t wild_bits = (uint32_t)sh.wild_key;
 
     if (p.splits > 1) {
         const size_t slot = (size_t)row * p.splits + split;
@@ -546,8 +471,8 @@ __global__ void __launch_bounds__(kThreads, FGK_STREAM_MIN_CTAS) stream_select_k
         if (tid == 0) {
             PartMeta meta;
             meta.count = held;
-            meta.wild_id = row_wild_id;
-            meta.wild_bits = row_wild_bits;
+            meta.wild_id = wild_id;
+            meta.wild_bits = wild_bits;
             meta.bad_history = bad_history;
             p.part_meta[slot] = meta;
         }
@@ -564,25 +489,21 @@ __global__ void __launch_bounds__(kThreads, FGK_STREAM_MIN_CTAS) stream_select_k
         // gather every split's survivors into the candidate buffer
         uint32_t total = 0;
         bad_history = 0;
-        row_wild_id = kPaddingId;
-        row_wild_bits = 0;
+        wild_id = kPaddingId;
+        wild_bits = 0;
         for (uint32_t s = 0; s < p.splits; s++) {
             const size_t from = (size_t)row * p.splits + s;
             const uint4 packed = __ldcg(reinterpret_cast<const uint4 *>(&p.part_meta[from]));
-            PartMeta meta;
-            meta.count = packed.x;
-            meta.wild_id = packed.y;
-            meta.wild_bits = packed.z;
-            meta.bad_history = packed.w;
-            if (tid < meta.count) {
+            const uint32_t count = packed.x;
+            if (tid < count) {
                 sh.cand.score[total + tid] = __ldcg(&p.part_scores[from * kMaxK + tid]);
                 sh.cand.id[total + tid] = __ldcg(&p.part_ids[from * kMaxK + tid]);
             }
-            total += meta.count;
-            if (meta.bad_history) bad_history = meta.bad_history;
-            if (meta.wild_id < row_wild_id) {
-                row_wild_id = meta.wild_id;
-                row_wild_bits = meta.wild_bits;
+            total += count;
+            if (packed.w) bad_history = packed.w;
+            if (packed.y < wild_id) {
+                wild_id = packed.y;
+                wild_bits = packed.z;
             }
         }
         __syncthreads();
@@ -591,7 +512,6 @@ __global__ void __launch_bounds__(kThreads, FGK_STREAM_MIN_CTAS) stream_select_k
         held = compact_topk<kThreads, kCandCap>(sh.cand, total, k);
     }
 
-    // ---- 4. row result ----
     if (shard_mode) {
         sort_candidates(sh.cand, sh.fin, held);
         if (tid < k) {
@@ -618,12 +538,12 @@ __global__ void __launch_bounds__(kThreads, FGK_STREAM_MIN_CTAS) stream_select_k
         if (tid == 0) {
             uint32_t status = kOk, token;
             float logit;
-            if (row_wild_id != kPaddingId) {
+            if (wild_id != kPaddingId) {
                 // a NaN/Inf beats every finite logit in the argmax order and is then
                 // rejected: src/output.c:593 (no penalties) / 737-739 (penalised)
                 status = penalties_active(cfg) ? kErrFormat : kErrMismatch;
-                token = row_wild_id;
-                logit = __uint_as_float(row_wild_bits);
+                token = wild_id;
+                logit = __uint_as_float(wild_bits);
             } else if (held == 0) {
                 status = kErrMismatch;
                 token = kPaddingId;
@@ -643,7 +563,145 @@ __global__ void __launch_bounds__(kThreads, FGK_STREAM_MIN_CTAS) stream_select_k
         return;
     }
     sort_candidates(sh.cand, sh.fin, held);
-    if (warp == 0) finish_select(sh.fin, held, cfg, p.uniforms[row], row, p.out);
+    if (tid < 32) finish_select(sh.fin, held, cfg, p.uniforms[row], row, p.out);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads, FGK_STREAM_MIN_CTAS)
+stream_select_kernel(const __grid_constant__ StreamParams p) {
+    using L = Loader<T>;
+    extern __shared__ __align__(16) uint32_t dyn_smem[];
+    __shared__ StreamShared sh;
+
+    const uint32_t tid = threadIdx.x;
+    const uint32_t split = blockIdx.x, row = blockIdx.y;
+    const SamplerConfig cfg = p.config_count > 1 ? p.configs[row] : p.config0;
+    const bool shard_mode = p.shard_k != 0;
+    const bool greedy = !shard_mode && cfg.temperature == 0.0f;
+    if (!shard_mode && !greedy && cfg.top_k == 0) return;  // rows without a top-k cut use the nucleus kernel
+
+    const uint32_t lo = split * p.split_len;
+    const T *columns = static_cast<const T *>(p.logits) + (size_t)row * p.row_stride + lo;
+    RowState state;
+    state.n = min(p.split_len, p.vocab - lo);
+    state.id_base = p.vocab_offset + lo;
+    state.k = shard_mode ? p.shard_k : (greedy ? 1u : cfg.top_k);
+    state.greedy = greedy;
+    state.aligned = (reinterpret_cast<uintptr_t>(columns) & 15u) == 0;
+    // without a count array frequency is +-0 and the product does not depend on the count
+    state.flat_offset = penalty_offset(1u, cfg.presence_penalty, cfg.frequency_penalty);
+    state.repetition = make_repetition(cfg.repetition_penalty);
+
+    if (tid == 0) {
+        sh.cand.count = 0;
+        sh.cand.tau_score = __uint_as_float(0xff800000u);
+        sh.cand.tau_id = kPaddingId;
+        sh.bad_history = 0;
+        sh.wild_key = ~0ull;
+        sh.distinct = 0;
+    }
+    __syncthreads();
+
+    // ---- 1. history slice -> bitmap / running popcount / offsets ----
+    state.flags = build_history(p, sh, dyn_smem, row, lo, state.n, cfg);
+
+    // ---- 2. stream the columns ----
+    // Tiles 1 .. full-1 of a 16-byte aligned row take the fast loop below: 128-bit
+    // loads at constant offsets from one running pointer (next tile in flight while
+    // this one is examined), one bitmap word per vector, one compare per vector.
+    // Everything else goes through careful_tile.
+    const uint32_t n = state.n;
+    const uint32_t tiles = (n + kTile - 1) / kTile;
+    const uint32_t full_tiles = state.aligned ? n / kTile : 0;
+    float tau = careful_tile<T>(p, sh, dyn_smem, columns, 0, state, __uint_as_float(0xff800000u));
+
+    if (full_tiles > 1) {
+        constexpr uint32_t kTileVectors = kTile / L::kPerVector;  // 128-bit vectors per tile
+        // this thread's vector u sits in bitmap word (tile_base / 32) + u * kWordsPerStep
+        // + word_lane, at bit bit_lane
+        constexpr uint32_t kWordsPerStep = kThreads * L::kPerVector / 32;
+        const uint32_t word_lane = tid * L::kPerVector / 32;
+        const uint32_t bit_lane = (tid * L::kPerVector) & 31u;
+        const bool seen_any = state.flags & kSeenAny, with_counts = state.flags & kWithCounts;
+        const uint32_t *bitmap = dyn_smem + word_lane;
+        const uint32_t *running = dyn_smem + p.bitmap_words + word_lane;
+        const uint32_t *dense = dyn_smem + 2 * p.bitmap_words;
+        const uint4 *source = reinterpret_cast<const uint4 *>(columns) + tid + kTileVectors;
+        uint4 raw[L::kVectors];
+#pragma unroll
+        for (int u = 0; u < L::kVectors; u++) raw[u] = load_stream_128(source + u * kThreads);
+        for (uint32_t t = 1; t < full_tiles; t++) {
+            float v[kElemsPerThread];
+#pragma unroll
+            for (int u = 0; u < L::kVectors; u++) L::unpack(raw[u], &v[u * L::kPerVector]);
+            source += kTileVectors;
+            if (t + 1 < full_tiles) {
+#pragma unroll
+                for (int u = 0; u < L::kVectors; u++) raw[u] = load_stream_128(source + u * kThreads);
+            }
+            const uint32_t tile_word = t * (kTile / 32);
+            if (seen_any) {
+#pragma unroll
+                for (int u = 0; u < L::kVectors; u++) {
+                    const uint32_t word = bitmap[tile_word + u * kWordsPerStep];
+                    const uint32_t bits = (word >> bit_lane) & ((1u << L::kPerVector) - 1u);
+                    if (bits == 0) continue;
+#pragma unroll
+                    for (int j = 0; j < L::kPerVector; j++) {
+                        if (bits & (1u << j)) {
+                            float offset = state.flat_offset;
+                            if (with_counts) {
+                                const uint32_t below = (1u << (bit_lane + j)) - 1u;
+                                offset = __uint_as_float(
+                                    dense[min(running[tile_word + u * kWordsPerStep] +
+                                                  __popc(word & below),
+                                              p.count_capacity - 1)]);
+                            }
+                            v[u * L::kPerVector + j] = penalise_with_offset(
+                                v[u * L::kPerVector + j], offset, state.repetition);
+                        }
+                    }
+                }
+            }
+            bool hot = false;  // a value above the bound (NaN never compares above)
+#pragma unroll
+            for (int u = 0; u < L::kVectors; u++) {
+                float top = v[u * L::kPerVector];
+#pragma unroll
+                for (int j = 1; j < L::kPerVector; j++) top = fmaxf(top, v[u * L::kPerVector + j]);
+                hot = hot || top > tau;
+            }
+            if (greedy) {  // the argmax order must see NaN and both infinities
+                uint32_t widest = 0;
+#pragma unroll
+                for (int e = 0; e < kElemsPerThread; e++)
+                    widest = max(widest, __float_as_uint(v[e]) & 0x7fffffffu);
+                hot = hot || widest >= 0x7f800000u;
+            }
+            uint32_t pending = 0;
+            bool trouble = false;
+            if (__any_sync(kFullMask, hot)) {  // rare: the values travel by value
+                Values16 x;
+#pragma unroll
+                for (int e = 0; e < kElemsPerThread; e++) x.v[e] = v[e];
+                pending = tile_slow_path<T>(sh.cand, x, t * kTile, n, tau, false, greedy,
+                                            state.id_base, &sh.wild_key, &trouble);
+            }
+            // one barrier per tile: does anybody need the list cut back?
+            if (__syncthreads_or(trouble)) {
+                Values16 x;
+#pragma unroll
+                for (int e = 0; e < kElemsPerThread; e++) x.v[e] = v[e];
+                tau = resolve_overflow<T>(sh.cand, x, pending, t * kTile, state.k, state.id_base);
+            }
+        }
+    }
+    // the ragged end of an aligned row, or every further tile of an unaligned one
+    for (uint32_t t = full_tiles > 1 ? full_tiles : 1; t < tiles; t++)
+        tau = careful_tile<T>(p, sh, dyn_smem, columns, t, state, tau);
+
+    // ---- 3./4. this split's k best, the row's result ----
+    finish_split(p, sh, row, split, state.k, greedy, shard_mode, cfg);
 }
 
 // ---------------------------------------------------------------- merge kernel
