@@ -22,14 +22,14 @@
 namespace fgk {
 
 #ifndef FGK_STREAM_MIN_CTAS
-#define FGK_STREAM_MIN_CTAS 3
+#define FGK_STREAM_MIN_CTAS 4
 #endif
 
 constexpr int kThreads = 256;
 constexpr int kElemsPerThread = 16;
 constexpr int kTile = kThreads * kElemsPerThread;  // 4096 logits per CTA iteration
-constexpr int kCandCap = 1024;
-constexpr uint32_t kMaxSplits = kCandCap / kMaxK;  // the merge fits one candidate buffer
+constexpr int kCandCap = 2048;
+constexpr uint32_t kMaxSplits = 16;  // the merge of 16 x 64 survivors fits one candidate buffer
 
 struct alignas(16) PartMeta {
     uint32_t count;         // finite candidates this split kept (<= k)
@@ -73,6 +73,7 @@ struct StreamShared {
     uint32_t wild_id;
     uint32_t wild_bits;
     uint32_t is_last;
+    uint32_t overflow;            // a value found no slot in the candidate list
 };
 
 template <typename T>
@@ -293,7 +294,7 @@ constexpr uint32_t kWithCounts = 2u;   // ... and a frequency penalty, so counts
 // registers do not weigh on the streaming loop.
 __device__ __noinline__ uint32_t build_history(const StreamParams &p, StreamShared &sh,
                                                uint32_t *dyn_smem, uint32_t row, uint32_t lo,
-                                               uint32_t n, const SamplerConfig &cfg) {
+                                               uint32_t n, const SamplerConfig cfg) {
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     uint32_t *bitmap = dyn_smem;
     uint32_t *running = dyn_smem + p.bitmap_words;
@@ -384,6 +385,117 @@ struct RowState {
     Repetition repetition;
 };
 
+// Cuts the candidate list back to its k best (which lifts the admission bound) and
+// returns the new bound.  Every thread of the CTA calls it.
+__device__ __noinline__ float cut_list(StreamShared &sh, uint32_t k) {
+    __syncthreads();
+    const uint32_t held = min(sh.cand.count, (uint32_t)kCandCap);
+    __syncthreads();  // everyone has read count before the cut rewrites it
+    compact_topk<kThreads, kCandCap>(sh.cand, held, k);
+    return sh.cand.tau_score;
+}
+
+// Tile -> sixteen penalised values per thread, element by element (any alignment,
+// any raggedness).  Columns past the end come back as -inf.
+template <typename T>
+__device__ __forceinline__ void load_penalised(const StreamParams &p, const uint32_t *dyn_smem,
+                                               const T *columns, uint32_t tile_base,
+                                               const RowState &row, Values16 &x) {
+    using L = Loader<T>;
+    uint4 raw[L::kVectors];
+    load_tile<T>(columns, tile_base, row.n, row.aligned, raw);
+#pragma unroll
+    for (int u = 0; u < L::kVectors; u++) L::unpack(raw[u], &x.v[u * L::kPerVector]);
+    if ((row.flags & kSeenAny) == 0) return;
+    const uint32_t *bitmap = dyn_smem;
+    const uint32_t *running = dyn_smem + p.bitmap_words;
+    const uint32_t *dense = dyn_smem + 2 * p.bitmap_words;
+#pragma unroll
+    for (int e = 0; e < kElemsPerThread; e++) {
+        const uint32_t column = column_of<T>(tile_base, e / L::kPerVector, e % L::kPerVector);
+        if (column >= row.n) continue;
+        const uint32_t word = bitmap[column >> 5];
+        if (((word >> (column & 31u)) & 1u) == 0) continue;
+        float offset = row.flat_offset;
+        if (row.flags & kWithCounts) {
+            const uint32_t at = running[column >> 5] + __popc(word & ((1u << (column & 31u)) - 1u));
+            offset = __uint_as_float(dense[min(at, p.count_capacity - 1)]);
+        }
+        x.v[e] = penalise_with_offset(x.v[e], offset, row.repetition);
+    }
+}
+
+// A tile of the fast loop pushed more values than the list could take (sorted or
+// constant rows do that).  Take back what the tile stored, then feed the tile again
+// from memory a quarter at a time with a cut before each quarter, so the list can
+// never overflow: k + kThreads * 4 <= kCandCap.  Ties with the bound are resolved on
+// the id, as the bound may now come from this very tile.  Every thread of the CTA
+// calls it.  Returns the new bound.
+template <typename T>
+__device__ __noinline__ float redo_tile(const StreamParams &p, StreamShared &sh,
+                                        const uint32_t *dyn_smem, const T *columns, uint32_t t,
+                                        const RowState row) {
+    using L = Loader<T>;
+    static_assert(kMaxK + kThreads * 4 <= kCandCap, "a quarter tile fits behind the k survivors");
+    constexpr int PER = kCandCap / kThreads;
+    const uint32_t tid = threadIdx.x;
+    const uint32_t tile_base = t * kTile;
+    const uint32_t first_id = row.id_base + tile_base;
+
+    __syncthreads();
+    const uint32_t held = min(sh.cand.count, (uint32_t)kCandCap);
+    float score[PER];
+    uint32_t id[PER];
+#pragma unroll
+    for (int j = 0; j < PER; j++) {
+        const uint32_t at = j * kThreads + tid;
+        id[j] = kPaddingId;
+        score[j] = 0.0f;
+        if (at < held) {
+            score[j] = sh.cand.score[at];
+            id[j] = sh.cand.id[at];
+        }
+    }
+    __syncthreads();
+    if (tid == 0) {
+        sh.cand.count = 0;
+        sh.overflow = 0;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < PER; j++) {
+        if (id[j] != kPaddingId && id[j] - first_id >= (uint32_t)kTile) {  // not from this tile
+            const uint32_t slot = atomicAdd(&sh.cand.count, 1u);
+            sh.cand.score[slot] = score[j];
+            sh.cand.id[slot] = id[j];
+        }
+    }
+    Values16 x;
+    load_penalised<T>(p, dyn_smem, columns, tile_base, row, x);
+#pragma unroll
+    for (int quarter = 0; quarter < 4; quarter++) {
+        const float tau = cut_list(sh, row.k);
+        const uint32_t tau_id = sh.cand.tau_id;
+#pragma unroll
+        for (int e = quarter * 4; e < quarter * 4 + 4; e++) {
+            const uint32_t column = column_of<T>(tile_base, e / L::kPerVector, e % L::kPerVector);
+            if (column >= row.n) continue;
+            if (is_nonfinite(x.v[e])) {
+                if (row.greedy)
+                    atomicMin(&sh.wild_key, ((unsigned long long)(row.id_base + column) << 32) |
+                                                __float_as_uint(x.v[e]));
+                continue;
+            }
+            if (precedes(x.v[e], row.id_base + column, tau, tau_id)) {
+                const uint32_t slot = atomicAdd(&sh.cand.count, 1u);
+                sh.cand.score[slot] = x.v[e];
+                sh.cand.id[slot] = row.id_base + column;
+            }
+        }
+    }
+    return cut_list(sh, row.k);
+}
+
 // One tile looked at element by element: tile 0 (it sets the admission bound), the
 // ragged last tile, and every tile of a row that is not 16-byte aligned.  Loads its
 // own data; out of line, so its sixteen values may live on the stack.  Every thread
@@ -391,33 +503,11 @@ struct RowState {
 template <typename T>
 __device__ __noinline__ float careful_tile(const StreamParams &p, StreamShared &sh,
                                            uint32_t *dyn_smem, const T *columns, uint32_t t,
-                                           const RowState &row, float tau) {
+                                           const RowState row, float tau) {
     using L = Loader<T>;
     const uint32_t tile_base = t * kTile;
-    uint4 raw[L::kVectors];
-    load_tile<T>(columns, tile_base, row.n, row.aligned, raw);
     Values16 x;
-#pragma unroll
-    for (int u = 0; u < L::kVectors; u++) L::unpack(raw[u], &x.v[u * L::kPerVector]);
-    if (row.flags & kSeenAny) {
-        const uint32_t *bitmap = dyn_smem;
-        const uint32_t *running = dyn_smem + p.bitmap_words;
-        const uint32_t *dense = dyn_smem + 2 * p.bitmap_words;
-#pragma unroll
-        for (int e = 0; e < kElemsPerThread; e++) {
-            const uint32_t column = column_of<T>(tile_base, e / L::kPerVector, e % L::kPerVector);
-            if (column >= row.n) continue;
-            const uint32_t word = bitmap[column >> 5];
-            if (((word >> (column & 31u)) & 1u) == 0) continue;
-            float offset = row.flat_offset;
-            if (row.flags & kWithCounts) {
-                const uint32_t at =
-                    running[column >> 5] + __popc(word & ((1u << (column & 31u)) - 1u));
-                offset = __uint_as_float(dense[min(at, p.count_capacity - 1)]);
-            }
-            x.v[e] = penalise_with_offset(x.v[e], offset, row.repetition);
-        }
-    }
+    load_penalised<T>(p, dyn_smem, columns, tile_base, row, x);
     if (t == 0) {
         // A valid lower bound for the k-th best: the k-th largest of the per-thread
         // maxima (k distinct elements are at least that large).
@@ -450,7 +540,7 @@ __device__ __noinline__ float careful_tile(const StreamParams &p, StreamShared &
 // of src/sampler.c:80-122).  Every thread of the CTA calls it.
 __device__ __noinline__ void finish_split(const StreamParams &p, StreamShared &sh, uint32_t row,
                                           uint32_t split, uint32_t k, bool greedy,
-                                          bool shard_mode, const SamplerConfig &cfg) {
+                                          bool shard_mode, const SamplerConfig cfg) {
     const uint32_t tid = threadIdx.x;
     __syncthreads();
     uint32_t held = min(sh.cand.count, (uint32_t)kCandCap);
@@ -566,6 +656,117 @@ __device__ __noinline__ void finish_split(const StreamParams &p, StreamShared &s
     if (tid < 32) finish_select(sh.fin, held, cfg, p.uniforms[row], row, p.out);
 }
 
+// The hot loop: tiles 1 .. full_tiles-1 of a 16-byte aligned row.  128-bit loads at
+// constant offsets from one running pointer (the next tile is in flight while this one
+// is examined), one bitmap word and one compare per vector; single elements are only
+// looked at by lanes that hold a value above the admission bound.  A function of its
+// own, and one that calls nothing: whatever is live across a call inside a loop gets
+// saved and restored on every trip.  So when the candidate list needs attention (a cut,
+// or a tile that overflowed it) the loop stops and says so; the caller deals with it
+// and comes back.  Returns the last tile it examined, with kNeedsAttention set if it
+// stopped early.
+constexpr uint32_t kNeedsAttention = 0x80000000u;
+
+template <typename T>
+__device__ __noinline__ uint32_t fast_tiles(const StreamParams &p, StreamShared &sh,
+                                            const uint32_t *dyn_smem, const T *columns,
+                                            uint32_t first_tile, uint32_t full_tiles,
+                                            const RowState state, const float tau) {
+    using L = Loader<T>;
+    const uint32_t tid = threadIdx.x;
+    const bool greedy = state.greedy;
+    const uint32_t n = state.n;
+    (void)n;
+    constexpr uint32_t kTileVectors = kTile / L::kPerVector;  // 128-bit vectors per tile
+    // this thread's vector u sits in bitmap word (tile_base / 32) + u * kWordsPerStep
+    // + word_lane, at bit bit_lane
+    constexpr uint32_t kWordsPerStep = kThreads * L::kPerVector / 32;
+    const uint32_t word_lane = tid * L::kPerVector / 32;
+    const uint32_t bit_lane = (tid * L::kPerVector) & 31u;
+    const bool seen_any = state.flags & kSeenAny, with_counts = state.flags & kWithCounts;
+    const uint32_t *bitmap = dyn_smem + word_lane;
+    const uint32_t *running = dyn_smem + p.bitmap_words + word_lane;
+    const uint32_t *dense = dyn_smem + 2 * p.bitmap_words;
+    // cut the list once it holds a few multiples of k: the bound stays close to the
+    // true k-th best and fewer values reach the list at all
+    const uint32_t cut_at = 4 * state.k + 64;
+    const uint4 *source =
+        reinterpret_cast<const uint4 *>(columns) + tid + (size_t)first_tile * kTileVectors;
+    uint4 raw[L::kVectors];
+#pragma unroll
+    for (int u = 0; u < L::kVectors; u++) raw[u] = load_stream_128(source + u * kThreads);
+    for (uint32_t t = first_tile; t < full_tiles; t++) {
+        source += kTileVectors;
+        const bool more = t + 1 < full_tiles;
+        const uint32_t tile_word = t * (kTile / 32);
+        bool want_cut = false;
+        // one 128-bit vector at a time: its register slot is refilled with the next
+        // tile's data as soon as it has been unpacked
+#pragma unroll
+        for (int u = 0; u < L::kVectors; u++) {
+            float v[L::kPerVector];
+            L::unpack(raw[u], v);
+            if (more) raw[u] = load_stream_128(source + u * kThreads);
+            if (seen_any) {
+                const uint32_t word = bitmap[tile_word + u * kWordsPerStep];
+                const uint32_t bits = (word >> bit_lane) & ((1u << L::kPerVector) - 1u);
+                if (bits != 0) {
+#pragma unroll
+                    for (int j = 0; j < L::kPerVector; j++) {
+                        if (bits & (1u << j)) {
+                            float offset = state.flat_offset;
+                            if (with_counts) {
+                                const uint32_t below = (1u << (bit_lane + j)) - 1u;
+                                offset = __uint_as_float(
+                                    dense[min(running[tile_word + u * kWordsPerStep] +
+                                                  __popc(word & below),
+                                              p.count_capacity - 1)]);
+                            }
+                            v[j] = penalise_with_offset(v[j], offset, state.repetition);
+                        }
+                    }
+                }
+            }
+            float top = v[0];  // NaN never compares above the bound
+#pragma unroll
+            for (int j = 1; j < L::kPerVector; j++) top = fmaxf(top, v[j]);
+            bool hot = top > tau;
+            if (greedy) {  // the argmax order must see NaN and both infinities
+                uint32_t widest = 0;
+#pragma unroll
+                for (int j = 0; j < L::kPerVector; j++)
+                    widest = max(widest, __float_as_uint(v[j]) & 0x7fffffffu);
+                hot = hot || widest >= 0x7f800000u;
+            }
+            if (hot) {
+                // Few lanes get here once the bound has settled.  Later columns carry
+                // larger ids than whatever produced the bound, so a tie with it loses.
+                const uint32_t first_id = state.id_base + column_of<T>(t * kTile, u, 0);
+#pragma unroll
+                for (int j = 0; j < L::kPerVector; j++) {
+                    if (is_nonfinite(v[j])) {
+                        if (greedy)
+                            atomicMin(&sh.wild_key, ((unsigned long long)(first_id + j) << 32) |
+                                                        __float_as_uint(v[j]));
+                    } else if (v[j] > tau) {
+                        const uint32_t slot = atomicAdd(&sh.cand.count, 1u);
+                        if (slot < (uint32_t)kCandCap) {
+                            sh.cand.score[slot] = v[j];
+                            sh.cand.id[slot] = first_id + j;
+                        } else {
+                            sh.overflow = 1;
+                        }
+                        want_cut = want_cut || slot >= cut_at;
+                    }
+                }
+            }
+        }
+        // one barrier per tile: does the list need attention?
+        if (__syncthreads_or(want_cut)) return t | kNeedsAttention;
+    }
+    return full_tiles - 1;
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kThreads, FGK_STREAM_MIN_CTAS)
 stream_select_kernel(const __grid_constant__ StreamParams p) {
@@ -599,6 +800,7 @@ stream_select_kernel(const __grid_constant__ StreamParams p) {
         sh.bad_history = 0;
         sh.wild_key = ~0ull;
         sh.distinct = 0;
+        sh.overflow = 0;
     }
     __syncthreads();
 
@@ -615,85 +817,14 @@ stream_select_kernel(const __grid_constant__ StreamParams p) {
     const uint32_t full_tiles = state.aligned ? n / kTile : 0;
     float tau = careful_tile<T>(p, sh, dyn_smem, columns, 0, state, __uint_as_float(0xff800000u));
 
-    if (full_tiles > 1) {
-        constexpr uint32_t kTileVectors = kTile / L::kPerVector;  // 128-bit vectors per tile
-        // this thread's vector u sits in bitmap word (tile_base / 32) + u * kWordsPerStep
-        // + word_lane, at bit bit_lane
-        constexpr uint32_t kWordsPerStep = kThreads * L::kPerVector / 32;
-        const uint32_t word_lane = tid * L::kPerVector / 32;
-        const uint32_t bit_lane = (tid * L::kPerVector) & 31u;
-        const bool seen_any = state.flags & kSeenAny, with_counts = state.flags & kWithCounts;
-        const uint32_t *bitmap = dyn_smem + word_lane;
-        const uint32_t *running = dyn_smem + p.bitmap_words + word_lane;
-        const uint32_t *dense = dyn_smem + 2 * p.bitmap_words;
-        const uint4 *source = reinterpret_cast<const uint4 *>(columns) + tid + kTileVectors;
-        uint4 raw[L::kVectors];
-#pragma unroll
-        for (int u = 0; u < L::kVectors; u++) raw[u] = load_stream_128(source + u * kThreads);
-        for (uint32_t t = 1; t < full_tiles; t++) {
-            float v[kElemsPerThread];
-#pragma unroll
-            for (int u = 0; u < L::kVectors; u++) L::unpack(raw[u], &v[u * L::kPerVector]);
-            source += kTileVectors;
-            if (t + 1 < full_tiles) {
-#pragma unroll
-                for (int u = 0; u < L::kVectors; u++) raw[u] = load_stream_128(source + u * kThreads);
-            }
-            const uint32_t tile_word = t * (kTile / 32);
-            if (seen_any) {
-#pragma unroll
-                for (int u = 0; u < L::kVectors; u++) {
-                    const uint32_t word = bitmap[tile_word + u * kWordsPerStep];
-                    const uint32_t bits = (word >> bit_lane) & ((1u << L::kPerVector) - 1u);
-                    if (bits == 0) continue;
-#pragma unroll
-                    for (int j = 0; j < L::kPerVector; j++) {
-                        if (bits & (1u << j)) {
-                            float offset = state.flat_offset;
-                            if (with_counts) {
-                                const uint32_t below = (1u << (bit_lane + j)) - 1u;
-                                offset = __uint_as_float(
-                                    dense[min(running[tile_word + u * kWordsPerStep] +
-                                                  __popc(word & below),
-                                              p.count_capacity - 1)]);
-                            }
-                            v[u * L::kPerVector + j] = penalise_with_offset(
-                                v[u * L::kPerVector + j], offset, state.repetition);
-                        }
-                    }
-                }
-            }
-            bool hot = false;  // a value above the bound (NaN never compares above)
-#pragma unroll
-            for (int u = 0; u < L::kVectors; u++) {
-                float top = v[u * L::kPerVector];
-#pragma unroll
-                for (int j = 1; j < L::kPerVector; j++) top = fmaxf(top, v[u * L::kPerVector + j]);
-                hot = hot || top > tau;
-            }
-            if (greedy) {  // the argmax order must see NaN and both infinities
-                uint32_t widest = 0;
-#pragma unroll
-                for (int e = 0; e < kElemsPerThread; e++)
-                    widest = max(widest, __float_as_uint(v[e]) & 0x7fffffffu);
-                hot = hot || widest >= 0x7f800000u;
-            }
-            uint32_t pending = 0;
-            bool trouble = false;
-            if (__any_sync(kFullMask, hot)) {  // rare: the values travel by value
-                Values16 x;
-#pragma unroll
-                for (int e = 0; e < kElemsPerThread; e++) x.v[e] = v[e];
-                pending = tile_slow_path<T>(sh.cand, x, t * kTile, n, tau, false, greedy,
-                                            state.id_base, &sh.wild_key, &trouble);
-            }
-            // one barrier per tile: does anybody need the list cut back?
-            if (__syncthreads_or(trouble)) {
-                Values16 x;
-#pragma unroll
-                for (int e = 0; e < kElemsPerThread; e++) x.v[e] = v[e];
-                tau = resolve_overflow<T>(sh.cand, x, pending, t * kTile, state.k, state.id_base);
-            }
+    for (uint32_t t = 1; t < full_tiles;) {
+        const uint32_t stopped = fast_tiles<T>(p, sh, dyn_smem, columns, t, full_tiles, state, tau);
+        t = (stopped & ~kNeedsAttention) + 1;
+        if (stopped & kNeedsAttention) {
+            // a tile pushed more than the list holds: feed it again in pieces;
+            // otherwise the list is merely long: cut it, which lifts the bound
+            if (sh.overflow) tau = redo_tile<T>(p, sh, dyn_smem, columns, t - 1, state);
+            else tau = cut_list(sh, state.k);
         }
     }
     // the ragged end of an aligned row, or every further tile of an unaligned one
