@@ -69,6 +69,7 @@ def build_library(verbose: bool = False, force: bool = False) -> Path:
     for name in CUDA_SOURCES:
         obj = OBJ_DIR / (name + ".o")
         extra = ["-Xptxas", "-v"] if verbose else []
+        extra += os.environ.get("FGK_EXTRA_NVCC_FLAGS", "").split()  # kernel-tuning experiments
         _run([NVCC, *NVCC_FLAGS, *extra, "-c", str(CSRC / "cuda" / name), "-o", str(obj)], verbose)
         objects.append(str(obj))
     for name in HOST_SOURCES:

@@ -78,6 +78,7 @@ typedef struct fgk_stream_launch {
     uint32_t *tickets;
     uint32_t bitmap_words;
     uint32_t count_capacity;
+    uint32_t dense_wide;
     fgk_select_output out;
 } fgk_stream_launch;
 
@@ -85,6 +86,7 @@ uint32_t fgk_stream_max_splits(void);
 uint32_t fgk_stream_tile(void);
 uint32_t fgk_stream_threads(void);
 uint64_t fgk_stream_part_meta_bytes(void);
+uint64_t fgk_stream_dynamic_smem(uint32_t bitmap_words, uint32_t count_capacity, uint32_t dense_wide);
 int fgk_stream_prepare(void);
 int fgk_launch_stream_select(const fgk_stream_launch *launch, void *stream);
 

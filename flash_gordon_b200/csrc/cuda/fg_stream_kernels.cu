@@ -28,7 +28,7 @@ namespace fgk {
 constexpr int kThreads = 256;
 constexpr int kElemsPerThread = 16;
 constexpr int kTile = kThreads * kElemsPerThread;  // 4096 logits per CTA iteration
-constexpr int kCandCap = 2048;
+constexpr int kCandCap = 1024;
 constexpr uint32_t kMaxSplits = 16;  // the merge of 16 x 64 survivors fits one candidate buffer
 
 struct alignas(16) PartMeta {
@@ -60,6 +60,7 @@ struct StreamParams {
     uint32_t history_max;           // caller's bound on any row's history length
     uint32_t bitmap_words;          // shared-memory layout (0: no history structure)
     uint32_t count_capacity;        // entries of the dense count array (0: counts unused)
+    uint32_t dense_wide;            // dense counts are u32 (histories longer than 65,535)
     SelectOutput out;
 };
 
@@ -282,6 +283,38 @@ __device__ __noinline__ float resolve_overflow(CandidateBuffer<kCandCap> &cand, 
     return tau;
 }
 
+// Shared-memory picture of the part of a row's history that falls into this split:
+//   bitmap   bit c set = column c occurs in the history            u32[bitmap_words]
+//   running  number of seen columns before each bitmap word        u16[bitmap_words]
+//   dense    occurrences of each seen column, in column order      u16 or u32[count_capacity]
+// (u32 counts only when a history may be longer than 65,535 tokens.)
+struct HistoryView {
+    uint32_t *bitmap;
+    uint16_t *running;
+    void *dense;
+    uint32_t capacity;
+    bool wide;
+
+    __device__ __forceinline__ uint32_t slot(uint32_t word_index, uint32_t word, uint32_t bit) const {
+        return min(running[word_index] + __popc(word & ((1u << bit) - 1u)), capacity - 1);
+    }
+    __device__ __forceinline__ uint32_t count(uint32_t word_index, uint32_t word, uint32_t bit) const {
+        const uint32_t at = slot(word_index, word, bit);
+        return wide ? static_cast<const uint32_t *>(dense)[at]
+                    : static_cast<const uint16_t *>(dense)[at];
+    }
+};
+
+__device__ __forceinline__ HistoryView history_view(const StreamParams &p, uint32_t *dyn_smem) {
+    HistoryView h;
+    h.bitmap = dyn_smem;
+    h.running = reinterpret_cast<uint16_t *>(dyn_smem + p.bitmap_words);
+    h.dense = dyn_smem + p.bitmap_words + (p.bitmap_words + 1) / 2;
+    h.capacity = p.count_capacity;
+    h.wide = p.dense_wide != 0;
+    return h;
+}
+
 // Flags build_history hands back.
 constexpr uint32_t kSeenAny = 1u;      // the row has penalties and history inside this split
 constexpr uint32_t kWithCounts = 2u;   // ... and a frequency penalty, so counts are kept
@@ -296,9 +329,9 @@ __device__ __noinline__ uint32_t build_history(const StreamParams &p, StreamShar
                                                uint32_t *dyn_smem, uint32_t row, uint32_t lo,
                                                uint32_t n, const SamplerConfig cfg) {
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
-    uint32_t *bitmap = dyn_smem;
-    uint32_t *running = dyn_smem + p.bitmap_words;
-    uint32_t *dense = dyn_smem + 2 * p.bitmap_words;
+    const HistoryView view = history_view(p, dyn_smem);
+    uint32_t *bitmap = view.bitmap;
+    uint16_t *running = view.running;
     const uint32_t words = (n + 31u) >> 5;
     uint32_t history_len = 0;
     const uint32_t *history = nullptr;
@@ -348,27 +381,26 @@ __device__ __noinline__ uint32_t build_history(const StreamParams &p, StreamShar
     for (uint32_t q = 0; q < warp; q++) before += sh.scan[q];
     if (tid == kThreads - 1) sh.distinct = before + mine;
     for (uint32_t w = w0; w < w1; w++) {
-        running[w] = before;
+        running[w] = (uint16_t)before;  // the host keeps count_capacity below 65,536
         before += __popc(bitmap[w]);
     }
     __syncthreads();
     // the host sizes count_capacity >= min(history_max, split_len) >= distinct
     const uint32_t distinct = min(sh.distinct, p.count_capacity);
-    for (uint32_t i = tid; i < distinct; i += kThreads) dense[i] = 0;
+    uint32_t *dense_words = static_cast<uint32_t *>(view.dense);
+    const uint32_t dense_word_count = view.wide ? distinct : (distinct + 1) / 2;
+    for (uint32_t i = tid; i < dense_word_count; i += kThreads) dense_words[i] = 0;
     __syncthreads();
     for (uint32_t i = tid; i < history_len; i += kThreads) {
         const uint32_t local = history[i] - first_global;
         if (local < n) {
-            const uint32_t word = bitmap[local >> 5];
-            const uint32_t at = running[local >> 5] + __popc(word & ((1u << (local & 31u)) - 1u));
-            if (at < p.count_capacity) atomicAdd(&dense[at], 1u);
+            const uint32_t at = view.slot(local >> 5, bitmap[local >> 5], local & 31u);
+            // 16-bit counts share a word: add into the right half (a half cannot carry,
+            // a history that could overflow it uses 32-bit counts)
+            if (view.wide) atomicAdd(&dense_words[at], 1u);
+            else atomicAdd(&dense_words[at >> 1], 1u << (16u * (at & 1u)));
         }
     }
-    __syncthreads();
-    // counts -> the offset each seen id is charged, once per row instead of per use
-    for (uint32_t i = tid; i < distinct; i += kThreads)
-        dense[i] = __float_as_uint(
-            penalty_offset(dense[i], cfg.presence_penalty, cfg.frequency_penalty));
     __syncthreads();
     return kSeenAny | kWithCounts;
 }
@@ -382,6 +414,7 @@ struct RowState {
     bool greedy;
     bool aligned;
     float flat_offset;   // offset when counts are not kept (frequency is +-0)
+    float presence, frequency;
     Repetition repetition;
 };
 
@@ -407,28 +440,25 @@ __device__ __forceinline__ void load_penalised(const StreamParams &p, const uint
 #pragma unroll
     for (int u = 0; u < L::kVectors; u++) L::unpack(raw[u], &x.v[u * L::kPerVector]);
     if ((row.flags & kSeenAny) == 0) return;
-    const uint32_t *bitmap = dyn_smem;
-    const uint32_t *running = dyn_smem + p.bitmap_words;
-    const uint32_t *dense = dyn_smem + 2 * p.bitmap_words;
+    const HistoryView view = history_view(p, const_cast<uint32_t *>(dyn_smem));
 #pragma unroll
     for (int e = 0; e < kElemsPerThread; e++) {
         const uint32_t column = column_of<T>(tile_base, e / L::kPerVector, e % L::kPerVector);
         if (column >= row.n) continue;
-        const uint32_t word = bitmap[column >> 5];
+        const uint32_t word = view.bitmap[column >> 5];
         if (((word >> (column & 31u)) & 1u) == 0) continue;
         float offset = row.flat_offset;
-        if (row.flags & kWithCounts) {
-            const uint32_t at = running[column >> 5] + __popc(word & ((1u << (column & 31u)) - 1u));
-            offset = __uint_as_float(dense[min(at, p.count_capacity - 1)]);
-        }
+        if (row.flags & kWithCounts)
+            offset = penalty_offset(view.count(column >> 5, word, column & 31u),
+                                    row.presence, row.frequency);
         x.v[e] = penalise_with_offset(x.v[e], offset, row.repetition);
     }
 }
 
 // A tile of the fast loop pushed more values than the list could take (sorted or
 // constant rows do that).  Take back what the tile stored, then feed the tile again
-// from memory a quarter at a time with a cut before each quarter, so the list can
-// never overflow: k + kThreads * 4 <= kCandCap.  Ties with the bound are resolved on
+// from memory an eighth at a time with a cut before each eighth, so the list can
+// never overflow: k + kThreads * 2 <= kCandCap.  Ties with the bound are resolved on
 // the id, as the bound may now come from this very tile.  Every thread of the CTA
 // calls it.  Returns the new bound.
 template <typename T>
@@ -436,7 +466,7 @@ __device__ __noinline__ float redo_tile(const StreamParams &p, StreamShared &sh,
                                         const uint32_t *dyn_smem, const T *columns, uint32_t t,
                                         const RowState row) {
     using L = Loader<T>;
-    static_assert(kMaxK + kThreads * 4 <= kCandCap, "a quarter tile fits behind the k survivors");
+    static_assert(kMaxK + kThreads * 2 <= kCandCap, "an eighth of a tile fits behind the k survivors");
     constexpr int PER = kCandCap / kThreads;
     const uint32_t tid = threadIdx.x;
     const uint32_t tile_base = t * kTile;
@@ -473,11 +503,11 @@ __device__ __noinline__ float redo_tile(const StreamParams &p, StreamShared &sh,
     Values16 x;
     load_penalised<T>(p, dyn_smem, columns, tile_base, row, x);
 #pragma unroll
-    for (int quarter = 0; quarter < 4; quarter++) {
+    for (int eighth = 0; eighth < 8; eighth++) {
         const float tau = cut_list(sh, row.k);
         const uint32_t tau_id = sh.cand.tau_id;
 #pragma unroll
-        for (int e = quarter * 4; e < quarter * 4 + 4; e++) {
+        for (int e = eighth * 2; e < eighth * 2 + 2; e++) {
             const uint32_t column = column_of<T>(tile_base, e / L::kPerVector, e % L::kPerVector);
             if (column >= row.n) continue;
             if (is_nonfinite(x.v[e])) {
@@ -665,9 +695,15 @@ __device__ __noinline__ void finish_split(const StreamParams &p, StreamShared &s
 // or a tile that overflowed it) the loop stops and says so; the caller deals with it
 // and comes back.  Returns the last tile it examined, with kNeedsAttention set if it
 // stopped early.
+//
+// kLowering: every penalty of the row can only lower a logit (presence >= 0,
+// frequency >= 0, repetition >= 1, all three roundings are monotone).  A raw value at
+// or below the bound then stays there once penalised, so the history is consulted
+// only for the few values that beat the bound raw.  Otherwise seen ids are penalised
+// before anything is compared.
 constexpr uint32_t kNeedsAttention = 0x80000000u;
 
-template <typename T>
+template <typename T, bool kLowering>
 __device__ __noinline__ uint32_t fast_tiles(const StreamParams &p, StreamShared &sh,
                                             const uint32_t *dyn_smem, const T *columns,
                                             uint32_t first_tile, uint32_t full_tiles,
@@ -684,9 +720,8 @@ __device__ __noinline__ uint32_t fast_tiles(const StreamParams &p, StreamShared 
     const uint32_t word_lane = tid * L::kPerVector / 32;
     const uint32_t bit_lane = (tid * L::kPerVector) & 31u;
     const bool seen_any = state.flags & kSeenAny, with_counts = state.flags & kWithCounts;
-    const uint32_t *bitmap = dyn_smem + word_lane;
-    const uint32_t *running = dyn_smem + p.bitmap_words + word_lane;
-    const uint32_t *dense = dyn_smem + 2 * p.bitmap_words;
+    const HistoryView view = history_view(p, const_cast<uint32_t *>(dyn_smem));
+    const uint32_t *bitmap = view.bitmap + word_lane;
     // cut the list once it holds a few multiples of k: the bound stays close to the
     // true k-th best and fewer values reach the list at all
     const uint32_t cut_at = 4 * state.k + 64;
@@ -707,7 +742,7 @@ __device__ __noinline__ uint32_t fast_tiles(const StreamParams &p, StreamShared 
             float v[L::kPerVector];
             L::unpack(raw[u], v);
             if (more) raw[u] = load_stream_128(source + u * kThreads);
-            if (seen_any) {
+            if (!kLowering && seen_any) {
                 const uint32_t word = bitmap[tile_word + u * kWordsPerStep];
                 const uint32_t bits = (word >> bit_lane) & ((1u << L::kPerVector) - 1u);
                 if (bits != 0) {
@@ -715,13 +750,11 @@ __device__ __noinline__ uint32_t fast_tiles(const StreamParams &p, StreamShared 
                     for (int j = 0; j < L::kPerVector; j++) {
                         if (bits & (1u << j)) {
                             float offset = state.flat_offset;
-                            if (with_counts) {
-                                const uint32_t below = (1u << (bit_lane + j)) - 1u;
-                                offset = __uint_as_float(
-                                    dense[min(running[tile_word + u * kWordsPerStep] +
-                                                  __popc(word & below),
-                                              p.count_capacity - 1)]);
-                            }
+                            if (with_counts)
+                                offset = penalty_offset(
+                                    view.count(tile_word + u * kWordsPerStep + word_lane, word,
+                                               bit_lane + j),
+                                    state.presence, state.frequency);
                             v[j] = penalise_with_offset(v[j], offset, state.repetition);
                         }
                     }
@@ -736,12 +769,30 @@ __device__ __noinline__ uint32_t fast_tiles(const StreamParams &p, StreamShared 
 #pragma unroll
                 for (int j = 0; j < L::kPerVector; j++)
                     widest = max(widest, __float_as_uint(v[j]) & 0x7fffffffu);
-                hot = hot || widest >= 0x7f800000u;
+                // also magnitudes a penalty could push to infinity (|v| >= 2^87 with a
+                // repetition factor of at most 2^40)
+                hot = hot || widest >= (kLowering ? 0x6b000000u : 0x7f800000u);
             }
             if (hot) {
                 // Few lanes get here once the bound has settled.  Later columns carry
                 // larger ids than whatever produced the bound, so a tie with it loses.
                 const uint32_t first_id = state.id_base + column_of<T>(t * kTile, u, 0);
+                if (kLowering && seen_any) {
+                    const uint32_t word = bitmap[tile_word + u * kWordsPerStep];
+                    const uint32_t bits = (word >> bit_lane) & ((1u << L::kPerVector) - 1u);
+#pragma unroll
+                    for (int j = 0; j < L::kPerVector; j++) {
+                        if (bits & (1u << j)) {
+                            float offset = state.flat_offset;
+                            if (with_counts)
+                                offset = penalty_offset(
+                                    view.count(tile_word + u * kWordsPerStep + word_lane, word,
+                                               bit_lane + j),
+                                    state.presence, state.frequency);
+                            v[j] = penalise_with_offset(v[j], offset, state.repetition);
+                        }
+                    }
+                }
 #pragma unroll
                 for (int j = 0; j < L::kPerVector; j++) {
                     if (is_nonfinite(v[j])) {
@@ -791,6 +842,8 @@ stream_select_kernel(const __grid_constant__ StreamParams p) {
     state.aligned = (reinterpret_cast<uintptr_t>(columns) & 15u) == 0;
     // without a count array frequency is +-0 and the product does not depend on the count
     state.flat_offset = penalty_offset(1u, cfg.presence_penalty, cfg.frequency_penalty);
+    state.presence = cfg.presence_penalty;
+    state.frequency = cfg.frequency_penalty;
     state.repetition = make_repetition(cfg.repetition_penalty);
 
     if (tid == 0) {
@@ -806,6 +859,10 @@ stream_select_kernel(const __grid_constant__ StreamParams p) {
 
     // ---- 1. history slice -> bitmap / running popcount / offsets ----
     state.flags = build_history(p, sh, dyn_smem, row, lo, state.n, cfg);
+#ifdef FGK_EXPERIMENT_HISTORY_ONLY
+    if (tid == 0) p.out.row_status[row] = 0;
+    return;
+#endif
 
     // ---- 2. stream the columns ----
     // Tiles 1 .. full-1 of a 16-byte aligned row take the fast loop below: 128-bit
@@ -817,8 +874,14 @@ stream_select_kernel(const __grid_constant__ StreamParams p) {
     const uint32_t full_tiles = state.aligned ? n / kTile : 0;
     float tau = careful_tile<T>(p, sh, dyn_smem, columns, 0, state, __uint_as_float(0xff800000u));
 
+    // can the row's penalties only lower a logit?  (rows without history count as such)
+    const bool lowering = !(state.flags & kSeenAny) ||
+                          (cfg.presence_penalty >= 0.0f && cfg.frequency_penalty >= 0.0f &&
+                           cfg.repetition_penalty >= 1.0f && state.repetition.tame);
     for (uint32_t t = 1; t < full_tiles;) {
-        const uint32_t stopped = fast_tiles<T>(p, sh, dyn_smem, columns, t, full_tiles, state, tau);
+        const uint32_t stopped =
+            lowering ? fast_tiles<T, true>(p, sh, dyn_smem, columns, t, full_tiles, state, tau)
+                     : fast_tiles<T, false>(p, sh, dyn_smem, columns, t, full_tiles, state, tau);
         t = (stopped & ~kNeedsAttention) + 1;
         if (stopped & kNeedsAttention) {
             // a tile pushed more than the list holds: feed it again in pieces;
@@ -972,6 +1035,16 @@ extern "C" uint32_t fgk_stream_tile(void) { return kTile; }
 extern "C" uint32_t fgk_stream_threads(void) { return kThreads; }
 extern "C" uint64_t fgk_stream_part_meta_bytes(void) { return sizeof(PartMeta); }
 
+// bitmap words, then (only when counts are kept) 16-bit running popcounts and the
+// dense counts, 16 or 32 bits each
+extern "C" uint64_t fgk_stream_dynamic_smem(uint32_t bitmap_words, uint32_t count_capacity,
+                                            uint32_t dense_wide) {
+    uint64_t words = bitmap_words;
+    if (count_capacity)
+        words += (bitmap_words + 1) / 2 + (dense_wide ? count_capacity : (count_capacity + 1) / 2);
+    return words * sizeof(uint32_t);
+}
+
 extern "C" int fgk_stream_prepare(void) {
     // opt in to the large dynamic shared-memory carve-out once per process
     cudaError_t e = cudaFuncSetAttribute(stream_select_kernel<float>,
@@ -1010,11 +1083,10 @@ extern "C" int fgk_launch_stream_select(const fgk_stream_launch *l, void *stream
     p.history_max = l->history_max;
     p.bitmap_words = l->bitmap_words;
     p.count_capacity = l->count_capacity;
+    p.dense_wide = l->dense_wide;
     p.out = make_output(&l->out);
     const dim3 grid(l->splits, l->rows);
-    // bitmap, then (only when counts are kept) running popcounts and dense counts
-    const size_t dynamic =
-        ((size_t)(l->count_capacity ? 2 : 1) * l->bitmap_words + l->count_capacity) * sizeof(uint32_t);
+    const size_t dynamic = fgk_stream_dynamic_smem(l->bitmap_words, l->count_capacity, l->dense_wide);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (l->dtype == 1u)
         stream_select_kernel<uint16_t><<<grid, kThreads, dynamic, s>>>(p);

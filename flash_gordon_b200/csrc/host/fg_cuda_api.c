@@ -430,7 +430,7 @@ fg_status fg_cuda_history_increment(fg_cuda_context *c, fg_cuda_tensor *counts, 
 /* ------------------------------------------------------------ fused batched */
 
 typedef struct stream_plan {
-    uint32_t splits, split_len, bitmap_words, count_capacity;
+    uint32_t splits, split_len, bitmap_words, count_capacity, dense_wide;
     size_t dynamic_smem;
 } stream_plan;
 
@@ -456,7 +456,9 @@ static bool plan_stream(const fg_cuda_context *c, uint32_t rows, uint32_t vocab,
         p.bitmap_words = penalties ? (len + 31u) / 32u : 0u;
         p.count_capacity = (penalties && counts) ? (history_max < len ? history_max : len) : 0u;
         if (p.count_capacity == 0u && penalties && counts) p.count_capacity = 1u;
-        p.dynamic_smem = ((size_t)(p.count_capacity ? 2u : 1u) * p.bitmap_words + p.count_capacity) * 4u;
+        if (p.count_capacity > 65535u) continue; /* running popcounts are 16 bits wide */
+        p.dense_wide = history_max > 65535u ? 1u : 0u;
+        p.dynamic_smem = (size_t)fgk_stream_dynamic_smem(p.bitmap_words, p.count_capacity, p.dense_wide);
         if (p.dynamic_smem > FGK_STREAM_MAX_DYNAMIC_SMEM) continue;
         const double units = (double)rows * splits;
         const double waves = ceil(units / slots);
@@ -614,6 +616,7 @@ static fg_status run_stream(fg_cuda_context *c, const fg_cuda_sample_args *a,
     l.tickets = c->tickets;
     l.bitmap_words = plan.bitmap_words;
     l.count_capacity = plan.count_capacity;
+    l.dense_wide = plan.dense_wide;
     fill_output(&l.out, c, a);
     const int e = fgk_launch_stream_select(&l, c->stream);
     c->launches++;
