@@ -179,7 +179,7 @@ def run_reference(args, rank: int):
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=200)
+    parser.add_argument("--steps", type=int, default=2000)
     parser.add_argument("--warmup", type=int, default=10)
     parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
     parser.add_argument("--e2e-steps", type=int, default=10)

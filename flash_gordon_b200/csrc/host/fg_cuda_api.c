@@ -434,45 +434,41 @@ typedef struct stream_plan {
     size_t dynamic_smem;
 } stream_plan;
 
-/* Picks how many CTAs share a row.  More splits fill the SMs when rows are few
- * and smooth the last wave when they are many; fewer splits amortise the
- * per-CTA history set-up.  Results do not depend on the choice. */
+/* Picks how many CTAs share a row.  Every CTA of a row rebuilds the row's history
+ * structure and pays the fixed cost of a split, so one CTA per row is best as
+ * soon as there are enough rows to occupy every CTA slot of the GPU; with fewer
+ * rows a row is cut into as many column ranges as it takes to fill the slots.
+ * Results do not depend on the choice. */
 static bool plan_stream(const fg_cuda_context *c, uint32_t rows, uint32_t vocab,
                         uint32_t history_max, bool penalties, bool counts, stream_plan *plan) {
     const uint32_t max_splits = fgk_stream_max_splits();
     const uint32_t tile = fgk_stream_tile();
-    const double slots = (double)c->sm_count * 4.0;
-    double best_score = -1.0;
-    stream_plan best = {0};
-    for (uint32_t want = 1; want <= max_splits; want++) {
-        if (c->forced_splits && want != c->forced_splits) continue;
+    const uint32_t slots = c->sm_count * 4u;
+    uint32_t want = c->forced_splits;
+    if (!want) {
+        want = rows >= slots ? 1u : (slots + rows - 1u) / rows;
+        /* a split shorter than two tiles is all fixed cost */
+        const uint32_t most = vocab / (2u * tile) ? vocab / (2u * tile) : 1u;
+        if (want > most) want = most;
+        if (want > max_splits) want = max_splits;
+    }
+    for (; want <= max_splits; want++) {
         uint32_t len = (vocab + want - 1u) / want;
         len = (len + 127u) & ~127u;
-        const uint32_t splits = (vocab + len - 1u) / len;
-        if (splits != want && !(c->forced_splits && want == c->forced_splits)) continue;
         stream_plan p;
-        p.splits = splits;
+        p.splits = (vocab + len - 1u) / len;
         p.split_len = len;
         p.bitmap_words = penalties ? (len + 31u) / 32u : 0u;
         p.count_capacity = (penalties && counts) ? (history_max < len ? history_max : len) : 0u;
         if (p.count_capacity == 0u && penalties && counts) p.count_capacity = 1u;
-        if (p.count_capacity > 65535u) continue; /* running popcounts are 16 bits wide */
         p.dense_wide = history_max > 65535u ? 1u : 0u;
         p.dynamic_smem = (size_t)fgk_stream_dynamic_smem(p.bitmap_words, p.count_capacity, p.dense_wide);
-        if (p.dynamic_smem > FGK_STREAM_MAX_DYNAMIC_SMEM) continue;
-        const double units = (double)rows * splits;
-        const double waves = ceil(units / slots);
-        double score = units / (waves * slots);
-        if (p.dynamic_smem > FGK_STREAM_COMFORT_DYNAMIC_SMEM) score *= 0.6;
-        if (len < 2u * tile && splits > 1u) score *= 0.85;
-        if (score > best_score + 0.03) {
-            best_score = score;
-            best = p;
-        }
+        /* running popcounts are 16 bits wide; more splits shrink both limits */
+        if (p.count_capacity > 65535u || p.dynamic_smem > FGK_STREAM_MAX_DYNAMIC_SMEM) continue;
+        *plan = p;
+        return true;
     }
-    if (best_score < 0.0) return false;
-    *plan = best;
-    return true;
+    return false;
 }
 
 typedef struct batch_traits {
