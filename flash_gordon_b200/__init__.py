@@ -148,6 +148,7 @@ def load_library() -> ctypes.CDLL:
         "fg_cuda_history_increment": (c_int, [P, P, u32, u32, E]),
         "fg_cuda_sample_batch": (c_int, [P, POINTER(SampleArgs), E]),
         "fg_cuda_sample_batch_host": (c_int, [P, POINTER(SampleArgs), E]),
+        "fg_cuda_sample_batch_static": (c_int, [c_int, P, POINTER(SampleArgs), E]),
         "fg_cuda_shard_topk": (c_int, [P, POINTER(SampleArgs), u32, u32, u32, P, P, E]),
         "fg_cuda_merge_select": (c_int, [P, POINTER(SampleArgs), P, P, u32, u32, P, P, E]),
     }

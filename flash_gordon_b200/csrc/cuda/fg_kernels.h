@@ -105,6 +105,11 @@ typedef struct fgk_merge_launch {
 
 int fgk_launch_merge_select(const fgk_merge_launch *launch, void *stream);
 
+/* scratch compiled into the library image (no allocation); address valid on `device`,
+ * which must be current on the first call for that device */
+#define FGK_STATIC_SCRATCH_BYTES (4u << 20)
+int fgk_static_scratch_address(int device, void **address);
+
 /* ---- device operators (fg_ops_kernels.cu) ---- */
 int fgk_launch_apply_penalties(float *logits, const uint32_t *counts, uint32_t values,
                                float presence, float frequency, float repetition, void *stream);

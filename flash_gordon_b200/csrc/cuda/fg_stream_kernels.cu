@@ -1115,3 +1115,30 @@ extern "C" int fgk_launch_merge_select(const fgk_merge_launch *l, void *stream) 
     merge_select_kernel<<<l->rows, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
     return (int)cudaGetLastError();
 }
+
+// ------------------------------------------------- scratch that nobody allocates
+//
+// For callers that cannot allocate device memory at all, the hand-off area of the
+// split path lives in the library image itself: every GPU that loads the library
+// carries these 4 MiB until the process exits.  In host code the array's name is
+// only a stand-in for the symbol; the device address comes from
+// cudaGetSymbolAddress, asked once per device with that device current.
+
+static __device__ __align__(256) unsigned char fgk_static_scratch[FGK_STATIC_SCRATCH_BYTES];
+
+extern "C" int fgk_static_scratch_address(int device, void **address) {
+    static void *known[64];
+    if (device < 0 || device >= 64) return (int)cudaErrorInvalidDevice;
+    if (!known[device]) {
+        int current = -1;
+        cudaError_t e = cudaGetDevice(&current);
+        if (e != cudaSuccess) return (int)e;
+        if (current != device) return (int)cudaErrorInvalidDevice;  // the caller makes it current first
+        void *found = nullptr;
+        e = cudaGetSymbolAddress(&found, fgk_static_scratch);
+        if (e != cudaSuccess) return (int)e;
+        known[device] = found;
+    }
+    *address = known[device];
+    return 0;
+}

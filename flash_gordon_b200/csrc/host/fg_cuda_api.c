@@ -772,3 +772,101 @@ fg_status fg_cuda_sample_batch_host(fg_cuda_context *c, const fg_cuda_sample_arg
     if (e) return fg_cuda_fail(err, e, "copying sampling results to the host");
     return collect_status(c, err);
 }
+
+/* ------------------------------------------------- the entry that allocates nothing */
+
+fg_status fg_cuda_sample_batch_static(int device, void *cuda_stream, const fg_cuda_sample_args *a,
+                                      fg_error *err) {
+    int sms = 0;
+    int e = device < 0 ? 101 : fgk_set_device(device);
+    if (!e) e = fgk_device_sm_count(device, &sms);
+    if (e) return fg_cuda_fail(err, e, "selecting the CUDA device");
+    /* a context on the stack: only its SM count is read by the checks and the planner */
+    fg_cuda_context view;
+    memset(&view, 0, sizeof(view));
+    view.device = device;
+    view.stream = cuda_stream;
+    view.sm_count = (uint32_t)sms;
+    batch_traits traits;
+    fg_status status = check_batch(&view, a, false, &traits, err);
+    if (status != FG_OK) return status;
+    if (traits.nucleus) {
+        fg_error_set(err, FG_ERR_UNAVAILABLE, "sampling without a top-k cut is not built yet");
+        return FG_ERR_UNAVAILABLE;
+    }
+    void *scratch = NULL;
+    e = fgk_static_scratch_address(device, &scratch); /* first call per device: cudaGetSymbolAddress */
+    if (!e) e = fgk_stream_prepare();
+    if (e) return fg_cuda_fail(err, e, "preparing the built-in scratch");
+
+    stream_plan plan;
+    if (!plan_stream(&view, a->rows, a->vocab, a->history_max, traits.penalties, traits.counts, &plan)) {
+        fg_error_set(err, FG_ERR_LIMIT, "history structure does not fit shared memory");
+        return FG_ERR_LIMIT;
+    }
+    /* layout: error word | tickets | per-row configs | split hand-off; fewer splits if it does not fit */
+    const size_t meta_bytes = (size_t)fgk_stream_part_meta_bytes();
+    const size_t at_tickets = 256u;
+    const size_t at_configs = at_tickets + (size_t)fg_align_up_u64((uint64_t)a->rows * 4u, 256u);
+    const size_t at_parts = at_configs + (a->config_count > 1u
+        ? (size_t)fg_align_up_u64((uint64_t)a->rows * sizeof(fg_sampler_config), 256u) : 0u);
+    size_t part_bytes = 0;
+    for (;;) {
+        const size_t slots = (size_t)a->rows * plan.splits;
+        part_bytes = plan.splits > 1u ? slots * (64u * 8u + meta_bytes) : 0u;
+        if (at_parts + part_bytes <= FGK_STATIC_SCRATCH_BYTES) break;
+        if (plan.splits == 1u) {
+            fg_error_set(err, FG_ERR_LIMIT,
+                         "%u rows need %zu bytes of scratch; the built-in scratch holds %u",
+                         a->rows, at_parts + part_bytes, (unsigned)FGK_STATIC_SCRATCH_BYTES);
+            return FG_ERR_LIMIT;
+        }
+        view.forced_splits = plan.splits - 1u;
+        if (!plan_stream(&view, a->rows, a->vocab, a->history_max, traits.penalties, traits.counts, &plan)) {
+            fg_error_set(err, FG_ERR_LIMIT, "no split count fits both shared memory and the built-in scratch");
+            return FG_ERR_LIMIT;
+        }
+    }
+    unsigned char *base = scratch;
+    /* the array keeps whatever the previous call left: the error word and the arrival
+     * counters must start clean */
+    e = fgk_memset_async(base, 0xff, 8u, cuda_stream);
+    if (!e) e = fgk_memset_async(base + at_tickets, 0, (size_t)a->rows * 4u, cuda_stream);
+    if (!e && a->config_count > 1u)
+        e = fgk_copy_to_device_async(base + at_configs, a->configs,
+                                     (size_t)a->rows * sizeof(fg_sampler_config), cuda_stream);
+    if (e) return fg_cuda_fail(err, e, "clearing the built-in scratch");
+
+    fgk_stream_launch l;
+    memset(&l, 0, sizeof(l));
+    l.logits = a->logits;
+    l.dtype = a->dtype;
+    l.rows = a->rows;
+    l.vocab = a->vocab;
+    l.row_stride = a->row_stride;
+    l.vocab_offset = 0u;
+    l.vocab_total = a->vocab;
+    l.splits = plan.splits;
+    l.split_len = plan.split_len;
+    l.history_tokens = traits.penalties ? a->history_tokens : NULL;
+    l.history_offsets = traits.penalties ? a->history_offsets : NULL;
+    l.history_max = a->history_max;
+    l.configs_device = a->config_count > 1u ? base + at_configs : NULL;
+    l.config0 = a->configs[0];
+    l.config_count = a->config_count;
+    l.uniforms = a->uniforms;
+    if (part_bytes) {
+        const size_t slots = (size_t)a->rows * plan.splits;
+        l.part_scores = (float *)(base + at_parts);
+        l.part_ids = (uint32_t *)(base + at_parts + slots * 64u * 4u);
+        l.part_meta = base + at_parts + slots * 64u * 8u;
+    }
+    l.tickets = (uint32_t *)(base + at_tickets);
+    l.bitmap_words = plan.bitmap_words;
+    l.count_capacity = plan.count_capacity;
+    l.dense_wide = plan.dense_wide;
+    view.first_error = (uint64_t *)base;
+    fill_output(&l.out, &view, a);
+    e = fgk_launch_stream_select(&l, cuda_stream);
+    return e ? fg_cuda_fail(err, e, "streaming select kernel") : FG_OK;
+}

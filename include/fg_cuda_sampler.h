@@ -233,6 +233,33 @@ fg_status fg_cuda_merge_select(fg_cuda_context *context, const fg_cuda_sample_ar
                                const uint32_t *shard_first, const uint32_t *shard_width,
                                fg_error *err);
 
+/* No counterpart in the reference.  fg_cuda_sample_batch for callers that must not
+ * allocate GPU memory: a serving process whose own arena already owns the whole
+ * device (so cudaMalloc fails, or may not be called by policy), or a decode loop
+ * that cannot afford the device-wide stall an allocation can cause.  It needs no
+ * fg_cuda_context and calls neither cudaMalloc/cudaFree nor any allocating
+ * library routine: the kernel's scratch (arrival counters, per-row configs, the
+ * hand-off between the CTAs that share a row) lives in a 4 MiB array compiled
+ * into the library, which every GPU that loads the library holds until exit.
+ *   - `device` and `cuda_stream` (a cudaStream_t, NULL = default stream) say where
+ *     to run; inputs and outputs are the caller's device buffers as in
+ *     fg_cuda_sample_batch (args->debug allowed, top_k == 0 rows not supported).
+ *   - Always asynchronous: it returns once the work is enqueued; per-row results
+ *     are in args->row_status after the caller synchronises the stream.
+ *   - The first call on a device looks up the array's device address
+ *     (cudaGetSymbolAddress, with that device made current); make that first
+ *     call before starting any stream capture.
+ *   - Limit: 256 + 4*rows (+ 40*rows with per-row configs) + 528*rows*splits
+ *     bytes must fit 4 MiB; the split count is lowered to make it fit and
+ *     FG_ERR_LIMIT names the sizes when even one CTA per row does not
+ *     (about 95,000 rows).
+ *   - All calls share the one array.  It keeps the previous call's contents (what
+ *     must start at zero is cleared on the stream by each call), and two calls
+ *     whose kernels overlap on the GPU — different streams, or different host
+ *     threads — race on it: issue them one after another on one stream. */
+fg_status fg_cuda_sample_batch_static(int device, void *cuda_stream,
+                                      const fg_cuda_sample_args *args, fg_error *err);
+
 /* Bytes of context scratch the last fg_cuda_sample_batch / shard_topk used
  * (reports and tests). */
 uint64_t fg_cuda_context_scratch_bytes(const fg_cuda_context *context);
