@@ -129,6 +129,7 @@ def load_library() -> ctypes.CDLL:
         "fg_cuda_context_sm_count": (u32, [P]),
         "fg_cuda_context_launches": (u64, [P]),
         "fg_cuda_context_set_splits": (c_int, [P, u32, E]),
+        "fg_cuda_context_set_path": (c_int, [P, u32, E]),
         "fg_cuda_context_scratch_bytes": (u64, [P]),
         "fg_cuda_begin": (c_int, [P, E]),
         "fg_cuda_end": (c_int, [P, E]),

@@ -121,6 +121,13 @@ class Context:
         if status != FG_OK:
             raise FgStatusError(status, err.text())
 
+    def set_path(self, path: int) -> None:
+        """0 automatic, 1 register-prefetch kernel, 2 shared-memory ring kernel."""
+        err = FgError()
+        status = self.lib.fg_cuda_context_set_path(self.handle, path, byref(err))
+        if status != FG_OK:
+            raise FgStatusError(status, err.text())
+
     def begin(self) -> None:
         err = FgError()
         status = self.lib.fg_cuda_begin(self.handle, byref(err))

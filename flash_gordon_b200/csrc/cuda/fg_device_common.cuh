@@ -124,6 +124,59 @@ __device__ __forceinline__ uint4 load_stream_128(const void *p) {
     return r;
 }
 
+// ---- asynchronous bulk copies (the non-tensor form of TMA) and their mbarriers ----
+// One thread asks the copy engine for `bytes` (a multiple of 16, both addresses
+// 16-byte aligned) from global into this CTA's shared memory; completion is counted
+// on an mbarrier the consumers poll.  No multicast anywhere.
+
+__device__ __forceinline__ uint32_t shared_address(const void *p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbarrier_init(uint64_t *barrier, uint32_t arrivals) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(shared_address(barrier)), "r"(arrivals));
+}
+
+__device__ __forceinline__ void mbarrier_fence_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+
+// the producer's arrival, announcing how many bytes the copy will deliver
+__device__ __forceinline__ void mbarrier_expect(uint64_t *barrier, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(shared_address(barrier)),
+                 "r"(bytes)
+                 : "memory");
+}
+
+__device__ __forceinline__ bool mbarrier_try_wait(uint64_t *barrier, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(shared_address(barrier)), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+
+// Bounded wait: gives up after about a second's worth of polls and reports false, so
+// a copy that never lands becomes an error status instead of a hung GPU.
+__device__ __forceinline__ bool mbarrier_wait(uint64_t *barrier, uint32_t parity) {
+    for (uint32_t polls = 0; polls < (1u << 22); polls++)
+        if (mbarrier_try_wait(barrier, parity)) return true;
+    return false;
+}
+
+__device__ __forceinline__ void bulk_copy_to_shared(void *shared_destination, const void *global_source,
+                                                    uint32_t bytes, uint64_t *barrier) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+            shared_address(shared_destination)),
+        "l"(global_source), "r"(bytes), "r"(shared_address(barrier))
+        : "memory");
+}
+
 // The POD the kernels read; layout of fg_sampler_config (include/fg_sampler.h).
 struct SamplerConfig {
     float temperature;

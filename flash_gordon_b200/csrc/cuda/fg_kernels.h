@@ -79,6 +79,10 @@ typedef struct fgk_stream_launch {
     uint32_t bitmap_words;
     uint32_t count_capacity;
     uint32_t dense_wide;
+    /* ring path only: global home of the per-(row, split) history structures */
+    uint32_t *history_global;
+    uint64_t history_stride_words;
+    void *history_meta; /* 8 bytes per (row, split); NULL when the batch has no history */
     fgk_select_output out;
 } fgk_stream_launch;
 
@@ -89,6 +93,9 @@ uint64_t fgk_stream_part_meta_bytes(void);
 uint64_t fgk_stream_dynamic_smem(uint32_t bitmap_words, uint32_t count_capacity, uint32_t dense_wide);
 int fgk_stream_prepare(void);
 int fgk_launch_stream_select(const fgk_stream_launch *launch, void *stream);
+/* rows through a shared-memory ring filled by bulk copies; needs 16-byte aligned rows */
+uint64_t fgk_ring_dynamic_smem(uint32_t dtype);
+int fgk_launch_ring_select(const fgk_stream_launch *launch, void *stream, uint32_t *launched);
 
 typedef struct fgk_merge_launch {
     const float *scores;

@@ -8,6 +8,7 @@
 #include "fg_host_internal.h"
 
 #include <math.h>
+#include <stdint.h>
 #include <stdlib.h>
 #include <string.h>
 
@@ -113,6 +114,7 @@ void fg_cuda_context_destroy(fg_cuda_context *c) {
         if (c->parts) fgk_free(c->parts);
         if (c->tickets) fgk_free(c->tickets);
         if (c->configs) fgk_free(c->configs);
+        if (c->history) fgk_free(c->history);
         if (c->first_error) fgk_free(c->first_error);
         if (c->staging) fgk_free(c->staging);
         if (c->pinned) fgk_host_free(c->pinned);
@@ -150,6 +152,15 @@ fg_status fg_cuda_context_set_splits(fg_cuda_context *c, uint32_t splits, fg_err
         return FG_ERR_ARGUMENT;
     }
     c->forced_splits = splits;
+    return FG_OK;
+}
+
+fg_status fg_cuda_context_set_path(fg_cuda_context *c, uint32_t path, fg_error *err) {
+    if (!c || path > FG_CUDA_PATH_RING) {
+        fg_error_set(err, FG_ERR_ARGUMENT, "invalid streaming path");
+        return FG_ERR_ARGUMENT;
+    }
+    c->path = path;
     return FG_OK;
 }
 
@@ -614,6 +625,33 @@ static fg_status run_stream(fg_cuda_context *c, const fg_cuda_sample_args *a,
     l.count_capacity = plan.count_capacity;
     l.dense_wide = plan.dense_wide;
     fill_output(&l.out, c, a);
+    /* Rows the copy engine can fetch (16-byte aligned row starts, at least one whole
+     * tile after the first) go through the shared-memory ring; the rest, and anything
+     * the caller pinned to it, through the register-prefetch kernel. */
+    const size_t element = a->dtype == FG_CUDA_BF16 ? 2u : 4u;
+    const bool ring_ok = ((uintptr_t)a->logits % 16u) == 0u && (a->row_stride * element) % 16u == 0u &&
+                         plan.split_len >= 2u * fgk_stream_tile();
+    if (c->path == FG_CUDA_PATH_RING && !ring_ok) {
+        fg_error_set(err, FG_ERR_ARGUMENT, "the ring path needs 16-byte aligned rows of at least two tiles");
+        return FG_ERR_ARGUMENT;
+    }
+    if (ring_ok && c->path != FG_CUDA_PATH_REGISTERS) {
+        if (traits->penalties) {
+            const size_t stride_words = plan.dynamic_smem / 4u;
+            const size_t history_bytes = slots * stride_words * 4u;
+            const size_t meta_at = (size_t)fg_align_up_u64(history_bytes, 256u);
+            status = fg_cuda_reserve(&c->history, &c->history_bytes, meta_at + slots * 8u, false, c, err);
+            if (status != FG_OK) return status;
+            l.history_global = c->history;
+            l.history_stride_words = stride_words;
+            l.history_meta = (unsigned char *)c->history + meta_at;
+            c->last_scratch_bytes += meta_at + slots * 8u;
+        }
+        uint32_t launched = 0;
+        const int e = fgk_launch_ring_select(&l, c->stream, &launched);
+        c->launches += launched;
+        return e ? fg_cuda_fail(err, e, "ring select kernels") : FG_OK;
+    }
     const int e = fgk_launch_stream_select(&l, c->stream);
     c->launches++;
     return e ? fg_cuda_fail(err, e, "streaming select kernel") : FG_OK;

@@ -13,12 +13,15 @@ struct fg_cuda_context {
     bool batch_active;
     uint64_t launches;
     uint32_t forced_splits;
+    uint32_t path;          /* FG_CUDA_PATH_* */
 
     /* device scratch, grown on demand and then reused (no allocation on a warm call) */
     void *parts;            /* candidate hand-off between the splits of a row */
     size_t parts_bytes;
     uint32_t *tickets;      /* one arrival counter per row, zero between launches */
     size_t tickets_bytes;
+    void *history;          /* ring path: history structures, one per (row, split) */
+    size_t history_bytes;
     void *configs;          /* per-row configs when they differ */
     size_t configs_bytes;
     uint64_t *first_error;  /* one device word */

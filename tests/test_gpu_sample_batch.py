@@ -17,6 +17,15 @@ pytestmark = pytest.mark.gpu
 PROBABILITY_RTOL = 1e-5
 
 
+@pytest.fixture(params=["auto", "registers"], autouse=True)
+def kernel_path(context, request):
+    """Every case runs twice: with the automatic choice (the shared-memory ring kernel
+    wherever rows are 16-byte aligned) and pinned to the register-prefetch kernel."""
+    context.set_path(0 if request.param == "auto" else 1)
+    yield request.param
+    context.set_path(0)
+
+
 def test_config1_greedy_single_row(context):
     w = synth.config1()
     expected = run_oracle(w, want_candidates=True)

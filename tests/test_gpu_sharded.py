@@ -14,6 +14,13 @@ from helpers import as_u32, assert_candidates_close, assert_rows_equal, logits_t
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(params=["auto", "registers"], autouse=True)
+def kernel_path(context, request):
+    context.set_path(0 if request.param == "auto" else 1)
+    yield request.param
+    context.set_path(0)
+
+
 def run_sharded(context, w, shards, k_shard, debug=False):
     wd = w.to("cuda")
     rows, vocab = wd.rows, wd.vocab
