@@ -122,7 +122,7 @@ class Context:
             raise FgStatusError(status, err.text())
 
     def set_path(self, path: int) -> None:
-        """0 automatic, 1 register-prefetch kernel, 2 shared-memory ring kernel."""
+        """0 automatic, 1 register-prefetch kernel, 2 shared-memory ring kernel, 3 ring where rows allow."""
         err = FgError()
         status = self.lib.fg_cuda_context_set_path(self.handle, path, byref(err))
         if status != FG_OK:

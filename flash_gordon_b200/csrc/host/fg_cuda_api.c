@@ -156,7 +156,7 @@ fg_status fg_cuda_context_set_splits(fg_cuda_context *c, uint32_t splits, fg_err
 }
 
 fg_status fg_cuda_context_set_path(fg_cuda_context *c, uint32_t path, fg_error *err) {
-    if (!c || path > FG_CUDA_PATH_RING) {
+    if (!c || path > FG_CUDA_PATH_RING_IF_POSSIBLE) {
         fg_error_set(err, FG_ERR_ARGUMENT, "invalid streaming path");
         return FG_ERR_ARGUMENT;
     }
@@ -635,7 +635,9 @@ static fg_status run_stream(fg_cuda_context *c, const fg_cuda_sample_args *a,
         fg_error_set(err, FG_ERR_ARGUMENT, "the ring path needs 16-byte aligned rows of at least two tiles");
         return FG_ERR_ARGUMENT;
     }
-    if (ring_ok && c->path != FG_CUDA_PATH_REGISTERS) {
+    /* measured on B200 the register-prefetch kernel is currently the faster one, so it
+     * is also what AUTO picks */
+    if (ring_ok && (c->path == FG_CUDA_PATH_RING || c->path == FG_CUDA_PATH_RING_IF_POSSIBLE)) {
         if (traits->penalties) {
             const size_t stride_words = plan.dynamic_smem / 4u;
             const size_t history_bytes = slots * stride_words * 4u;

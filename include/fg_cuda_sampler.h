@@ -64,13 +64,16 @@ uint64_t fg_cuda_context_launches(const fg_cuda_context *context);
  * 16).  Results never depend on it. */
 fg_status fg_cuda_context_set_splits(fg_cuda_context *context, uint32_t splits, fg_error *err);
 /* Tuning knob, no reference counterpart: which of the two fused kernels a batch
- * takes.  AUTO sends rows whose starts are 16-byte aligned through the
- * shared-memory ring fed by bulk copies and everything else through the
- * register-prefetch kernel; the other two values pin the choice (RING fails with
- * FG_ERR_ARGUMENT on rows it cannot take).  Results never depend on it. */
-#define FG_CUDA_PATH_AUTO      0u
-#define FG_CUDA_PATH_REGISTERS 1u
-#define FG_CUDA_PATH_RING      2u
+ * takes — the register-prefetch kernel (any alignment) or the one that streams
+ * rows through a shared-memory ring fed by bulk copies (rows whose starts are
+ * 16-byte aligned).  AUTO is the library's choice, currently the
+ * register-prefetch kernel, which measures faster; RING fails with
+ * FG_ERR_ARGUMENT on rows it cannot take, RING_IF_POSSIBLE falls back instead.
+ * Results never depend on it. */
+#define FG_CUDA_PATH_AUTO             0u
+#define FG_CUDA_PATH_REGISTERS        1u
+#define FG_CUDA_PATH_RING             2u
+#define FG_CUDA_PATH_RING_IF_POSSIBLE 3u
 fg_status fg_cuda_context_set_path(fg_cuda_context *context, uint32_t path, fg_error *err);
 /* fg_vk_begin / fg_vk_end (include/fg_vk.h:147-148): the reference records
  * dispatches into one submission and waits on its fence at `end`.  Here begin

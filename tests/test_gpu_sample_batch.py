@@ -17,11 +17,11 @@ pytestmark = pytest.mark.gpu
 PROBABILITY_RTOL = 1e-5
 
 
-@pytest.fixture(params=["auto", "registers"], autouse=True)
+@pytest.fixture(params=["ring_if_possible", "registers"], autouse=True)
 def kernel_path(context, request):
-    """Every case runs twice: with the automatic choice (the shared-memory ring kernel
-    wherever rows are 16-byte aligned) and pinned to the register-prefetch kernel."""
-    context.set_path(0 if request.param == "auto" else 1)
+    """Every case runs twice: through the shared-memory ring kernel wherever rows are
+    16-byte aligned, and pinned to the register-prefetch kernel."""
+    context.set_path(3 if request.param == "ring_if_possible" else 1)
     yield request.param
     context.set_path(0)
 

@@ -14,9 +14,9 @@ from helpers import as_u32, assert_candidates_close, assert_rows_equal, logits_t
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(params=["auto", "registers"], autouse=True)
+@pytest.fixture(params=["ring_if_possible", "registers"], autouse=True)
 def kernel_path(context, request):
-    context.set_path(0 if request.param == "auto" else 1)
+    context.set_path(3 if request.param == "ring_if_possible" else 1)
     yield request.param
     context.set_path(0)
 
