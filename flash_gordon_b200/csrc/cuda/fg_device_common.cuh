@@ -196,6 +196,40 @@ __device__ __forceinline__ bool penalties_active(const SamplerConfig &c) {
            c.repetition_penalty != 1.0f;
 }
 
+// Picture of the part of a row's history that falls into one column range, in shared
+// or global memory:
+//   bitmap   bit c set = column c occurs in the history            u32[bitmap_words]
+//   running  number of seen columns before each bitmap word        u16[bitmap_words]
+//   dense    occurrences of each seen column, in column order      u16 or u32[capacity]
+// (u32 counts only when a history may be longer than 65,535 tokens.)
+struct HistoryView {
+    uint32_t *bitmap;
+    uint16_t *running;
+    void *dense;
+    uint32_t capacity;
+    bool wide;
+
+    __device__ __forceinline__ uint32_t slot(uint32_t word_index, uint32_t word, uint32_t bit) const {
+        return min(running[word_index] + __popc(word & ((1u << bit) - 1u)), capacity - 1);
+    }
+    __device__ __forceinline__ uint32_t count(uint32_t word_index, uint32_t word, uint32_t bit) const {
+        const uint32_t at = slot(word_index, word, bit);
+        return wide ? static_cast<const uint32_t *>(dense)[at]
+                    : static_cast<const uint16_t *>(dense)[at];
+    }
+};
+
+__device__ __forceinline__ HistoryView make_history_view(uint32_t *memory, uint32_t bitmap_words,
+                                                         uint32_t capacity, bool wide) {
+    HistoryView h;
+    h.bitmap = memory;
+    h.running = reinterpret_cast<uint16_t *>(memory + bitmap_words);
+    h.dense = memory + bitmap_words + (bitmap_words + 1) / 2;
+    h.capacity = capacity;
+    h.wide = wide;
+    return h;
+}
+
 // fg_status values used on the device (include/fg.h).
 constexpr uint32_t kOk = 0u, kErrFormat = 4u, kErrMismatch = 5u, kErrLimit = 8u;
 

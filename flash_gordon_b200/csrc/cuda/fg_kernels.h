@@ -117,6 +117,31 @@ int fgk_launch_merge_select(const fgk_merge_launch *launch, void *stream);
 #define FGK_STATIC_SCRATCH_BYTES (4u << 20)
 int fgk_static_scratch_address(int device, void **address);
 
+/* ---- sampling without a top-k cut (fg_nucleus_kernel.cu) ---- */
+typedef struct fgk_nucleus_launch {
+    const void *logits;
+    uint32_t dtype;
+    uint32_t rows, vocab;
+    uint64_t row_stride;
+    const void *configs_device;
+    fg_sampler_config config0;
+    uint32_t config_count;
+    const float *uniforms;
+    float *scratch;          /* ctas rows of scratch_stride floats */
+    uint64_t scratch_stride;
+    uint32_t ctas;           /* persistent CTAs, one scratch row each */
+    const uint32_t *history_global;
+    uint64_t history_stride_words;
+    const void *history_meta;
+    uint32_t splits, split_len, bitmap_words, count_capacity, dense_wide;
+    fgk_select_output out;
+} fgk_nucleus_launch;
+
+int fgk_nucleus_prepare(void);
+int fgk_launch_nucleus_select(const fgk_nucleus_launch *launch, void *stream);
+/* the history pass of the ring path on its own (fills history_global / history_meta) */
+int fgk_launch_history_build(const fgk_stream_launch *launch, void *stream);
+
 /* ---- device operators (fg_ops_kernels.cu) ---- */
 int fgk_launch_apply_penalties(float *logits, const uint32_t *counts, uint32_t values,
                                float presence, float frequency, float repetition, void *stream);

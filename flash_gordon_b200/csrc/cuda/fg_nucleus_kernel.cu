@@ -1,0 +1,502 @@
+// Sampling without a top-k cut: top-p over the whole vocabulary, then temperature and
+// inverse CDF — the reference's select step (src/sampler.c:97-121) with limit = every
+// finite logit.  The reference caps candidates at 64; this is the documented
+// generalisation for rows whose nucleus spans tens of thousands of tokens.
+//
+// The vocabulary is never sorted.  A persistent CTA per SM streams a row from HBM once
+// (penalties applied on the way) into its own scratch row, which stays in L2, and then
+// narrows down two positions of the (value descending, id ascending) order by MSB-first
+// radix descent over the 32-bit monotone value key, 12 + 12 + 8 bits: first the element
+// where the cumulative raw-softmax mass reaches top_p, then the element the draw lands
+// on under the tempered weights.  Each level is one pass over the scratch row that
+// builds a bucketed histogram of counts and masses in shared memory, followed by a
+// block-wide prefix sum from the top bucket down.  Equal values are resolved on the
+// id with the same descent (counts only).
+//
+// Masses are exp(s - max) in fp64, accumulated as 2^-40 fixed point in 64-bit
+// integers: integer addition is associative, so the result does not depend on the
+// order threads arrive in, and the 1e-12 grid is far below one element's weight.
+// The reference adds doubles left to right; the two agree unless the top-p bound or
+// the draw falls within ~1e-11 (relative) of an edge of the CDF.
+#include "fg_block_select.cuh"
+#include "fg_kernels.h"
+
+namespace fgk {
+
+constexpr int kNucleusThreads = 1024;
+constexpr int kBuckets = 4096;
+constexpr size_t kNucleusDynamic = kBuckets * (sizeof(unsigned long long) + sizeof(uint32_t));
+
+struct NucleusParams {
+    const void *logits;
+    uint32_t dtype;
+    uint32_t rows, vocab;
+    uint64_t row_stride;
+    const SamplerConfig *configs;
+    SamplerConfig config0;
+    uint32_t config_count;
+    const float *uniforms;
+    float *scratch;            // gridDim.x rows of scratch_stride floats
+    uint64_t scratch_stride;
+    // history structures built by history_build_kernel, one per (row, split)
+    const uint32_t *history_global;
+    uint64_t history_stride_words;
+    const void *history_meta;
+    uint32_t splits, split_len, bitmap_words, count_capacity, dense_wide;
+    SelectOutput out;
+};
+
+struct NucleusShared {
+    unsigned long long *mass;         // kBuckets entries, dynamic shared memory
+    uint32_t *count;                  // kBuckets entries
+    double table[64];                 // 2^(j/64)
+    unsigned long long scan_mass[32];
+    uint32_t scan_count[32];
+    unsigned long long total_mass;
+    float reduce_max[32];
+    uint32_t reduce_count[32];
+    // result of a scan
+    uint32_t hit_bucket;
+    unsigned long long hit_mass_before;
+    uint32_t hit_count_before;
+    uint32_t hit_found;
+};
+
+// exp(x) * 2^40 for x <= 0 as a 64-bit integer (round to nearest): argument reduction
+// to n/64 * ln2 + r, |r| <= ln2/128, a 64-entry table of 2^(j/64) and a degree-5
+// polynomial (truncation 4e-17).  Below e^-70 the weight is under the fixed-point grid.
+__device__ __forceinline__ unsigned long long exp_fixed(double x, const double *table) {
+    if (!(x > -70.0)) return 0ull;
+    const double scaled = x * 92.33248261689366;                  // 64 / ln 2
+    const double shifted = scaled + 6755399441055744.0;           // 1.5 * 2^52: rounds to nearest
+    const int n = __double2loint(shifted);
+    const double nd = shifted - 6755399441055744.0;
+    double r = fma(nd, -1.0830424696249145e-02, x);               // ln2/64, high part
+    r = fma(nd, -3.623510646634843e-19, r);                       // low part
+    double p = fma(r, 8.3333333333333332e-03, 4.1666666666666664e-02);
+    p = fma(p, r, 1.6666666666666666e-01);
+    p = fma(p, r, 0.5);
+    p = fma(p, r, 1.0);
+    p = fma(p, r, 1.0);                                           // 1 + r + r^2/2 + ... + r^5/120
+    const int j = n & 63, k = n >> 6;                             // floor division for negative n
+    const double scale = __longlong_as_double((long long)(k + 40 + 1023) << 52);
+    return __double2ull_rn(table[j] * p * scale);
+}
+
+// Block-wide: walk the buckets from the top; find the first bucket b where
+// before + mass(>= b) reaches `target` (strict: exceeds it).  All threads call.
+__device__ void find_crossing(NucleusShared &sh, uint32_t buckets, unsigned long long before,
+                              unsigned long long target, bool strict) {
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    const uint32_t per = (buckets + kNucleusThreads - 1) / kNucleusThreads;
+    // thread t owns buckets top-down: indices buckets-1 - (t*per + i)
+    unsigned long long mine_mass = 0;
+    uint32_t mine_count = 0;
+    for (uint32_t i = 0; i < per; i++) {
+        const uint32_t at = tid * per + i;
+        if (at < buckets) {
+            mine_mass += sh.mass[buckets - 1 - at];
+            mine_count += sh.count[buckets - 1 - at];
+        }
+    }
+    unsigned long long incl_mass = mine_mass;
+    uint32_t incl_count = mine_count;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const unsigned long long up_mass = __shfl_up_sync(kFullMask, incl_mass, d);
+        const uint32_t up_count = __shfl_up_sync(kFullMask, incl_count, d);
+        if (lane >= (uint32_t)d) {
+            incl_mass += up_mass;
+            incl_count += up_count;
+        }
+    }
+    if (lane == 31) {
+        sh.scan_mass[warp] = incl_mass;
+        sh.scan_count[warp] = incl_count;
+    }
+    if (tid == 0) sh.hit_found = 0;
+    __syncthreads();
+    unsigned long long prior_mass = before + incl_mass - mine_mass;
+    uint32_t prior_count = incl_count - mine_count;
+    for (uint32_t w = 0; w < warp; w++) {
+        prior_mass += sh.scan_mass[w];
+        prior_count += sh.scan_count[w];
+    }
+    const unsigned long long after = prior_mass + mine_mass;
+    const bool was = strict ? prior_mass > target : prior_mass >= target;
+    const bool now = strict ? after > target : after >= target;
+    if (!was && now) {  // exactly one thread
+        for (uint32_t i = 0; i < per; i++) {
+            const uint32_t at = tid * per + i;
+            if (at >= buckets) break;
+            const uint32_t b = buckets - 1 - at;
+            const unsigned long long next = prior_mass + sh.mass[b];
+            if (strict ? next > target : next >= target) {
+                sh.hit_bucket = b;
+                sh.hit_mass_before = prior_mass;
+                sh.hit_count_before = prior_count;
+                sh.hit_found = 1;
+                break;
+            }
+            prior_mass = next;
+            prior_count += sh.count[b];
+        }
+    }
+    __syncthreads();
+}
+
+__device__ __forceinline__ void clear_histogram(NucleusShared &sh, uint32_t buckets) {
+    for (uint32_t b = threadIdx.x; b < buckets; b += kNucleusThreads) {
+        sh.mass[b] = 0;
+        sh.count[b] = 0;
+    }
+    __syncthreads();
+}
+
+// Which elements of the scratch row take part in a descent.
+struct Nucleus {
+    uint32_t key;     // value key of the last element inside
+    uint32_t id;      // ... and its id (ties on the key are ordered by id)
+    bool everything;  // no cut yet: every finite value takes part
+    __device__ __forceinline__ bool holds(uint32_t k, uint32_t i) const {
+        return everything || k > key || (k == key && i <= id);
+    }
+};
+
+// One radix descent over the scratch row.  Weights are exp(value * inv_t - top * inv_t);
+// finds the first element of the (key descending, id ascending) order, restricted to
+// `inside`, at which the cumulative weight reaches `target` (strict: exceeds it).
+// When even the total does not, the last element inside is returned.  Outputs the
+// element's key and id, the cumulative weight up to and including it and its rank.
+// All threads of the CTA call it.
+__device__ void descend(NucleusShared &sh, const float *values, uint32_t vocab, double inv_t,
+                        double top, const Nucleus inside, unsigned long long target, bool strict,
+                        uint32_t *out_key, uint32_t *out_id, unsigned long long *out_mass,
+                        uint32_t *out_rank) {
+    const uint32_t tid = threadIdx.x;
+    const double top_scaled = top * inv_t;
+    uint32_t prefix = 0;  // key bits fixed so far
+    unsigned long long before = 0;
+    uint32_t rank_before = 0;
+    unsigned long long weight_of_key = 0;
+    uint32_t same_key = 0;
+    bool clipped = false;  // target beyond the total: steer to the last element inside
+    const int shifts[3] = {20, 8, 0};
+    const uint32_t widths[3] = {4096, 4096, 256};
+    for (int level = 0; level < 3; level++) {
+        const int shift = shifts[level];
+        const uint32_t buckets = widths[level];
+        clear_histogram(sh, buckets);
+        for (uint32_t i = tid; i < vocab; i += kNucleusThreads) {
+            const float v = values[i];
+            if (is_nonfinite(v)) continue;
+            const uint32_t key = float_key(v);
+            if (level > 0 && (key >> (shift + (level == 1 ? 12 : 8))) != prefix) continue;
+            if (!inside.holds(key, i)) continue;
+            const unsigned long long w = exp_fixed((double)v * inv_t - top_scaled, sh.table);
+            const uint32_t b = (key >> shift) & (buckets - 1);
+            atomicAdd(&sh.mass[b], w);
+            atomicAdd(&sh.count[b], 1u);
+        }
+        __syncthreads();
+        if (!clipped) {
+            find_crossing(sh, buckets, before, target, strict);
+            // the total stays below the target (rounding of the draw, or top_p = 1): the
+            // answer is the last element inside, i.e. the lowest non-empty bucket from here on
+            if (!sh.hit_found) clipped = true;
+            __syncthreads();
+        }
+        if (clipped) {
+            // lowest non-empty bucket: scan by thread 0 (rare path)
+            if (tid == 0) {
+                unsigned long long m = before;
+                uint32_t c = 0, last = 0;
+                bool any = false;
+                for (uint32_t at = 0; at < buckets; at++) {
+                    const uint32_t b = buckets - 1 - at;
+                    if (sh.count[b]) {
+                        if (any) {
+                            m += sh.mass[last];
+                            c += sh.count[last];
+                        }
+                        last = b;
+                        any = true;
+                    }
+                }
+                sh.hit_bucket = last;
+                sh.hit_mass_before = m;
+                sh.hit_count_before = c;
+                sh.hit_found = any ? 1u : 0u;
+            }
+            __syncthreads();
+        }
+        const uint32_t b = sh.hit_bucket;
+        before = sh.hit_mass_before;
+        rank_before += sh.hit_count_before;
+        weight_of_key = sh.mass[b];
+        same_key = sh.count[b];
+        prefix = (prefix << (level == 2 ? 8 : 12)) | b;
+        __syncthreads();
+    }
+    // `prefix` is now a full key; same_key elements share it, each weighing the same
+    const uint32_t key = prefix;
+    const unsigned long long each = same_key ? weight_of_key / same_key : 0;
+    uint32_t need = same_key;  // how many of the equal-valued elements it takes, 1-based
+    if (!clipped && each > 0) {
+        // smallest j with before + j*each reaching the target
+        const unsigned long long gap = target > before ? target - before : 0;
+        unsigned long long j = strict ? gap / each + 1 : (gap + each - 1) / each;
+        if (j < 1) j = 1;
+        if (j < need) need = (uint32_t)j;
+    }
+    // the need-th smallest id among the elements with this key that are inside
+    uint32_t id_prefix = 0, id_rank = need;
+    if (same_key > 1) {
+        for (int level = 0; level < 3; level++) {
+            const int shift = shifts[level];
+            const uint32_t buckets = widths[level];
+            clear_histogram(sh, buckets);
+            for (uint32_t i = tid; i < vocab; i += kNucleusThreads) {
+                const float v = values[i];
+                if (is_nonfinite(v) || float_key(v) != key || !inside.holds(key, i)) continue;
+                if (level > 0 && (i >> (shift + (level == 1 ? 12 : 8))) != id_prefix) continue;
+                // ascending ids: store reversed so the top-down walk visits small ids first
+                atomicAdd(&sh.count[buckets - 1 - ((i >> shift) & (buckets - 1))], 1u);
+                atomicAdd(&sh.mass[buckets - 1 - ((i >> shift) & (buckets - 1))], 1ull);
+            }
+            __syncthreads();
+            find_crossing(sh, buckets, 0, id_rank, false);
+            const uint32_t b = sh.hit_bucket;
+            id_rank -= (uint32_t)sh.hit_mass_before;
+            id_prefix = (id_prefix << (level == 2 ? 8 : 12)) | (buckets - 1 - b);
+            __syncthreads();
+        }
+    } else {
+        // the single element with this key: find its id
+        if (tid == 0) sh.hit_bucket = kPaddingId;
+        __syncthreads();
+        for (uint32_t i = tid; i < vocab; i += kNucleusThreads) {
+            const float v = values[i];
+            if (!is_nonfinite(v) && float_key(v) == key && inside.holds(key, i)) sh.hit_bucket = i;
+        }
+        __syncthreads();
+        id_prefix = sh.hit_bucket;
+        __syncthreads();
+    }
+    *out_key = key;
+    *out_id = id_prefix;
+    *out_mass = before + (unsigned long long)need * each;
+    *out_rank = rank_before + need;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kNucleusThreads, 1) nucleus_select_kernel(const NucleusParams p) {
+    extern __shared__ __align__(16) unsigned char histogram_memory[];
+    __shared__ NucleusShared sh;
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    if (tid == 0) {
+        sh.mass = reinterpret_cast<unsigned long long *>(histogram_memory);
+        sh.count = reinterpret_cast<uint32_t *>(histogram_memory + kBuckets * sizeof(unsigned long long));
+    }
+    if (tid < 64) sh.table[tid] = exp2((double)tid / 64.0);
+    float *values = p.scratch + (size_t)blockIdx.x * p.scratch_stride;
+    __syncthreads();
+
+    for (uint32_t row = blockIdx.x; row < p.rows; row += gridDim.x) {
+        const SamplerConfig cfg = p.config_count > 1 ? p.configs[row] : p.config0;
+        if (cfg.temperature == 0.0f || cfg.top_k != 0) continue;  // the streaming kernel's rows
+
+        // ---- pass 1: HBM -> penalised fp32 row in scratch, maximum on the way ----
+        const T *columns = static_cast<const T *>(p.logits) + (size_t)row * p.row_stride;
+        const Repetition repetition = make_repetition(cfg.repetition_penalty);
+        const float flat_offset = penalty_offset(1u, cfg.presence_penalty, cfg.frequency_penalty);
+        float best = __uint_as_float(0xff800000u);
+        uint32_t finite = 0, bad_history = 0;
+        for (uint32_t split = 0; split < p.splits; split++) {
+            const uint32_t lo = split * p.split_len;
+            const uint32_t n = min(p.split_len, p.vocab - lo);
+            uint32_t flags = 0;
+            HistoryView history = make_history_view(nullptr, 0, 0, false);
+            if (p.history_meta != nullptr) {
+                const size_t unit = (size_t)row * p.splits + split;
+                const uint2 meta = reinterpret_cast<const uint2 *>(p.history_meta)[unit];
+                flags = meta.x;
+                if (meta.y) bad_history = meta.y;
+                history = make_history_view(
+                    const_cast<uint32_t *>(p.history_global) + unit * p.history_stride_words,
+                    p.bitmap_words, p.count_capacity, p.dense_wide != 0);
+            }
+            for (uint32_t c = tid; c < n; c += kNucleusThreads) {
+                float v;
+                if (sizeof(T) == 2) v = bf16_bits_to_float(reinterpret_cast<const uint16_t *>(columns)[lo + c]);
+                else v = reinterpret_cast<const float *>(columns)[lo + c];
+                if (flags & 1u) {
+                    const uint32_t word = history.bitmap[c >> 5];
+                    if ((word >> (c & 31u)) & 1u) {
+                        float offset = flat_offset;
+                        if (flags & 2u)
+                            offset = penalty_offset(history.count(c >> 5, word, c & 31u),
+                                                    cfg.presence_penalty, cfg.frequency_penalty);
+                        v = penalise_with_offset(v, offset, repetition);
+                    }
+                }
+                values[lo + c] = v;
+                if (!is_nonfinite(v)) {
+                    best = fmaxf(best, v);
+                    finite++;
+                }
+            }
+        }
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) {
+            best = fmaxf(best, __shfl_xor_sync(kFullMask, best, d));
+            finite += __shfl_xor_sync(kFullMask, finite, d);
+        }
+        if (lane == 0) {
+            sh.reduce_max[warp] = best;
+            sh.reduce_count[warp] = finite;
+        }
+        __syncthreads();  // also makes the scratch row visible to the whole CTA
+        best = sh.reduce_max[0];
+        finite = sh.reduce_count[0];
+        for (int w = 1; w < kNucleusThreads / 32; w++) {
+            best = fmaxf(best, sh.reduce_max[w]);
+            finite += sh.reduce_count[w];
+        }
+        __syncthreads();
+        if (bad_history || finite == 0) {
+            // src/output.c:610-612 / src/sampler.c:97 "sampler received no finite candidates"
+            if (tid == 0) {
+                report_row(p.out, row, bad_history ? bad_history : kErrFormat, kPaddingId, 0.0f);
+                if (p.out.dbg_count) p.out.dbg_count[row] = 0;
+            }
+            continue;
+        }
+
+        // ---- top-p on the un-tempered softmax: where does the mass reach top_p? ----
+        Nucleus all;
+        all.everything = true;
+        all.key = 0;
+        all.id = 0;
+        // total mass first (one pass), then the descent
+        unsigned long long partial = 0;
+        for (uint32_t i = tid; i < p.vocab; i += kNucleusThreads) {
+            const float v = values[i];
+            if (!is_nonfinite(v)) partial += exp_fixed((double)v - (double)best, sh.table);
+        }
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) partial += __shfl_xor_sync(kFullMask, partial, d);
+        if (lane == 0) sh.scan_mass[warp] = partial;
+        __syncthreads();
+        unsigned long long raw_sum = 0;
+        for (int w = 0; w < kNucleusThreads / 32; w++) raw_sum += sh.scan_mass[w];
+        __syncthreads();
+        // cumulative / sum >= top_p  <=>  cumulative >= top_p * sum
+        const double bound = (double)cfg.top_p * (double)raw_sum;
+        unsigned long long target = (unsigned long long)ceil(bound);
+        if (target > raw_sum) target = raw_sum;
+        Nucleus nucleus;
+        nucleus.everything = false;
+        unsigned long long mass_at_cut;
+        uint32_t size;
+        descend(sh, values, p.vocab, 1.0, (double)best, all, target, false, &nucleus.key, &nucleus.id,
+                &mass_at_cut, &size);
+
+        // ---- temperature weights of the nucleus, then the draw ----
+        const double inv_t = 1.0 / (double)cfg.temperature;
+        unsigned long long weight_sum = mass_at_cut;  // temperature 1: same weights
+        if (cfg.temperature != 1.0f) {
+            partial = 0;
+            for (uint32_t i = tid; i < p.vocab; i += kNucleusThreads) {
+                const float v = values[i];
+                if (is_nonfinite(v)) continue;
+                if (nucleus.holds(float_key(v), i))
+                    partial += exp_fixed(((double)v - (double)best) * inv_t, sh.table);
+            }
+#pragma unroll
+            for (int d = 16; d > 0; d >>= 1) partial += __shfl_xor_sync(kFullMask, partial, d);
+            if (lane == 0) sh.scan_mass[warp] = partial;
+            __syncthreads();
+            weight_sum = 0;
+            for (int w = 0; w < kNucleusThreads / 32; w++) weight_sum += sh.scan_mass[w];
+            __syncthreads();
+        }
+        float u = p.uniforms[row];
+        if (is_nonfinite(u) || u < 0.0f) u = 0.0f;
+        if (u >= 1.0f) u = __uint_as_float(0x3f7fffffu);
+        // first element whose cumulative weight exceeds draw = u * sum
+        const unsigned long long draw = (unsigned long long)floor((double)u * (double)weight_sum);
+        uint32_t picked_key, picked_id, picked_rank;
+        unsigned long long picked_mass;
+        descend(sh, values, p.vocab, inv_t, (double)best, nucleus, draw, true, &picked_key, &picked_id,
+                &picked_mass, &picked_rank);
+        if (tid == 0) {
+            if (weight_sum == 0 || raw_sum == 0 || picked_id >= p.vocab) {
+                report_row(p.out, row, kErrFormat, kPaddingId, 0.0f);
+            } else {
+                report_row(p.out, row, kOk, picked_id, values[picked_id]);
+            }
+            if (p.out.dbg_count) p.out.dbg_count[row] = size;  // nucleus size; the list itself is not dumped
+        }
+        __syncthreads();
+    }
+}
+
+}  // namespace fgk
+
+using namespace fgk;
+
+extern "C" int fgk_nucleus_prepare(void) {
+    cudaError_t e = cudaFuncSetAttribute(nucleus_select_kernel<float>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kNucleusDynamic);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(nucleus_select_kernel<uint16_t>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kNucleusDynamic);
+    return (int)e;
+}
+
+extern "C" int fgk_launch_nucleus_select(const fgk_nucleus_launch *l, void *stream) {
+    NucleusParams p;
+    p.logits = l->logits;
+    p.dtype = l->dtype;
+    p.rows = l->rows;
+    p.vocab = l->vocab;
+    p.row_stride = l->row_stride;
+    p.configs = reinterpret_cast<const SamplerConfig *>(l->configs_device);
+    p.config0.temperature = l->config0.temperature;
+    p.config0.top_p = l->config0.top_p;
+    p.config0.top_k = l->config0.top_k;
+    p.config0.presence_penalty = l->config0.presence_penalty;
+    p.config0.frequency_penalty = l->config0.frequency_penalty;
+    p.config0.repetition_penalty = l->config0.repetition_penalty;
+    p.config0.min_p = l->config0.min_p;
+    p.config0.pad_ = 0;
+    p.config0.seed = l->config0.seed;
+    p.config_count = l->config_count;
+    p.uniforms = l->uniforms;
+    p.scratch = l->scratch;
+    p.scratch_stride = l->scratch_stride;
+    p.history_global = l->history_global;
+    p.history_stride_words = l->history_stride_words;
+    p.history_meta = l->history_meta;
+    p.splits = l->splits;
+    p.split_len = l->split_len;
+    p.bitmap_words = l->bitmap_words;
+    p.count_capacity = l->count_capacity;
+    p.dense_wide = l->dense_wide;
+    p.out.tokens = l->out.tokens;
+    p.out.token_logits = l->out.token_logits;
+    p.out.row_status = l->out.row_status;
+    p.out.first_error = reinterpret_cast<unsigned long long *>(l->out.first_error);
+    p.out.dbg_count = l->out.dbg_count;
+    p.out.dbg_ids = l->out.dbg_ids;
+    p.out.dbg_scores = l->out.dbg_scores;
+    p.out.dbg_raw = l->out.dbg_raw;
+    p.out.dbg_tempered = l->out.dbg_tempered;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (l->dtype == 1u)
+        nucleus_select_kernel<uint16_t><<<l->ctas, kNucleusThreads, kNucleusDynamic, s>>>(p);
+    else
+        nucleus_select_kernel<float><<<l->ctas, kNucleusThreads, kNucleusDynamic, s>>>(p);
+    return (int)cudaGetLastError();
+}

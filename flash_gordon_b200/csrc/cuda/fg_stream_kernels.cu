@@ -293,36 +293,8 @@ __device__ __noinline__ float resolve_overflow(CandidateBuffer<kCandCap> &cand, 
     return tau;
 }
 
-// Shared-memory picture of the part of a row's history that falls into this split:
-//   bitmap   bit c set = column c occurs in the history            u32[bitmap_words]
-//   running  number of seen columns before each bitmap word        u16[bitmap_words]
-//   dense    occurrences of each seen column, in column order      u16 or u32[count_capacity]
-// (u32 counts only when a history may be longer than 65,535 tokens.)
-struct HistoryView {
-    uint32_t *bitmap;
-    uint16_t *running;
-    void *dense;
-    uint32_t capacity;
-    bool wide;
-
-    __device__ __forceinline__ uint32_t slot(uint32_t word_index, uint32_t word, uint32_t bit) const {
-        return min(running[word_index] + __popc(word & ((1u << bit) - 1u)), capacity - 1);
-    }
-    __device__ __forceinline__ uint32_t count(uint32_t word_index, uint32_t word, uint32_t bit) const {
-        const uint32_t at = slot(word_index, word, bit);
-        return wide ? static_cast<const uint32_t *>(dense)[at]
-                    : static_cast<const uint16_t *>(dense)[at];
-    }
-};
-
-__device__ __forceinline__ HistoryView history_view(const StreamParams &p, uint32_t *dyn_smem) {
-    HistoryView h;
-    h.bitmap = dyn_smem;
-    h.running = reinterpret_cast<uint16_t *>(dyn_smem + p.bitmap_words);
-    h.dense = dyn_smem + p.bitmap_words + (p.bitmap_words + 1) / 2;
-    h.capacity = p.count_capacity;
-    h.wide = p.dense_wide != 0;
-    return h;
+__device__ __forceinline__ HistoryView history_view(const StreamParams &p, uint32_t *memory) {
+    return make_history_view(memory, p.bitmap_words, p.count_capacity, p.dense_wide != 0);
 }
 
 // Flags build_history hands back.
@@ -1383,6 +1355,13 @@ extern "C" int fgk_launch_stream_select(const fgk_stream_launch *l, void *stream
         stream_select_kernel<uint16_t><<<grid, kThreads, dynamic, s>>>(p);
     else
         stream_select_kernel<float><<<grid, kThreads, dynamic, s>>>(p);
+    return (int)cudaGetLastError();
+}
+
+extern "C" int fgk_launch_history_build(const fgk_stream_launch *l, void *stream) {
+    const StreamParams p = to_stream_params(l);
+    const size_t dynamic = fgk_stream_dynamic_smem(l->bitmap_words, l->count_capacity, l->dense_wide);
+    history_build_kernel<<<dim3(l->splits, l->rows), kThreads, dynamic, static_cast<cudaStream_t>(stream)>>>(p);
     return (int)cudaGetLastError();
 }
 

@@ -95,6 +95,7 @@ fg_status fg_cuda_context_create(int device, fg_cuda_context **out, fg_error *er
     if (!e) e = fgk_device_sm_count(device, &sms);
     if (!e) e = fgk_stream_create(&c->own_stream);
     if (!e) e = fgk_stream_prepare();
+    if (!e) e = fgk_nucleus_prepare();
     if (!e) e = fgk_malloc((void **)&c->first_error, 256u);
     if (e) {
         fg_status status = fg_cuda_fail(err, e, "opening the CUDA context");
@@ -115,6 +116,7 @@ void fg_cuda_context_destroy(fg_cuda_context *c) {
         if (c->tickets) fgk_free(c->tickets);
         if (c->configs) fgk_free(c->configs);
         if (c->history) fgk_free(c->history);
+        if (c->nucleus) fgk_free(c->nucleus);
         if (c->first_error) fgk_free(c->first_error);
         if (c->staging) fgk_free(c->staging);
         if (c->pinned) fgk_host_free(c->pinned);
@@ -659,6 +661,83 @@ static fg_status run_stream(fg_cuda_context *c, const fg_cuda_sample_args *a,
     return e ? fg_cuda_fail(err, e, "streaming select kernel") : FG_OK;
 }
 
+/* Rows without a top-k cut: history pass (when there are penalties), then the
+ * persistent nucleus kernel, one scratch row per CTA. */
+static fg_status run_nucleus(fg_cuda_context *c, const fg_cuda_sample_args *a,
+                             const batch_traits *traits, fg_error *err) {
+    fg_cuda_context planner = *c;
+    planner.forced_splits = 1u; /* as few column ranges as the history structure's limits allow */
+    stream_plan plan;
+    if (!plan_stream(&planner, a->rows, a->vocab, a->history_max, traits->penalties, traits->counts, &plan)) {
+        fg_error_set(err, FG_ERR_LIMIT, "history structure does not fit shared memory");
+        return FG_ERR_LIMIT;
+    }
+    const uint32_t ctas = a->rows < c->sm_count ? a->rows : c->sm_count;
+    const size_t stride = (size_t)fg_align_up_u64(a->vocab, 64u);
+    fg_status status = fg_cuda_reserve(&c->nucleus, &c->nucleus_bytes, (size_t)ctas * stride * 4u, false, c, err);
+    const void *configs_device = NULL;
+    if (status == FG_OK) status = upload_configs(c, a, &configs_device, err);
+    if (status != FG_OK) return status;
+    const size_t slots = (size_t)a->rows * plan.splits;
+
+    fgk_nucleus_launch n;
+    memset(&n, 0, sizeof(n));
+    n.logits = a->logits;
+    n.dtype = a->dtype;
+    n.rows = a->rows;
+    n.vocab = a->vocab;
+    n.row_stride = a->row_stride;
+    n.configs_device = configs_device;
+    n.config0 = a->configs[0];
+    n.config_count = a->config_count;
+    n.uniforms = a->uniforms;
+    n.scratch = c->nucleus;
+    n.scratch_stride = stride;
+    n.ctas = ctas;
+    n.splits = plan.splits;
+    n.split_len = plan.split_len;
+    n.bitmap_words = plan.bitmap_words;
+    n.count_capacity = plan.count_capacity;
+    n.dense_wide = plan.dense_wide;
+    fill_output(&n.out, c, a);
+    c->last_scratch_bytes = (size_t)ctas * stride * 4u;
+    if (traits->penalties) {
+        const size_t stride_words = plan.dynamic_smem / 4u;
+        const size_t meta_at = (size_t)fg_align_up_u64(slots * stride_words * 4u, 256u);
+        status = fg_cuda_reserve(&c->history, &c->history_bytes, meta_at + slots * 8u, false, c, err);
+        if (status != FG_OK) return status;
+        fgk_stream_launch h;
+        memset(&h, 0, sizeof(h));
+        h.rows = a->rows;
+        h.vocab = a->vocab;
+        h.vocab_total = a->vocab;
+        h.splits = plan.splits;
+        h.split_len = plan.split_len;
+        h.history_tokens = a->history_tokens;
+        h.history_offsets = a->history_offsets;
+        h.history_max = a->history_max;
+        h.configs_device = configs_device;
+        h.config0 = a->configs[0];
+        h.config_count = a->config_count;
+        h.bitmap_words = plan.bitmap_words;
+        h.count_capacity = plan.count_capacity;
+        h.dense_wide = plan.dense_wide;
+        h.history_global = c->history;
+        h.history_stride_words = stride_words;
+        h.history_meta = (unsigned char *)c->history + meta_at;
+        const int e = fgk_launch_history_build(&h, c->stream);
+        c->launches++;
+        if (e) return fg_cuda_fail(err, e, "history kernel");
+        n.history_global = c->history;
+        n.history_stride_words = stride_words;
+        n.history_meta = h.history_meta;
+        c->last_scratch_bytes += meta_at + slots * 8u;
+    }
+    const int e = fgk_launch_nucleus_select(&n, c->stream);
+    c->launches++;
+    return e ? fg_cuda_fail(err, e, "nucleus kernel") : FG_OK;
+}
+
 static fg_status arm_first_error(fg_cuda_context *c, fg_error *err) {
     const int e = fgk_memset_async(c->first_error, 0xff, 8u, c->stream);
     return e ? fg_cuda_fail(err, e, "arming the error word") : FG_OK;
@@ -668,14 +747,11 @@ fg_status fg_cuda_sample_batch(fg_cuda_context *c, const fg_cuda_sample_args *a,
     batch_traits traits;
     fg_status status = check_batch(c, a, false, &traits, err);
     if (status != FG_OK) return status;
-    if (traits.nucleus) {
-        fg_error_set(err, FG_ERR_UNAVAILABLE, "sampling without a top-k cut is not built yet");
-        return FG_ERR_UNAVAILABLE;
-    }
     status = fg_cuda_enter(c, err);
     if (status == FG_OK) status = arm_first_error(c, err);
     if (status == FG_OK && traits.topk_rows)
         status = run_stream(c, a, &traits, 0u, a->vocab, 0u, NULL, NULL, err);
+    if (status == FG_OK && traits.nucleus) status = run_nucleus(c, a, &traits, err);
     if (status != FG_OK || (a->flags & FG_CUDA_SAMPLE_ASYNC)) return status;
     return collect_status(c, err);
 }

@@ -22,6 +22,8 @@ struct fg_cuda_context {
     size_t tickets_bytes;
     void *history;          /* ring path: history structures, one per (row, split) */
     size_t history_bytes;
+    void *nucleus;          /* one fp32 scratch row per persistent CTA of the nucleus kernel */
+    size_t nucleus_bytes;
     void *configs;          /* per-row configs when they differ */
     size_t configs_bytes;
     uint64_t *first_error;  /* one device word */
