@@ -25,7 +25,7 @@ namespace fgk {
 
 constexpr int kNucleusThreads = 1024;
 constexpr int kBuckets = 4096;
-constexpr size_t kNucleusDynamic = kBuckets * (sizeof(unsigned long long) + sizeof(uint32_t));
+constexpr size_t kNucleusHistogramBytes = kBuckets * (sizeof(unsigned long long) + sizeof(uint32_t));
 
 struct NucleusParams {
     const void *logits;
@@ -289,6 +289,225 @@ __device__ void descend(NucleusShared &sh, const float *values, uint32_t vocab, 
     *out_rank = rank_before + need;
 }
 
+// ---- the usual case: value buckets, then an exact look inside one bucket ----
+//
+// Buckets of equal width in the value itself, 1/256 wide and counted down from the
+// row's maximum (bucket 0 holds the largest values; everything 16 below the maximum,
+// where weights are below 2^-23, shares the last bucket).  Unlike the top bits of the
+// float key this spreads real logit rows over hundreds of buckets, which keeps the
+// shared-memory atomics apart.  One pass fills the histogram (this is where exp() is
+// paid), a prefix sum finds the bucket in which the target is reached, a second pass
+// gathers that bucket's members — a few hundred — and they are ordered exactly.
+
+constexpr uint32_t kListCap = 2048;
+
+struct NucleusList {
+    float value[kListCap];
+    uint32_t id[kListCap];
+    float sorted_value[kListCap];
+    uint32_t sorted_id[kListCap];
+    unsigned long long weight[kListCap];  // of the sorted entries, then their running sum
+    uint32_t count;
+};
+
+__device__ __forceinline__ uint32_t value_bucket(float v, float top) {
+    const double below = ((double)top - (double)v) * 256.0;  // exact, >= 0
+    return below >= (double)(kBuckets - 1) ? (uint32_t)(kBuckets - 1) : (uint32_t)below;
+}
+
+// Like find_crossing but walking the buckets upwards from 0; also leaves the sum of
+// all masses in sh.total_mass.  target_of(total) is evaluated once the total is known.
+// All threads call.  sh.hit_found == 0 means the total never reaches the target.
+template <typename TargetOf>
+__device__ unsigned long long find_crossing_up(NucleusShared &sh, TargetOf target_of, bool strict) {
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    constexpr uint32_t per = kBuckets / kNucleusThreads;
+    unsigned long long mine_mass = 0;
+    uint32_t mine_count = 0;
+#pragma unroll
+    for (uint32_t i = 0; i < per; i++) {
+        mine_mass += sh.mass[tid * per + i];
+        mine_count += sh.count[tid * per + i];
+    }
+    unsigned long long incl_mass = mine_mass;
+    uint32_t incl_count = mine_count;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const unsigned long long up_mass = __shfl_up_sync(kFullMask, incl_mass, d);
+        const uint32_t up_count = __shfl_up_sync(kFullMask, incl_count, d);
+        if (lane >= (uint32_t)d) {
+            incl_mass += up_mass;
+            incl_count += up_count;
+        }
+    }
+    if (lane == 31) {
+        sh.scan_mass[warp] = incl_mass;
+        sh.scan_count[warp] = incl_count;
+    }
+    if (tid == 0) sh.hit_found = 0;
+    __syncthreads();
+    unsigned long long prior_mass = incl_mass - mine_mass, total = 0;
+    uint32_t prior_count = incl_count - mine_count;
+    for (uint32_t w = 0; w < kNucleusThreads / 32; w++) {
+        if (w < warp) {
+            prior_mass += sh.scan_mass[w];
+            prior_count += sh.scan_count[w];
+        }
+        total += sh.scan_mass[w];
+    }
+    const unsigned long long target = target_of(total);
+    const unsigned long long after = prior_mass + mine_mass;
+    const bool was = strict ? prior_mass > target : prior_mass >= target;
+    const bool now = strict ? after > target : after >= target;
+    if (!was && now) {  // exactly one thread
+#pragma unroll
+        for (uint32_t i = 0; i < per; i++) {
+            const uint32_t b = tid * per + i;
+            const unsigned long long next = prior_mass + sh.mass[b];
+            if (strict ? next > target : next >= target) {
+                sh.hit_bucket = b;
+                sh.hit_mass_before = prior_mass;
+                sh.hit_count_before = prior_count;
+                sh.hit_found = 1;
+                break;
+            }
+            prior_mass = next;
+            prior_count += sh.count[b];
+        }
+    }
+    if (tid == 0) sh.total_mass = total;
+    __syncthreads();
+    return target;
+}
+
+struct Position {
+    uint32_t key, id;            // the element found
+    unsigned long long mass;     // cumulative weight up to and including it
+    uint32_t rank;               // its 1-based position in the order
+    unsigned long long total;    // weight of everything inside
+    bool ok;                     // false: fall back to the generic descent
+};
+
+// One phase: among the elements `inside`, weights exp((v - top) * inv_t), find the
+// first element of the (value descending, id ascending) order at which the running
+// weight reaches target_of(total) (strict: exceeds it); if it never does, the last
+// element inside.  All threads call.
+template <typename TargetOf>
+__device__ Position locate(NucleusShared &sh, NucleusList &list, const float *values, uint32_t vocab,
+                           double inv_t, float top, const Nucleus inside, TargetOf target_of,
+                           bool strict) {
+    const uint32_t tid = threadIdx.x;
+    Position found;
+    found.ok = false;
+    clear_histogram(sh, kBuckets);
+    for (uint32_t i = tid; i < vocab; i += kNucleusThreads) {
+        const float v = values[i];
+        if (is_nonfinite(v) || !inside.holds(float_key(v), i)) continue;
+        const unsigned long long w = exp_fixed(((double)v - (double)top) * inv_t, sh.table);
+        const uint32_t b = value_bucket(v, top);
+        atomicAdd(&sh.mass[b], w);
+        atomicAdd(&sh.count[b], 1u);
+    }
+    __syncthreads();
+    const unsigned long long target = find_crossing_up(sh, target_of, strict);
+    found.total = sh.total_mass;
+    bool clipped = false;
+    if (!sh.hit_found) {
+        // never reached (top_p = 1 or a draw rounded up to the total): the last element
+        // inside, i.e. the last member of the last non-empty bucket
+        clipped = true;
+        __syncthreads();
+        if (tid == 0) {
+            unsigned long long m = 0;
+            uint32_t c = 0, last = 0;
+            bool any = false;
+            for (uint32_t b = 0; b < kBuckets; b++) {
+                if (sh.count[b]) {
+                    if (any) {
+                        m += sh.mass[last];
+                        c += sh.count[last];
+                    }
+                    last = b;
+                    any = true;
+                }
+            }
+            sh.hit_bucket = last;
+            sh.hit_mass_before = m;
+            sh.hit_count_before = c;
+        }
+        __syncthreads();
+    }
+    const uint32_t bucket = sh.hit_bucket;
+    const unsigned long long before = sh.hit_mass_before;
+    const uint32_t rank_before = sh.hit_count_before;
+    const uint32_t members = sh.count[bucket];
+    __syncthreads();
+    if (members == 0 || members > kListCap) return found;  // crowded bucket (heavy ties): generic path
+
+    // gather the bucket's members
+    if (tid == 0) list.count = 0;
+    __syncthreads();
+    for (uint32_t i = tid; i < vocab; i += kNucleusThreads) {
+        const float v = values[i];
+        if (is_nonfinite(v) || !inside.holds(float_key(v), i)) continue;
+        if (value_bucket(v, top) != bucket) continue;
+        const uint32_t slot = atomicAdd(&list.count, 1u);
+        list.value[slot] = v;
+        list.id[slot] = i;
+    }
+    __syncthreads();
+    // order them: rank by counting, (value descending, id ascending); -0.0 and +0.0 tie
+    for (uint32_t a = tid; a < members; a += kNucleusThreads) {
+        const float v = list.value[a];
+        const uint32_t id = list.id[a];
+        uint32_t rank = 0;
+        for (uint32_t b = 0; b < members; b++) rank += precedes(list.value[b], list.id[b], v, id) ? 1u : 0u;
+        list.sorted_value[rank] = v;
+        list.sorted_id[rank] = id;
+        list.weight[rank] = exp_fixed(((double)v - (double)top) * inv_t, sh.table);
+    }
+    __syncthreads();
+    // running sum over at most 2048 entries: two per thread, then the usual scan
+    {
+        const uint32_t lane = tid & 31u, warp = tid >> 5;
+        const uint32_t a0 = 2 * tid, a1 = 2 * tid + 1;
+        const unsigned long long w0 = a0 < members ? list.weight[a0] : 0;
+        const unsigned long long w1 = a1 < members ? list.weight[a1] : 0;
+        unsigned long long incl = w0 + w1;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const unsigned long long up = __shfl_up_sync(kFullMask, incl, d);
+            if (lane >= (uint32_t)d) incl += up;
+        }
+        if (lane == 31) sh.scan_mass[warp] = incl;
+        __syncthreads();
+        unsigned long long prior = incl - (w0 + w1);
+        for (uint32_t w = 0; w < warp; w++) prior += sh.scan_mass[w];
+        if (a0 < members) list.weight[a0] = before + prior + w0;
+        if (a1 < members) list.weight[a1] = before + prior + w0 + w1;
+        if (tid == 0) sh.hit_bucket = kPaddingId;
+        __syncthreads();
+    }
+    // the first entry whose running sum reaches the target (exactly one thread sees the step)
+    for (uint32_t a = tid; a < members; a += kNucleusThreads) {
+        const unsigned long long here = list.weight[a];
+        const unsigned long long prev = a ? list.weight[a - 1] : before;
+        const bool was = strict ? prev > target : prev >= target;
+        const bool now = strict ? here > target : here >= target;
+        if (!clipped && !was && now) sh.hit_bucket = a;
+    }
+    __syncthreads();
+    uint32_t at = sh.hit_bucket;
+    if (clipped || at == kPaddingId) at = members - 1;
+    found.key = float_key(list.sorted_value[at]);
+    found.id = list.sorted_id[at];
+    found.mass = list.weight[at];
+    found.rank = rank_before + at + 1;
+    found.ok = true;
+    __syncthreads();
+    return found;
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kNucleusThreads, 1) nucleus_select_kernel(const NucleusParams p) {
     extern __shared__ __align__(16) unsigned char histogram_memory[];
@@ -300,6 +519,7 @@ __global__ void __launch_bounds__(kNucleusThreads, 1) nucleus_select_kernel(cons
     }
     if (tid < 64) sh.table[tid] = exp2((double)tid / 64.0);
     float *values = p.scratch + (size_t)blockIdx.x * p.scratch_stride;
+    NucleusList &list = *reinterpret_cast<NucleusList *>(histogram_memory + kNucleusHistogramBytes);
     __syncthreads();
 
     for (uint32_t row = blockIdx.x; row < p.rows; row += gridDim.x) {
@@ -378,35 +598,59 @@ __global__ void __launch_bounds__(kNucleusThreads, 1) nucleus_select_kernel(cons
         all.everything = true;
         all.key = 0;
         all.id = 0;
-        // total mass first (one pass), then the descent
-        unsigned long long partial = 0;
-        for (uint32_t i = tid; i < p.vocab; i += kNucleusThreads) {
-            const float v = values[i];
-            if (!is_nonfinite(v)) partial += exp_fixed((double)v - (double)best, sh.table);
-        }
-#pragma unroll
-        for (int d = 16; d > 0; d >>= 1) partial += __shfl_xor_sync(kFullMask, partial, d);
-        if (lane == 0) sh.scan_mass[warp] = partial;
-        __syncthreads();
-        unsigned long long raw_sum = 0;
-        for (int w = 0; w < kNucleusThreads / 32; w++) raw_sum += sh.scan_mass[w];
-        __syncthreads();
+        const double top_p = (double)cfg.top_p;
         // cumulative / sum >= top_p  <=>  cumulative >= top_p * sum
-        const double bound = (double)cfg.top_p * (double)raw_sum;
-        unsigned long long target = (unsigned long long)ceil(bound);
-        if (target > raw_sum) target = raw_sum;
+        auto mass_target = [top_p](unsigned long long total) {
+            const unsigned long long t = (unsigned long long)ceil(top_p * (double)total);
+            return t > total ? total : t;
+        };
         Nucleus nucleus;
         nucleus.everything = false;
-        unsigned long long mass_at_cut;
+        unsigned long long raw_sum, mass_at_cut;
         uint32_t size;
-        descend(sh, values, p.vocab, 1.0, (double)best, all, target, false, &nucleus.key, &nucleus.id,
-                &mass_at_cut, &size);
+        const Position cut = locate(sh, list, values, p.vocab, 1.0, best, all, mass_target, false);
+        if (cut.ok) {
+            nucleus.key = cut.key;
+            nucleus.id = cut.id;
+            raw_sum = cut.total;
+            mass_at_cut = cut.mass;
+            size = cut.rank;
+        } else {
+            // a bucket too crowded to order in shared memory: the generic radix descent
+            unsigned long long partial = 0;
+            for (uint32_t i = tid; i < p.vocab; i += kNucleusThreads) {
+                const float v = values[i];
+                if (!is_nonfinite(v)) partial += exp_fixed((double)v - (double)best, sh.table);
+            }
+#pragma unroll
+            for (int d = 16; d > 0; d >>= 1) partial += __shfl_xor_sync(kFullMask, partial, d);
+            if (lane == 0) sh.scan_mass[warp] = partial;
+            __syncthreads();
+            raw_sum = 0;
+            for (int w = 0; w < kNucleusThreads / 32; w++) raw_sum += sh.scan_mass[w];
+            __syncthreads();
+            descend(sh, values, p.vocab, 1.0, (double)best, all, mass_target(raw_sum), false, &nucleus.key,
+                    &nucleus.id, &mass_at_cut, &size);
+        }
 
         // ---- temperature weights of the nucleus, then the draw ----
         const double inv_t = 1.0 / (double)cfg.temperature;
-        unsigned long long weight_sum = mass_at_cut;  // temperature 1: same weights
-        if (cfg.temperature != 1.0f) {
-            partial = 0;
+        float u = p.uniforms[row];
+        if (is_nonfinite(u) || u < 0.0f) u = 0.0f;
+        if (u >= 1.0f) u = __uint_as_float(0x3f7fffffu);
+        const double draw_at = (double)u;
+        // first element whose cumulative weight exceeds draw = u * sum
+        auto draw_target = [draw_at](unsigned long long total) {
+            return (unsigned long long)floor(draw_at * (double)total);
+        };
+        uint32_t picked_id;
+        unsigned long long weight_sum;
+        const Position pick = locate(sh, list, values, p.vocab, inv_t, best, nucleus, draw_target, true);
+        if (pick.ok) {
+            picked_id = pick.id;
+            weight_sum = pick.total;
+        } else {
+            unsigned long long partial = 0;
             for (uint32_t i = tid; i < p.vocab; i += kNucleusThreads) {
                 const float v = values[i];
                 if (is_nonfinite(v)) continue;
@@ -420,16 +664,11 @@ __global__ void __launch_bounds__(kNucleusThreads, 1) nucleus_select_kernel(cons
             weight_sum = 0;
             for (int w = 0; w < kNucleusThreads / 32; w++) weight_sum += sh.scan_mass[w];
             __syncthreads();
+            uint32_t picked_key, picked_rank;
+            unsigned long long picked_mass;
+            descend(sh, values, p.vocab, inv_t, (double)best, nucleus, draw_target(weight_sum), true,
+                    &picked_key, &picked_id, &picked_mass, &picked_rank);
         }
-        float u = p.uniforms[row];
-        if (is_nonfinite(u) || u < 0.0f) u = 0.0f;
-        if (u >= 1.0f) u = __uint_as_float(0x3f7fffffu);
-        // first element whose cumulative weight exceeds draw = u * sum
-        const unsigned long long draw = (unsigned long long)floor((double)u * (double)weight_sum);
-        uint32_t picked_key, picked_id, picked_rank;
-        unsigned long long picked_mass;
-        descend(sh, values, p.vocab, inv_t, (double)best, nucleus, draw, true, &picked_key, &picked_id,
-                &picked_mass, &picked_rank);
         if (tid == 0) {
             if (weight_sum == 0 || raw_sum == 0 || picked_id >= p.vocab) {
                 report_row(p.out, row, kErrFormat, kPaddingId, 0.0f);
@@ -445,6 +684,8 @@ __global__ void __launch_bounds__(kNucleusThreads, 1) nucleus_select_kernel(cons
 }  // namespace fgk
 
 using namespace fgk;
+
+static constexpr size_t kNucleusDynamic = kNucleusHistogramBytes + sizeof(NucleusList);
 
 extern "C" int fgk_nucleus_prepare(void) {
     cudaError_t e = cudaFuncSetAttribute(nucleus_select_kernel<float>,

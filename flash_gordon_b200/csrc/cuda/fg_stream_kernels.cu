@@ -334,13 +334,24 @@ __device__ __noinline__ uint32_t build_history(const StreamParams &p, StreamShar
     for (uint32_t w = tid; w < words; w += kThreads) bitmap[w] = 0;
     __syncthreads();
     const uint32_t first_global = p.vocab_offset + lo;
-    for (uint32_t i = tid; i < history_len; i += kThreads) {
-        const uint32_t token = history[i];
-        if (token >= p.vocab_total) sh.bad_history = kErrFormat;
-        const uint32_t local = token - first_global;  // wraps for ids below the split
-        if (local < n) {
-            const uint32_t bit = 1u << (local & 31u);
-            if ((bitmap[local >> 5] & bit) == 0) atomicOr(&bitmap[local >> 5], bit);
+    // four tokens per thread and trip, loaded before any is used: the loop is a chain of
+    // global-load latencies otherwise
+    for (uint32_t base = 0; base < history_len; base += 4 * kThreads) {
+        uint32_t token[4];
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+            const uint32_t i = base + q * kThreads + tid;
+            token[q] = i < history_len ? history[i] : 0u;
+        }
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+            if (base + q * kThreads + tid >= history_len) continue;
+            if (token[q] >= p.vocab_total) sh.bad_history = kErrFormat;
+            const uint32_t local = token[q] - first_global;  // wraps for ids below the split
+            if (local < n) {
+                const uint32_t bit = 1u << (local & 31u);
+                if ((bitmap[local >> 5] & bit) == 0) atomicOr(&bitmap[local >> 5], bit);
+            }
         }
     }
     __syncthreads();
@@ -373,14 +384,23 @@ __device__ __noinline__ uint32_t build_history(const StreamParams &p, StreamShar
     const uint32_t dense_word_count = view.wide ? distinct : (distinct + 1) / 2;
     for (uint32_t i = tid; i < dense_word_count; i += kThreads) dense_words[i] = 0;
     __syncthreads();
-    for (uint32_t i = tid; i < history_len; i += kThreads) {
-        const uint32_t local = history[i] - first_global;
-        if (local < n) {
-            const uint32_t at = view.slot(local >> 5, bitmap[local >> 5], local & 31u);
-            // 16-bit counts share a word: add into the right half (a half cannot carry,
-            // a history that could overflow it uses 32-bit counts)
-            if (view.wide) atomicAdd(&dense_words[at], 1u);
-            else atomicAdd(&dense_words[at >> 1], 1u << (16u * (at & 1u)));
+    for (uint32_t base = 0; base < history_len; base += 4 * kThreads) {
+        uint32_t token[4];
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+            const uint32_t i = base + q * kThreads + tid;
+            token[q] = i < history_len ? history[i] : 0u;
+        }
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+            const uint32_t local = token[q] - first_global;
+            if (base + q * kThreads + tid < history_len && local < n) {
+                const uint32_t at = view.slot(local >> 5, bitmap[local >> 5], local & 31u);
+                // 16-bit counts share a word: add into the right half (a half cannot carry,
+                // a history that could overflow it uses 32-bit counts)
+                if (view.wide) atomicAdd(&dense_words[at], 1u);
+                else atomicAdd(&dense_words[at >> 1], 1u << (16u * (at & 1u)));
+            }
         }
     }
     __syncthreads();
