@@ -25,7 +25,7 @@ OBJ_DIR = PKG / "build"
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 CC = os.environ.get("CC", "gcc")
 
-CUDA_SOURCES = ["fg_stream_kernels.cu", "fg_nucleus_kernel.cu", "fg_ops_kernels.cu", "fg_runtime.cu"]
+CUDA_SOURCES = ["fg_stream_kernels.cu", "fg_persistent_kernel.cu", "fg_nucleus_kernel.cu", "fg_ops_kernels.cu", "fg_runtime.cu"]
 HOST_SOURCES = ["fg_util.c", "fg_sampler_host.c", "fg_cuda_api.c"]
 
 # sm_100a only; -fmad=false so no fp32/fp64 multiply-add is contracted anywhere

@@ -42,10 +42,17 @@ struct FinishBuffer {
     uint32_t status;
 };
 
+// How the threads that share a candidate list meet: the whole CTA by default; a
+// kernel whose CTA also holds warps with another job passes a named barrier instead.
+struct WholeBlock {
+    static __device__ __forceinline__ void sync() { __syncthreads(); }
+};
+
 // Keeps the k best of buf[0..n) (n <= CAP) at buf[0..k) in unspecified order,
 // sets buf.tau_* to the k-th best and returns the new count.  All THREADS
-// threads of the CTA must call it with the same n and k.  n <= k is a no-op.
-template <int THREADS, int CAP>
+// threads that meet at Bar (numbered 0 .. THREADS-1 by threadIdx.x) must call it
+// with the same n and k.  n <= k is a no-op.
+template <int THREADS, int CAP, class Bar = WholeBlock>
 __device__ uint32_t compact_topk(CandidateBuffer<CAP> &buf, uint32_t n, uint32_t k) {
     static_assert(CAP % THREADS == 0, "buffer is a whole number of entries per thread");
     constexpr int PER = CAP / THREADS;
@@ -71,13 +78,13 @@ __device__ uint32_t compact_topk(CandidateBuffer<CAP> &buf, uint32_t n, uint32_t
     int shift = 56;
     for (int pass = 0; pass < 8; pass++) {
         if (tid < 256) buf.hist[tid] = 0;
-        __syncthreads();
+        Bar::sync();
 #pragma unroll
         for (int j = 0; j < PER; j++) {
             if (key[j] != 0 && (pass == 0 || (key[j] >> (shift + 8)) == prefix))
                 atomicAdd(&buf.hist[(key[j] >> shift) & 255u], 1u);
         }
-        __syncthreads();
+        Bar::sync();
         if (tid < 32) {
             // lane l owns digits 255-8l .. 248-8l, walked from the top
             uint32_t mine = 0;
@@ -106,7 +113,7 @@ __device__ uint32_t compact_topk(CandidateBuffer<CAP> &buf, uint32_t n, uint32_t
                 }
             }
         }
-        __syncthreads();
+        Bar::sync();
         prefix = (prefix << 8) | buf.sel_digit;
         need = buf.sel_need;
         bucket = buf.sel_bucket;
@@ -118,7 +125,7 @@ __device__ uint32_t compact_topk(CandidateBuffer<CAP> &buf, uint32_t n, uint32_t
         buf.eq_count = 0;
         buf.min_key = ~0ull;
     }
-    __syncthreads();
+    Bar::sync();
 #pragma unroll
     for (int j = 0; j < PER; j++) {
         if (key[j] == 0) continue;
@@ -132,19 +139,19 @@ __device__ uint32_t compact_topk(CandidateBuffer<CAP> &buf, uint32_t n, uint32_t
             atomicMin(&buf.min_key, (unsigned long long)key[j]);
         }
     }
-    __syncthreads();
+    Bar::sync();
     if (tid == 0) {
         buf.tau_score = key_to_float((uint32_t)(buf.min_key >> 32));
         buf.tau_id = ~(uint32_t)(buf.min_key & 0xffffffffull);
         buf.count = buf.out_count;
     }
-    __syncthreads();
+    Bar::sync();
     return buf.out_count;
 }
 
 // buf[0..n), n <= 64, into fin.score/id in sampling order.  Entries that compare
 // equal on (score, id) keep their buffer order.  All threads call; ends synced.
-template <int CAP>
+template <int CAP, class Bar = WholeBlock>
 __device__ void sort_candidates(const CandidateBuffer<CAP> &buf, FinishBuffer &fin, uint32_t n) {
     const uint32_t tid = threadIdx.x;
     if (tid < n) {
@@ -159,7 +166,7 @@ __device__ void sort_candidates(const CandidateBuffer<CAP> &buf, FinishBuffer &f
         fin.score[rank] = s;
         fin.id[rank] = id;
     }
-    __syncthreads();
+    Bar::sync();
 }
 
 struct SelectOutput {

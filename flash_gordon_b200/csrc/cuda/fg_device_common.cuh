@@ -177,6 +177,29 @@ __device__ __forceinline__ void bulk_copy_to_shared(void *shared_destination, co
         : "memory");
 }
 
+// a consumer's arrival: "this stage may be overwritten"
+__device__ __forceinline__ void mbarrier_arrive(uint64_t *barrier) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(shared_address(barrier)) : "memory");
+}
+
+// L2 policy for bytes that are read exactly once: first in line for eviction, so
+// that they do not push out what is read again (token histories, scratch rows).
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+    uint64_t policy;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+    return policy;
+}
+
+__device__ __forceinline__ void bulk_copy_to_shared_hinted(void *shared_destination,
+                                                           const void *global_source, uint32_t bytes,
+                                                           uint64_t *barrier, uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, "
+        "[%3], %4;" ::"r"(shared_address(shared_destination)),
+        "l"(global_source), "r"(bytes), "r"(shared_address(barrier)), "l"(policy)
+        : "memory");
+}
+
 // The POD the kernels read; layout of fg_sampler_config (include/fg_sampler.h).
 struct SamplerConfig {
     float temperature;

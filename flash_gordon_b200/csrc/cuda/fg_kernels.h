@@ -79,7 +79,7 @@ typedef struct fgk_stream_launch {
     uint32_t bitmap_words;
     uint32_t count_capacity;
     uint32_t dense_wide;
-    /* ring path only: global home of the per-(row, split) history structures */
+    /* history pass only: global home of the per-(row, split) history structures */
     uint32_t *history_global;
     uint64_t history_stride_words;
     void *history_meta; /* 8 bytes per (row, split); NULL when the batch has no history */
@@ -93,9 +93,17 @@ uint64_t fgk_stream_part_meta_bytes(void);
 uint64_t fgk_stream_dynamic_smem(uint32_t bitmap_words, uint32_t count_capacity, uint32_t dense_wide);
 int fgk_stream_prepare(void);
 int fgk_launch_stream_select(const fgk_stream_launch *launch, void *stream);
-/* rows through a shared-memory ring filled by bulk copies; needs 16-byte aligned rows */
-uint64_t fgk_ring_dynamic_smem(uint32_t dtype);
-int fgk_launch_ring_select(const fgk_stream_launch *launch, void *stream, uint32_t *launched);
+
+/* ---- persistent ring kernel (fg_persistent_kernel.cu) ----
+ * Takes a fgk_stream_launch with splits == 1, rows and row stride multiples of 16 bytes,
+ * and only rows whose penalties cannot raise a logit.  Of the history fields it uses
+ * bitmap_words alone (the bitmap lives behind the ring in dynamic shared memory). */
+#define FGK_PERSIST_MAX_DYNAMIC_SMEM (200 * 1024)
+uint64_t fgk_persistent_dynamic_smem(uint32_t bitmap_words);
+/* CTAs of the kernel one SM holds at this much dynamic shared memory (0 on error) */
+uint32_t fgk_persistent_ctas_per_sm(uint32_t dtype, uint64_t dynamic_smem);
+int fgk_persistent_prepare(void);
+int fgk_launch_persistent_select(const fgk_stream_launch *launch, uint32_t ctas, void *stream);
 
 typedef struct fgk_merge_launch {
     const float *scores;
@@ -139,7 +147,7 @@ typedef struct fgk_nucleus_launch {
 
 int fgk_nucleus_prepare(void);
 int fgk_launch_nucleus_select(const fgk_nucleus_launch *launch, void *stream);
-/* the history pass of the ring path on its own (fills history_global / history_meta) */
+/* the history pass (fills history_global / history_meta) */
 int fgk_launch_history_build(const fgk_stream_launch *launch, void *stream);
 
 /* ---- device operators (fg_ops_kernels.cu) ---- */

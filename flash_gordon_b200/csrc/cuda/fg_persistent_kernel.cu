@@ -1,0 +1,802 @@
+// Persistent sampling kernel for sm_100a: rows stream through a shared-memory ring
+// that a warp of its own keeps full.
+//
+// One CTA = eight consumer warps + one copy warp, FGK_PERSIST_CTAS of them per SM,
+// each working through rows  blockIdx.x, blockIdx.x + gridDim.x, ...
+//
+//   copy warp   one lane asks the copy engine (cp.async.bulk + mbarrier) for 16 KB
+//               tiles, row after row, as fast as ring stages come free.  It never
+//               waits for anything but a free stage, so bytes stay in flight while the
+//               consumers build a history bitmap, cut a candidate list or finish a row
+//               -- the next row's first tiles are already there when they come back.
+//   consumers   per row: (1) bitmap of the ids in the row's token history, in shared
+//               memory; (2) tile 0 gives a first admission bound; (3) every further
+//               tile costs a 128-bit shared load, three maxima and one compare per
+//               vector -- single elements are looked at only above the bound;
+//               (4) the select step of src/sampler.c:80-122 on the k survivors.
+//
+// The kernel takes rows whose penalties can only lower a logit (presence >= 0,
+// frequency >= 0, repetition >= 1, or no penalties / no history at all).  Then a raw
+// value at or below the bound stays there, so the history matters only for the few
+// values above it.  An id that was seen is charged  frequency * count + presence
+// (src/sampler.c:52-58); the count is not tabulated per row (src/output.c:601-617
+// keeps a vocabulary-wide table per session): when the penalty for count = 1 -- an
+// upper bound of the penalised value -- still beats the bound, the id is put aside and
+// its occurrences are counted in the token list when the list is next cut.  Everything
+// else (penalties that can raise a logit, rows that are not 16-byte aligned, column
+// splits) stays with stream_select_kernel.
+#include <cstring>
+
+#include "fg_block_select.cuh"
+#include "fg_kernels.h"
+
+namespace fgk {
+namespace persist {
+
+#ifndef FGK_PERSIST_STAGES
+#define FGK_PERSIST_STAGES 4
+#endif
+#ifndef FGK_PERSIST_CTAS
+#define FGK_PERSIST_CTAS 2
+#endif
+
+constexpr int kStages = FGK_PERSIST_STAGES;
+constexpr int kConsumers = 256;
+constexpr int kConsumerWarps = kConsumers / 32;
+constexpr int kBlock = kConsumers + 32;  // + the copy warp
+constexpr uint32_t kStageBytes = 16384;
+constexpr int kVectors = 4;              // 128-bit vectors per consumer thread and tile
+constexpr int kCandCap = 1024;
+constexpr int kDeferCap = 256;           // ids put aside until their occurrences are counted
+constexpr uint32_t kWaitPolls = 1u << 22;
+
+// The eight consumer warps meet at named barrier 1; the copy warp never does.
+struct ConsumerBarrier {
+    static __device__ __forceinline__ void sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+    static __device__ __forceinline__ bool sync_or(bool mine) {
+        uint32_t any;
+        asm volatile(
+            "{\n\t.reg .pred in, out;\n\t"
+            "setp.ne.u32 in, %1, 0;\n\t"
+            "bar.red.or.pred out, 1, 256, in;\n\t"
+            "selp.u32 %0, 1, 0, out;\n\t}"
+            : "=r"(any)
+            : "r"((uint32_t)mine)
+            : "memory");
+        return any != 0;
+    }
+};
+using CB = ConsumerBarrier;
+
+template <typename T>
+struct Lanes;
+template <>
+struct Lanes<float> {
+    static constexpr int kPer = 4;  // logits per 128-bit vector
+    static __device__ __forceinline__ void unpack(const uint4 &raw, float *v) {
+        v[0] = __uint_as_float(raw.x);
+        v[1] = __uint_as_float(raw.y);
+        v[2] = __uint_as_float(raw.z);
+        v[3] = __uint_as_float(raw.w);
+    }
+};
+template <>
+struct Lanes<uint16_t> {  // bf16 bit patterns
+    static constexpr int kPer = 8;
+    static __device__ __forceinline__ void unpack(const uint4 &raw, float *v) {
+        v[0] = __uint_as_float(raw.x << 16);
+        v[1] = __uint_as_float(raw.x & 0xffff0000u);
+        v[2] = __uint_as_float(raw.y << 16);
+        v[3] = __uint_as_float(raw.y & 0xffff0000u);
+        v[4] = __uint_as_float(raw.z << 16);
+        v[5] = __uint_as_float(raw.z & 0xffff0000u);
+        v[6] = __uint_as_float(raw.w << 16);
+        v[7] = __uint_as_float(raw.w & 0xffff0000u);
+    }
+};
+
+struct Params {
+    const void *logits;
+    uint64_t row_stride;  // elements
+    uint32_t rows, vocab;
+    uint32_t vocab_offset, vocab_total;
+    const uint32_t *history_tokens;
+    const uint64_t *history_offsets;
+    uint32_t history_max;
+    uint32_t bitmap_words;          // 0: the batch has no history
+    const SamplerConfig *configs;   // device copy when config_count > 1
+    SamplerConfig config0;
+    uint32_t config_count;
+    uint32_t shard_k;               // != 0: write candidates instead of sampling
+    const float *uniforms;
+    float *shard_scores;
+    uint32_t *shard_ids;
+    SelectOutput out;
+};
+
+struct Shared {
+    CandidateBuffer<kCandCap> cand;
+    FinishBuffer fin;
+    float defer_raw[kDeferCap];      // raw logit of an id put aside
+    uint32_t defer_id[kDeferCap];
+    uint32_t defer_seen[kDeferCap];  // its occurrences in the history, once counted
+    alignas(8) uint64_t full[kStages];   // "the tile has landed"
+    alignas(8) uint64_t empty[kStages];  // "the consumers are done with the stage"
+    unsigned long long wild_key;     // greedy rows: min over NaN/Inf of (id << 32 | value bits)
+    uint32_t defer_count;
+    uint32_t bad_history;
+    uint32_t overflow;               // a value found no slot in one of the lists
+    uint32_t ring_error;             // a bounded wait ran out
+    uint32_t first_key;              // tile 0: the smallest of the warps' j-th largest keys
+};
+
+// What the consumers need to know about the row; lives in registers.
+struct Row {
+    const uint32_t *tokens;  // the row's history
+    uint32_t history_len;
+    uint32_t id_base;        // global id of column 0
+    uint32_t k, cut_at;
+    float flat_offset;       // charge for count = 1 (the exact charge when frequency is +-0)
+    float presence, frequency;
+    Repetition repetition;
+    bool greedy, seen_any, with_counts;
+};
+
+__device__ __forceinline__ bool bounded_wait(uint64_t *barrier, uint32_t parity) {
+    for (uint32_t polls = 0; polls < kWaitPolls; polls++)
+        if (mbarrier_try_wait(barrier, parity)) return true;
+    return false;
+}
+
+// One element that the vector test could not rule out.  kPair compares with the
+// bound as a (score, id) pair -- always right once a cut has produced the pair --
+// otherwise only the score is compared: strictly for tiles after the one(s) the
+// bound came from (their ids are larger, a tie loses), inclusively for tile 0.
+// Returns true when a list wants a cut.
+template <bool kGreedy, bool kPair>
+__device__ __forceinline__ bool consider(Shared &sh, const Row &r, float x, uint32_t id, bool seen,
+                                         float tau, uint32_t tau_id, bool inclusive) {
+    if (seen) {
+        const float bound = penalise_with_offset(x, r.flat_offset, r.repetition);
+        if (r.with_counts) {
+            // the charge grows with the count, so `bound` is the most the id can keep
+            const bool alive = (kPair || inclusive) ? bound >= tau : bound > tau;
+            // greedy rows must also see NaN/Inf, raw or made by the penalty
+            const bool wild = kGreedy && (__float_as_uint(x) & 0x7fffffffu) >= 0x6b000000u;
+            if (!(alive || wild)) return false;
+            const uint32_t slot = atomicAdd(&sh.defer_count, 1u);
+            if (slot < (uint32_t)kDeferCap) {
+                sh.defer_raw[slot] = x;
+                sh.defer_id[slot] = id;
+            } else {
+                sh.overflow = 1;
+            }
+            return slot >= (uint32_t)kDeferCap / 2;
+        }
+        x = bound;
+    }
+    if (is_nonfinite(x)) {
+        if (kGreedy) atomicMin(&sh.wild_key, ((unsigned long long)id << 32) | __float_as_uint(x));
+        return false;
+    }
+    const bool take = kPair ? precedes(x, id, tau, tau_id) : (inclusive ? x >= tau : x > tau);
+    if (!take) return false;
+    const uint32_t slot = atomicAdd(&sh.cand.count, 1u);
+    if (slot < (uint32_t)kCandCap) {
+        sh.cand.score[slot] = x;
+        sh.cand.id[slot] = id;
+    } else {
+        sh.overflow = 1;
+    }
+    return slot >= r.cut_at;
+}
+
+// The lists want attention.  Ids that were put aside get their occurrences counted in
+// the row's token list and their exact penalised value, and join the candidates if they
+// precede the bound; then the candidate list is cut back to its k best, which lifts the
+// bound.  Every consumer calls it; returns the new bound's score (the pair is in
+// sh.cand.tau_*).
+__device__ __noinline__ float attend(Shared &sh, const Row r) {
+    const uint32_t tid = threadIdx.x, lane = tid & 31u;
+    CB::sync();
+    const uint32_t aside = min(sh.defer_count, (uint32_t)kDeferCap);
+    uint32_t held = min(sh.cand.count, (uint32_t)kCandCap);
+    CB::sync();  // everyone has read the counts before anything rewrites them
+    if (aside != 0) {
+        if (held + aside > (uint32_t)kCandCap) {  // make room first
+            compact_topk<kConsumers, kCandCap, CB>(sh.cand, held, r.k);
+            held = min(held, r.k);
+        }
+        if (tid < aside) sh.defer_seen[tid] = 0;
+        CB::sync();
+        constexpr int kBatch = 8;
+        for (uint32_t base = 0; base < r.history_len; base += kBatch * kConsumers) {
+            uint32_t token[kBatch];
+#pragma unroll
+            for (int q = 0; q < kBatch; q++) {
+                const uint32_t i = base + q * kConsumers + tid;
+                token[q] = i < r.history_len ? r.tokens[i] : kPaddingId;  // the padding id is nobody's
+            }
+            for (uint32_t d = 0; d < aside; d++) {
+                const uint32_t id = sh.defer_id[d];
+                uint32_t hits = 0;
+#pragma unroll
+                for (int q = 0; q < kBatch; q++) hits += token[q] == id ? 1u : 0u;
+                hits = __reduce_add_sync(kFullMask, hits);
+                if (lane == 0 && hits != 0) atomicAdd(&sh.defer_seen[d], hits);
+            }
+        }
+        CB::sync();
+        const float tau = sh.cand.tau_score;
+        const uint32_t tau_id = sh.cand.tau_id;
+        if (tid < aside) {
+            const uint32_t id = sh.defer_id[tid];
+            const float x = penalise_with_offset(
+                sh.defer_raw[tid], penalty_offset(sh.defer_seen[tid], r.presence, r.frequency),
+                r.repetition);
+            if (is_nonfinite(x)) {
+                if (r.greedy)
+                    atomicMin(&sh.wild_key, ((unsigned long long)id << 32) | __float_as_uint(x));
+            } else if (precedes(x, id, tau, tau_id)) {
+                const uint32_t slot = atomicAdd(&sh.cand.count, 1u);  // room was made above
+                sh.cand.score[slot] = x;
+                sh.cand.id[slot] = id;
+            }
+        }
+        CB::sync();
+        if (tid == 0) sh.defer_count = 0;
+        held = min(sh.cand.count, (uint32_t)kCandCap);
+        CB::sync();
+    }
+    compact_topk<kConsumers, kCandCap, CB>(sh.cand, held, r.k);
+    return sh.cand.tau_score;
+}
+
+// Bits of the row's bitmap that belong to vector `g` of the tile starting at bitmap
+// word `tile_word` (tiles start on a word boundary, vectors never straddle one).
+template <typename T>
+__device__ __forceinline__ uint32_t seen_bits(const uint32_t *bitmap, uint32_t tile_word, uint32_t g) {
+    constexpr int kPer = Lanes<T>::kPer;
+    const uint32_t column = g * kPer;
+    return (bitmap[tile_word + (column >> 5)] >> (column & 31u)) & ((1u << kPer) - 1u);
+}
+
+// A tile pushed more values than a list could take (sorted or constant rows do that,
+// or a row whose first tile gave no bound).  Take back what the tile stored, then feed
+// it again from the ring one element per thread at a time with a cut before each, so
+// that no list can overflow: k + 256 <= kCandCap, 256 <= kDeferCap.  The bound may now
+// come from this very tile, so everything is compared as a pair.  Every consumer calls
+// it; returns the new bound.
+template <typename T>
+__device__ __noinline__ float redo_tile(Shared &sh, const uint32_t *bitmap, const uint4 *stage,
+                                        uint32_t t, uint32_t valid_vectors, const Row r) {
+    using L = Lanes<T>;
+    constexpr int kPer = L::kPer;
+    constexpr uint32_t kTile = kStageBytes / sizeof(T);
+    static_assert(kMaxK + kConsumers <= kCandCap && kConsumers <= kDeferCap, "a slice always fits");
+    constexpr int PER = kCandCap / kConsumers;
+    const uint32_t tid = threadIdx.x;
+    const uint32_t first_id = r.id_base + t * kTile;
+
+    CB::sync();
+    const uint32_t held = min(sh.cand.count, (uint32_t)kCandCap);
+    const uint32_t aside = min(sh.defer_count, (uint32_t)kDeferCap);
+    float score[PER];
+    uint32_t id[PER];
+#pragma unroll
+    for (int j = 0; j < PER; j++) {
+        const uint32_t at = j * kConsumers + tid;
+        id[j] = kPaddingId;
+        score[j] = 0.0f;
+        if (at < held) {
+            score[j] = sh.cand.score[at];
+            id[j] = sh.cand.id[at];
+        }
+    }
+    float aside_raw = 0.0f;
+    uint32_t aside_id = kPaddingId;
+    if (tid < aside) {
+        aside_raw = sh.defer_raw[tid];
+        aside_id = sh.defer_id[tid];
+    }
+    CB::sync();
+    if (tid == 0) {
+        sh.cand.count = 0;
+        sh.defer_count = 0;
+        sh.overflow = 0;
+    }
+    CB::sync();
+#pragma unroll
+    for (int j = 0; j < PER; j++) {
+        if (id[j] != kPaddingId && id[j] - first_id >= kTile) {  // not from this tile
+            const uint32_t slot = atomicAdd(&sh.cand.count, 1u);
+            sh.cand.score[slot] = score[j];
+            sh.cand.id[slot] = id[j];
+        }
+    }
+    if (aside_id != kPaddingId && aside_id - first_id >= kTile) {
+        const uint32_t slot = atomicAdd(&sh.defer_count, 1u);
+        sh.defer_raw[slot] = aside_raw;
+        sh.defer_id[slot] = aside_id;
+    }
+    const uint32_t tile_word = t * (kTile / 32);
+    for (int u = 0; u < kVectors; u++) {
+        const uint32_t g = u * kConsumers + tid;
+        float v[kPer];
+        uint32_t bits = 0;
+        const bool live = g < valid_vectors;
+        if (live) {
+            L::unpack(stage[g], v);
+            if (r.seen_any) bits = seen_bits<T>(bitmap, tile_word, g);
+        }
+#pragma unroll
+        for (int j = 0; j < kPer; j++) {
+            const float tau = attend(sh, r);
+            const uint32_t tau_id = sh.cand.tau_id;
+            if (live) {
+                const uint32_t element_id = first_id + g * kPer + j;
+                if (r.greedy) consider<true, true>(sh, r, v[j], element_id, (bits >> j) & 1u, tau, tau_id, true);
+                else consider<false, true>(sh, r, v[j], element_id, (bits >> j) & 1u, tau, tau_id, true);
+            }
+        }
+    }
+    return attend(sh, r);
+}
+
+// Position in the ring; the copy warp and the consumers count tiles the same way.
+struct RingCursor {
+    uint32_t stage = 0, use = 0;  // `use` counts how often the ring has wrapped
+    __device__ __forceinline__ void advance() {
+        if (++stage == (uint32_t)kStages) {
+            stage = 0;
+            use++;
+        }
+    }
+};
+
+constexpr uint32_t kNeedsAttention = 0x80000000u;
+
+// Tile 0 of a row: every element is looked at.  The first bound is the smallest, over
+// the eight warps, of each warp's j-th largest per-thread maximum of unseen finite
+// values, j = ceil(k / 8): at least k distinct elements are that large.  (No bound when
+// some warp has fewer than j such threads; the tile then overflows the list and is fed
+// again in slices.)  Returns the bound; sh.overflow tells whether a list ran over.
+template <typename T>
+__device__ __noinline__ float first_tile(Shared &sh, const uint32_t *bitmap, const uint4 *stage,
+                                         uint32_t valid_vectors, const Row r) {
+    using L = Lanes<T>;
+    constexpr int kPer = L::kPer;
+    const uint32_t tid = threadIdx.x, lane = tid & 31u;
+    float v[kVectors][kPer];
+    uint32_t bits[kVectors];
+    float best = __uint_as_float(0xff800000u);
+    bool have = false;
+#pragma unroll
+    for (int u = 0; u < kVectors; u++) {
+        const uint32_t g = u * kConsumers + tid;
+        bits[u] = 0;
+        if (g < valid_vectors) {
+            L::unpack(stage[g], v[u]);
+            if (r.seen_any) bits[u] = seen_bits<T>(bitmap, 0, g);
+        } else {
+#pragma unroll
+            for (int j = 0; j < kPer; j++) v[u][j] = __uint_as_float(0xff800000u);
+        }
+#pragma unroll
+        for (int j = 0; j < kPer; j++) {
+            if (!((bits[u] >> j) & 1u) && !is_nonfinite(v[u][j])) {
+                best = fmaxf(best, v[u][j]);
+                have = true;
+            }
+        }
+    }
+    uint32_t key = have ? float_key(best) : 0u;
+    const uint32_t per_warp = (r.k + kConsumerWarps - 1) / kConsumerWarps;
+    uint32_t kth = 0;
+    for (uint32_t i = 0; i < per_warp; i++) {
+        kth = __reduce_max_sync(kFullMask, key);
+        if (kth == 0) break;
+        const unsigned owners = __ballot_sync(kFullMask, key == kth);
+        if ((int)lane == __ffs(owners) - 1) key = 0;
+    }
+    if (lane == 0) atomicMin(&sh.first_key, kth);
+    CB::sync();
+    const float tau = key_to_float(sh.first_key);
+    if (tid == 0) {
+        sh.cand.tau_score = tau;
+        sh.cand.tau_id = kPaddingId;
+    }
+#pragma unroll
+    for (int u = 0; u < kVectors; u++) {
+        const uint32_t g = u * kConsumers + tid;
+        if (g >= valid_vectors) continue;
+#pragma unroll
+        for (int j = 0; j < kPer; j++) {
+            const uint32_t id = r.id_base + g * kPer + j;
+            if (r.greedy) consider<true, false>(sh, r, v[u][j], id, (bits[u] >> j) & 1u, tau, kPaddingId, true);
+            else consider<false, false>(sh, r, v[u][j], id, (bits[u] >> j) & 1u, tau, kPaddingId, true);
+        }
+    }
+    return tau;
+}
+
+// The hot loop over tiles first .. tiles-1 of a row.  Calls nothing: whatever is live
+// across a call inside a loop is saved and restored on every trip.  When a list wants
+// attention the loop stops with the stage still held (the caller may have to read the
+// tile again) and says so in the top bit of the tile number it returns.
+template <typename T, bool kGreedy>
+__device__ __noinline__ uint32_t hot_tiles(Shared &sh, const uint32_t *bitmap, const unsigned char *ring,
+                                           uint32_t first, uint32_t tiles, uint32_t last_vectors,
+                                           const uint32_t row_sequence, const Row r, const float tau) {
+    using L = Lanes<T>;
+    constexpr int kPer = L::kPer;
+    constexpr uint32_t kTile = kStageBytes / sizeof(T);
+    const uint32_t tid = threadIdx.x;
+    for (uint32_t t = first; t < tiles; t++) {
+        const uint32_t at = (row_sequence + t) % kStages, use = (row_sequence + t) / kStages;
+        if (!sh.ring_error && !bounded_wait(&sh.full[at], use & 1u)) sh.ring_error = 1;
+        const uint4 *stage = reinterpret_cast<const uint4 *>(ring + (size_t)at * kStageBytes);
+        const uint32_t valid_vectors = t + 1 == tiles ? last_vectors : kStageBytes / 16u;
+        const uint32_t tile_word = t * (kTile / 32);
+        bool want = false;
+        uint4 raw[kVectors];
+#ifdef FGK_EXPERIMENT_NO_COMPUTE
+        if (valid_vectors == 12345u) want = stage[tid].x == 77u;
+        if (CB::sync_or(want)) return t | kNeedsAttention;
+        if (tid == 0) mbarrier_arrive(&sh.empty[at]);
+        continue;
+#endif
+#pragma unroll
+        for (int u = 0; u < kVectors; u++) {
+            const uint32_t g = u * kConsumers + tid;
+            raw[u] = g < valid_vectors ? stage[g]
+                                       : make_uint4(0xff80ff80u, 0xff80ff80u, 0xff80ff80u, 0xff80ff80u);
+        }
+#pragma unroll
+        for (int u = 0; u < kVectors; u++) {
+            float v[kPer];
+            L::unpack(raw[u], v);
+            float top = v[0];  // NaN never compares above the bound
+#pragma unroll
+            for (int j = 1; j < kPer; j++) top = fmaxf(top, v[j]);
+            bool hot = top > tau;
+            if (kGreedy) {  // the argmax order must see NaN and both infinities, and
+                            // magnitudes a repetition factor of at most 2^40 could push there
+                uint32_t widest = 0;
+#pragma unroll
+                for (int j = 0; j < kPer; j++) widest = max(widest, __float_as_uint(v[j]) & 0x7fffffffu);
+                hot = hot || widest >= 0x6b000000u;
+            }
+            const uint32_t g = u * kConsumers + tid;
+            if (hot && g < valid_vectors) {
+                const uint32_t bits = r.seen_any ? seen_bits<T>(bitmap, tile_word, g) : 0u;
+                const uint32_t first_id = r.id_base + t * kTile + g * kPer;
+#pragma unroll
+                for (int j = 0; j < kPer; j++)
+                    want |= consider<kGreedy, false>(sh, r, v[j], first_id + j, (bits >> j) & 1u, tau,
+                                                     kPaddingId, false);
+            }
+        }
+        // (the filler past the row's end reads as a NaN in fp32 and as -inf in bf16: never
+        // above the bound, and the test on g keeps greedy rows from looking at it)
+        if (CB::sync_or(want)) return t | kNeedsAttention;
+        if (tid == 0) mbarrier_arrive(&sh.empty[at]);
+    }
+    return tiles - 1;
+}
+
+// Phase 1 of a row: bitmap of the history ids that fall into this kernel's columns.
+// Returns false (and the status in sh.bad_history) when the history is unusable.
+__device__ __noinline__ void build_bitmap(Shared &sh, uint32_t *bitmap, const Params &p, const Row r) {
+    const uint32_t tid = threadIdx.x;
+    uint4 *wide = reinterpret_cast<uint4 *>(bitmap);
+    const uint32_t quads = (p.bitmap_words + 3u) / 4u;  // the host rounds the allocation up
+    for (uint32_t i = tid; i < quads; i += kConsumers) wide[i] = make_uint4(0, 0, 0, 0);
+    CB::sync();
+    constexpr int kBatch = 8;  // tokens per thread and trip, loaded before any is used
+    for (uint32_t base = 0; base < r.history_len; base += kBatch * kConsumers) {
+        uint32_t token[kBatch];
+#pragma unroll
+        for (int q = 0; q < kBatch; q++) {
+            const uint32_t i = base + q * kConsumers + tid;
+            token[q] = i < r.history_len ? r.tokens[i] : p.vocab_offset;
+        }
+#pragma unroll
+        for (int q = 0; q < kBatch; q++) {
+            if (base + q * kConsumers + tid >= r.history_len) continue;
+            if (token[q] >= p.vocab_total) sh.bad_history = kErrFormat;
+            const uint32_t local = token[q] - p.vocab_offset;  // wraps for ids below the span
+            if (local < p.vocab) {
+                const uint32_t bit = 1u << (local & 31u);
+                if ((bitmap[local >> 5] & bit) == 0) atomicOr(&bitmap[local >> 5], bit);
+            }
+        }
+    }
+    CB::sync();
+}
+
+// Phase 4: the row's result from the candidate list (shard candidates, the greedy
+// winner, or the select step of src/sampler.c:80-122).  Every consumer calls it.
+__device__ __noinline__ void finish_row(Shared &sh, const Params &p, uint32_t row, const Row r,
+                                        const SamplerConfig cfg, bool shard_mode) {
+    const uint32_t tid = threadIdx.x;
+    attend(sh, r);  // counts what was put aside and leaves the k best
+    const uint32_t held = min(sh.cand.count, r.k);
+    uint32_t bad_history = sh.bad_history;
+    if (sh.ring_error) bad_history = kErrLimit;  // a tile never landed
+    const uint32_t wild_id = (uint32_t)(sh.wild_key >> 32);  // the padding id when nothing was seen
+    const uint32_t wild_bits = (uint32_t)sh.wild_key;
+
+    if (shard_mode) {
+        sort_candidates<kCandCap, CB>(sh.cand, sh.fin, held);
+        if (tid < r.k) {
+            const size_t at = (size_t)row * r.k + tid;
+            const bool live = tid < held && !bad_history;
+            p.shard_scores[at] = live ? sh.fin.score[tid] : __uint_as_float(0xff800000u);
+            p.shard_ids[at] = live ? sh.fin.id[tid] : kPaddingId;
+        }
+        if (tid == 0) {
+            p.out.row_status[row] = bad_history;
+            if (bad_history) atomicMin(p.out.first_error, ((unsigned long long)row << 8) | bad_history);
+        }
+        return;
+    }
+    if (bad_history) {  // "history token ... is outside vocabulary", src/output.c:610-612
+        if (tid == 0) {
+            report_row(p.out, row, bad_history, kPaddingId, 0.0f);
+            if (p.out.dbg_count) p.out.dbg_count[row] = 0;
+        }
+        return;
+    }
+    if (r.greedy) {
+        if (tid == 0) {
+            uint32_t status = kOk, token;
+            float logit;
+            if (wild_id != kPaddingId) {
+                // a NaN/Inf beats every finite logit in the argmax order and is then
+                // rejected: src/output.c:593 (no penalties) / 737-739 (penalised)
+                status = penalties_active(cfg) ? kErrFormat : kErrMismatch;
+                token = wild_id;
+                logit = __uint_as_float(wild_bits);
+            } else if (held == 0) {
+                status = kErrMismatch;
+                token = kPaddingId;
+                logit = 0.0f;
+            } else {
+                token = sh.cand.id[0];
+                logit = sh.cand.score[0];
+            }
+            report_row(p.out, row, status, token, logit);
+            if (p.out.dbg_count) {
+                const bool ok = status == kOk;
+                p.out.dbg_count[row] = ok ? 1u : 0u;
+                if (p.out.dbg_ids) p.out.dbg_ids[(size_t)row * kMaxK] = ok ? token : kPaddingId;
+                if (p.out.dbg_scores) p.out.dbg_scores[(size_t)row * kMaxK] = ok ? logit : 0.0f;
+            }
+        }
+        return;
+    }
+    sort_candidates<kCandCap, CB>(sh.cand, sh.fin, held);
+    if (tid < 32) finish_select(sh.fin, held, cfg, p.uniforms[row], row, p.out);
+}
+
+// Does this kernel sample the row, or is it left to the kernel without a top-k cut?
+__device__ __forceinline__ bool row_is_ours(const SamplerConfig &cfg, bool shard_mode) {
+    return shard_mode || cfg.temperature == 0.0f || cfg.top_k != 0;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kBlock, FGK_PERSIST_CTAS)
+persistent_select_kernel(const __grid_constant__ Params p) {
+    extern __shared__ __align__(128) unsigned char dynamic[];
+    __shared__ Shared sh;
+    unsigned char *ring = dynamic;
+    uint32_t *bitmap = reinterpret_cast<uint32_t *>(dynamic + (size_t)kStages * kStageBytes);
+
+    const uint32_t tid = threadIdx.x;
+    const bool shard_mode = p.shard_k != 0;
+    const uint32_t row_bytes = p.vocab * (uint32_t)sizeof(T);
+    const uint32_t tiles = (row_bytes + kStageBytes - 1) / kStageBytes;
+
+    if (tid == 0) {
+#pragma unroll
+        for (int s = 0; s < kStages; s++) {
+            mbarrier_init(&sh.full[s], 1);
+            mbarrier_init(&sh.empty[s], 1);
+        }
+        mbarrier_fence_init();
+        sh.ring_error = 0;
+    }
+    __syncthreads();
+
+    if (tid >= (uint32_t)kConsumers) {
+        // ---------------------------------------------------------------- copy warp
+        if (tid != (uint32_t)kConsumers) return;
+        const uint64_t policy = l2_policy_evict_first();
+        RingCursor cursor;
+        bool gave_up = false;
+        for (uint32_t row = blockIdx.x; row < p.rows && !gave_up; row += gridDim.x) {
+            const SamplerConfig cfg = p.config_count > 1 ? p.configs[row] : p.config0;
+            if (!row_is_ours(cfg, shard_mode)) continue;
+            const unsigned char *source =
+                static_cast<const unsigned char *>(p.logits) + (size_t)row * p.row_stride * sizeof(T);
+            for (uint32_t t = 0; t < tiles; t++) {
+                if (cursor.use != 0 && !bounded_wait(&sh.empty[cursor.stage], (cursor.use - 1u) & 1u)) {
+                    sh.ring_error = 1;  // the consumers see it and fail their rows
+                    gave_up = true;
+                    break;
+                }
+                const uint32_t bytes = min(kStageBytes, row_bytes - t * kStageBytes);
+                mbarrier_expect(&sh.full[cursor.stage], bytes);
+                bulk_copy_to_shared_hinted(ring + (size_t)cursor.stage * kStageBytes,
+                                           source + (size_t)t * kStageBytes, bytes,
+                                           &sh.full[cursor.stage], policy);
+                cursor.advance();
+            }
+        }
+        if (gave_up) {
+            // copies already asked for still write into this CTA's shared memory: see them
+            // land (bounded) before the CTA may go away
+            for (int s = 0; s < kStages; s++) {
+                const uint32_t issued = cursor.use + ((uint32_t)s < cursor.stage ? 1u : 0u);
+                if (issued != 0) bounded_wait(&sh.full[s], (issued - 1u) & 1u);
+            }
+        }
+        return;
+    }
+
+    // -------------------------------------------------------------------- consumers
+    uint32_t row_sequence = 0;  // tiles of earlier rows: tile t of this row is ring tile row_sequence + t
+    for (uint32_t row = blockIdx.x; row < p.rows; row += gridDim.x) {
+        const SamplerConfig cfg = p.config_count > 1 ? p.configs[row] : p.config0;
+        if (!row_is_ours(cfg, shard_mode)) continue;
+        Row r;
+        r.greedy = !shard_mode && cfg.temperature == 0.0f;
+        r.k = shard_mode ? p.shard_k : (r.greedy ? 1u : cfg.top_k);
+        r.cut_at = 4 * r.k + 64;
+        r.id_base = p.vocab_offset;
+        r.flat_offset = penalty_offset(1u, cfg.presence_penalty, cfg.frequency_penalty);
+        r.presence = cfg.presence_penalty;
+        r.frequency = cfg.frequency_penalty;
+        r.repetition = make_repetition(cfg.repetition_penalty);
+        r.tokens = nullptr;
+        r.history_len = 0;
+        uint32_t bad_history = 0;
+        if (p.history_tokens != nullptr && p.history_offsets != nullptr && p.bitmap_words != 0 &&
+            penalties_active(cfg)) {
+            const uint64_t begin = p.history_offsets[row], end = p.history_offsets[row + 1];
+            if (end < begin || end - begin > p.history_max) {
+                bad_history = kErrLimit;
+            } else {
+                r.tokens = p.history_tokens + begin;
+                r.history_len = (uint32_t)(end - begin);
+            }
+        }
+        r.seen_any = r.history_len != 0;
+        r.with_counts = r.seen_any && cfg.frequency_penalty != 0.0f;
+        // the host sends only rows whose penalties cannot raise a logit; a row that
+        // slipped through is failed rather than sampled wrongly
+        if (r.seen_any && !(cfg.presence_penalty >= 0.0f && cfg.frequency_penalty >= 0.0f &&
+                            cfg.repetition_penalty >= 1.0f && r.repetition.tame))
+            bad_history = kErrLimit;
+
+        if (tid == 0) {
+            sh.cand.count = 0;
+            sh.cand.tau_score = __uint_as_float(0xff800000u);
+            sh.cand.tau_id = kPaddingId;
+            sh.defer_count = 0;
+            sh.bad_history = bad_history;
+            sh.wild_key = ~0ull;
+            sh.overflow = 0;
+            sh.first_key = 0xffffffffu;
+        }
+        if (r.seen_any) build_bitmap(sh, bitmap, p, r);
+        else CB::sync();
+
+        const uint32_t last_vectors = (row_bytes - (tiles - 1) * kStageBytes) / 16u;
+        // ---- tile 0 ----
+        const uint32_t at0 = row_sequence % kStages;
+        if (!sh.ring_error && !bounded_wait(&sh.full[at0], (row_sequence / kStages) & 1u)) sh.ring_error = 1;
+        const uint4 *stage0 = reinterpret_cast<const uint4 *>(ring + (size_t)at0 * kStageBytes);
+        const uint32_t vectors0 = tiles == 1 ? last_vectors : kStageBytes / 16u;
+        float tau = first_tile<T>(sh, bitmap, stage0, vectors0, r);
+        CB::sync();
+        if (sh.overflow) tau = redo_tile<T>(sh, bitmap, stage0, 0, vectors0, r);
+        if (tid == 0) mbarrier_arrive(&sh.empty[at0]);
+
+        // ---- tiles 1 .. ----
+        for (uint32_t t = 1; t < tiles;) {
+            const uint32_t stopped =
+                r.greedy ? hot_tiles<T, true>(sh, bitmap, ring, t, tiles, last_vectors, row_sequence, r, tau)
+                         : hot_tiles<T, false>(sh, bitmap, ring, t, tiles, last_vectors, row_sequence, r, tau);
+            t = (stopped & ~kNeedsAttention) + 1;
+            if (stopped & kNeedsAttention) {
+                const uint32_t at = (row_sequence + t - 1) % kStages;
+                if (sh.overflow) {
+                    const uint4 *stage = reinterpret_cast<const uint4 *>(ring + (size_t)at * kStageBytes);
+                    tau = redo_tile<T>(sh, bitmap, stage, t - 1, t == tiles ? last_vectors : kStageBytes / 16u, r);
+                } else {
+                    tau = attend(sh, r);
+                }
+                if (tid == 0) mbarrier_arrive(&sh.empty[at]);
+            }
+        }
+        finish_row(sh, p, row, r, cfg, shard_mode);
+        CB::sync();  // the lists are free for the next row
+        row_sequence += tiles;
+    }
+}
+
+}  // namespace persist
+}  // namespace fgk
+
+// ------------------------------------------------------------------ host side
+
+using namespace fgk;
+
+static persist::Params to_persist_params(const fgk_stream_launch *l) {
+    persist::Params p;
+    p.logits = l->logits;
+    p.row_stride = l->row_stride;
+    p.rows = l->rows;
+    p.vocab = l->vocab;
+    p.vocab_offset = l->vocab_offset;
+    p.vocab_total = l->vocab_total;
+    p.history_tokens = l->history_tokens;
+    p.history_offsets = l->history_offsets;
+    p.history_max = l->history_max;
+    p.bitmap_words = l->bitmap_words;
+    p.configs = static_cast<const SamplerConfig *>(l->configs_device);
+    static_assert(sizeof(fg_sampler_config) == sizeof(SamplerConfig), "config layout");
+    memcpy(&p.config0, &l->config0, sizeof(SamplerConfig));
+    p.config_count = l->config_count;
+    p.shard_k = l->shard_k;
+    p.uniforms = l->uniforms;
+    p.shard_scores = l->shard_scores;
+    p.shard_ids = l->shard_ids;
+    p.out.tokens = l->out.tokens;
+    p.out.token_logits = l->out.token_logits;
+    p.out.row_status = l->out.row_status;
+    p.out.first_error = reinterpret_cast<unsigned long long *>(l->out.first_error);
+    p.out.dbg_count = l->out.dbg_count;
+    p.out.dbg_ids = l->out.dbg_ids;
+    p.out.dbg_scores = l->out.dbg_scores;
+    p.out.dbg_raw = l->out.dbg_raw;
+    p.out.dbg_tempered = l->out.dbg_tempered;
+    return p;
+}
+
+extern "C" uint64_t fgk_persistent_dynamic_smem(uint32_t bitmap_words) {
+    return (uint64_t)persist::kStages * persist::kStageBytes + (((uint64_t)bitmap_words + 3u) / 4u) * 16u;
+}
+
+extern "C" uint32_t fgk_persistent_ctas_per_sm(uint32_t dtype, uint64_t dynamic_smem) {
+    int blocks = 0;
+    const cudaError_t e =
+        dtype == 0 ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(
+                         &blocks, persist::persistent_select_kernel<float>, persist::kBlock, (size_t)dynamic_smem)
+                   : cudaOccupancyMaxActiveBlocksPerMultiprocessor(
+                         &blocks, persist::persistent_select_kernel<uint16_t>, persist::kBlock, (size_t)dynamic_smem);
+    return e == cudaSuccess && blocks > 0 ? (uint32_t)blocks : 0u;
+}
+
+extern "C" int fgk_persistent_prepare(void) {
+    cudaError_t e = cudaFuncSetAttribute(persist::persistent_select_kernel<float>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         FGK_PERSIST_MAX_DYNAMIC_SMEM);
+    if (e != cudaSuccess) return (int)e;
+    e = cudaFuncSetAttribute(persist::persistent_select_kernel<uint16_t>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, FGK_PERSIST_MAX_DYNAMIC_SMEM);
+    return (int)e;
+}
+
+extern "C" int fgk_launch_persistent_select(const fgk_stream_launch *l, uint32_t ctas, void *stream) {
+    const persist::Params p = to_persist_params(l);
+    const size_t dynamic = (size_t)fgk_persistent_dynamic_smem(l->bitmap_words);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (l->dtype == 0)
+        persist::persistent_select_kernel<float><<<ctas, persist::kBlock, dynamic, s>>>(p);
+    else
+        persist::persistent_select_kernel<uint16_t><<<ctas, persist::kBlock, dynamic, s>>>(p);
+    return (int)cudaGetLastError();
+}

@@ -21,12 +21,6 @@
 
 namespace fgk {
 
-#ifndef FGK_RING_STAGES
-#define FGK_RING_STAGES 3   // 16 KB (fp32) tiles the copy engine keeps in flight per CTA
-#endif
-#ifndef FGK_RING_MIN_CTAS
-#define FGK_RING_MIN_CTAS 3
-#endif
 #ifndef FGK_STREAM_MIN_CTAS
 #define FGK_STREAM_MIN_CTAS 4
 #endif
@@ -67,7 +61,7 @@ struct StreamParams {
     uint32_t bitmap_words;          // shared-memory layout (0: no history structure)
     uint32_t count_capacity;        // entries of the dense count array (0: counts unused)
     uint32_t dense_wide;            // dense counts are u32 (histories longer than 65,535)
-    // ring path: history structures built by history_build_kernel, one slot per (row, split)
+    // history structures built by history_build_kernel, one slot per (row, split)
     uint32_t *history_global;
     uint64_t history_stride_words;
     void *history_meta;
@@ -820,6 +814,20 @@ __device__ __noinline__ uint32_t fast_tiles(const StreamParams &p, StreamShared 
     return full_tiles - 1;
 }
 
+#ifdef FGK_PHASE_CLOCKS
+__device__ unsigned long long fgk_phase_clocks[8];
+#define FGK_TICK(slot)                                                          \
+    do {                                                                         \
+        if (threadIdx.x == 0) {                                                  \
+            const long long now = clock64();                                     \
+            atomicAdd(&fgk_phase_clocks[slot], (unsigned long long)(now - tick)); \
+            tick = now;                                                          \
+        }                                                                        \
+    } while (0)
+#else
+#define FGK_TICK(slot) do { } while (0)
+#endif
+
 template <typename T>
 __global__ void __launch_bounds__(kThreads, FGK_STREAM_MIN_CTAS)
 stream_select_kernel(const __grid_constant__ StreamParams p) {
@@ -829,6 +837,9 @@ stream_select_kernel(const __grid_constant__ StreamParams p) {
 
     const uint32_t tid = threadIdx.x;
     const uint32_t split = blockIdx.x, row = blockIdx.y;
+#ifdef FGK_PHASE_CLOCKS
+    long long tick = clock64();
+#endif
     const SamplerConfig cfg = p.config_count > 1 ? p.configs[row] : p.config0;
     const bool shard_mode = p.shard_k != 0;
     const bool greedy = !shard_mode && cfg.temperature == 0.0f;
@@ -861,6 +872,7 @@ stream_select_kernel(const __grid_constant__ StreamParams p) {
 
     // ---- 1. history slice -> bitmap / running popcount / offsets ----
     state.flags = build_history(p, sh, dyn_smem, row, lo, state.n, cfg);
+    FGK_TICK(0);
 #ifdef FGK_EXPERIMENT_HISTORY_ONLY
     if (tid == 0) p.out.row_status[row] = 0;
     return;
@@ -875,6 +887,7 @@ stream_select_kernel(const __grid_constant__ StreamParams p) {
     const uint32_t tiles = (n + kTile - 1) / kTile;
     const uint32_t full_tiles = state.aligned ? n / kTile : 0;
     float tau = careful_tile<T>(p, sh, dyn_smem, columns, 0, state, __uint_as_float(0xff800000u));
+    FGK_TICK(1);
 
     // can the row's penalties only lower a logit?  (rows without history count as such)
     const bool lowering = !(state.flags & kSeenAny) ||
@@ -885,38 +898,43 @@ stream_select_kernel(const __grid_constant__ StreamParams p) {
             lowering ? fast_tiles<T, true>(p, sh, dyn_smem, columns, t, full_tiles, state, tau)
                      : fast_tiles<T, false>(p, sh, dyn_smem, columns, t, full_tiles, state, tau);
         t = (stopped & ~kNeedsAttention) + 1;
+        FGK_TICK(2);
         if (stopped & kNeedsAttention) {
             // a tile pushed more than the list holds: feed it again in pieces;
             // otherwise the list is merely long: cut it, which lifts the bound
             if (sh.overflow) tau = redo_tile<T>(p, sh, dyn_smem, columns, t - 1, state);
             else tau = cut_list(sh, state.k);
+            FGK_TICK(3);
+#ifdef FGK_PHASE_CLOCKS
+            if (tid == 0) atomicAdd(&fgk_phase_clocks[6], 1ull);
+#endif
         }
     }
     // the ragged end of an aligned row, or every further tile of an unaligned one
     for (uint32_t t = full_tiles > 1 ? full_tiles : 1; t < tiles; t++)
         tau = careful_tile<T>(p, sh, dyn_smem, columns, t, state, tau);
+    FGK_TICK(4);
 
     // ---- 3./4. this split's k best, the row's result ----
     finish_split(p, sh, row, split, state.k, greedy, shard_mode, cfg);
+    FGK_TICK(5);
 }
 
-// ======================================================================= ring path
+#ifdef FGK_PHASE_CLOCKS
+extern "C" int fgk_read_phase_clocks(unsigned long long *out, int reset) {
+    cudaError_t e = cudaMemcpyFromSymbol(out, fgk_phase_clocks, sizeof(unsigned long long) * 8);
+    if (e == cudaSuccess && reset) {
+        unsigned long long zero[8] = {0};
+        e = cudaMemcpyToSymbol(fgk_phase_clocks, zero, sizeof(zero));
+    }
+    return (int)e;
+}
+#endif
+
+// ================================================================== history pass
 //
-// The same algorithm with the row streamed through a ring of shared-memory stages that
-// the copy engine fills (cp.async.bulk + mbarrier): bytes in flight no longer cost
-// registers, so the consumer loop is a handful of instructions per tile and keeps
-// running while lists are cut or rows finish.  The row's history structure is built by
-// a pass of its own (history_build_kernel) into global memory and consulted from
-// there; with penalties that can only lower a logit that happens for a few values per
-// tile.  Needs 16-byte aligned rows; everything else takes stream_select_kernel.
-
-constexpr int kRingStages = FGK_RING_STAGES;
-
-struct RingShared {
-    StreamShared common;
-    alignas(8) uint64_t full[kRingStages];  // one mbarrier per stage: "the tile has landed"
-    uint32_t ring_error;                    // a bounded wait ran out
-};
+// The history structures of a whole batch, built by a pass of their own into global
+// memory: the kernel without a top-k cut reads them from there.
 
 // Per (row, split): what build_history returned and the status a broken history earns.
 struct alignas(8) HistoryMeta {
@@ -924,8 +942,8 @@ struct alignas(8) HistoryMeta {
     uint32_t bad_history;
 };
 
-// Pass 1 of the ring path: build_history in shared memory, then the structure is
-// copied verbatim to the unit's slot in global memory.
+// build_history in shared memory, then the structure is copied verbatim to the unit's
+// slot in global memory.
 __global__ void __launch_bounds__(kThreads) history_build_kernel(const __grid_constant__ StreamParams p) {
     extern __shared__ __align__(16) uint32_t dyn_smem[];
     __shared__ StreamShared sh;
@@ -953,214 +971,6 @@ __global__ void __launch_bounds__(kThreads) history_build_kernel(const __grid_co
         meta.bad_history = sh.bad_history;
         reinterpret_cast<HistoryMeta *>(p.history_meta)[unit] = meta;
     }
-}
-
-// The consumer loop over ring tiles first_tile .. full_tiles-1 (tile i lives in stage
-// (i - 1) % kRingStages; tile 0 never enters the ring).  Same contract as fast_tiles:
-// calls nothing, returns the last tile examined, with kNeedsAttention set when the
-// candidate list wants a cut or overflowed.
-template <typename T, bool kLowering, bool kGreedy>
-__device__ __noinline__ uint32_t ring_tiles(const StreamParams &p, RingShared &rs,
-                                            const uint32_t *history, unsigned char *ring,
-                                            const T *columns, uint32_t first_tile,
-                                            uint32_t full_tiles, const RowState state,
-                                            const float tau) {
-    using L = Loader<T>;
-    StreamShared &sh = rs.common;
-    const uint32_t tid = threadIdx.x;
-    constexpr uint32_t kTileBytes = kTile * sizeof(T);
-    constexpr uint32_t kWordsPerStep = kThreads * L::kPerVector / 32;
-    const uint32_t word_lane = tid * L::kPerVector / 32;
-    const uint32_t bit_lane = (tid * L::kPerVector) & 31u;
-    const bool seen_any = state.flags & kSeenAny, with_counts = state.flags & kWithCounts;
-    const HistoryView view = history_view(p, const_cast<uint32_t *>(history));
-    const uint32_t *bitmap = view.bitmap + word_lane;
-    const uint32_t cut_at = 4 * state.k + 64;
-    for (uint32_t t = first_tile; t < full_tiles; t++) {
-        const uint32_t stage = (t - 1) % kRingStages;
-        const uint32_t parity = ((t - 1) / kRingStages) & 1u;
-        if (!mbarrier_wait(&rs.full[stage], parity)) rs.ring_error = 1;  // values are then garbage; the row fails
-        const uint4 *tile = reinterpret_cast<const uint4 *>(ring + (size_t)stage * kTileBytes) + tid;
-        float v[kElemsPerThread];
-#pragma unroll
-        for (int u = 0; u < L::kVectors; u++) L::unpack(tile[u * kThreads], &v[u * L::kPerVector]);
-        const uint32_t tile_word = t * (kTile / 32);
-        if (!kLowering && seen_any) {
-#pragma unroll
-            for (int u = 0; u < L::kVectors; u++) {
-                const uint32_t word = bitmap[tile_word + u * kWordsPerStep];
-                const uint32_t bits = (word >> bit_lane) & ((1u << L::kPerVector) - 1u);
-                if (bits == 0) continue;
-#pragma unroll
-                for (int j = 0; j < L::kPerVector; j++) {
-                    if (bits & (1u << j)) {
-                        float offset = state.flat_offset;
-                        if (with_counts)
-                            offset = penalty_offset(
-                                view.count(tile_word + u * kWordsPerStep + word_lane, word,
-                                           bit_lane + j),
-                                state.presence, state.frequency);
-                        v[u * L::kPerVector + j] =
-                            penalise_with_offset(v[u * L::kPerVector + j], offset, state.repetition);
-                    }
-                }
-            }
-        }
-        float top = v[0];  // NaN never wins a maximum, nor compares above the bound
-#pragma unroll
-        for (int e = 1; e < kElemsPerThread; e++) top = fmaxf(top, v[e]);
-        bool hot = top > tau;
-        if (kGreedy) {
-            uint32_t widest = 0;
-#pragma unroll
-            for (int e = 0; e < kElemsPerThread; e++)
-                widest = max(widest, __float_as_uint(v[e]) & 0x7fffffffu);
-            // with lowering penalties also magnitudes a repetition factor of at most 2^40
-            // could push to infinity
-            hot = hot || widest >= (kLowering ? 0x6b000000u : 0x7f800000u);
-        }
-        bool want_cut = false;
-        if (hot) {
-            // Few threads get here once the bound has settled.  Later columns carry
-            // larger ids than whatever produced the bound, so a tie with it loses.
-#pragma unroll
-            for (int u = 0; u < L::kVectors; u++) {
-                const uint32_t first_id =
-                    state.id_base + t * kTile + (u * kThreads + tid) * L::kPerVector;
-                uint32_t word = 0, bits = 0;
-                if (kLowering && seen_any) {
-                    word = bitmap[tile_word + u * kWordsPerStep];
-                    bits = (word >> bit_lane) & ((1u << L::kPerVector) - 1u);
-                }
-#pragma unroll
-                for (int j = 0; j < L::kPerVector; j++) {
-                    float x = v[u * L::kPerVector + j];
-                    if (kLowering && (bits & (1u << j))) {
-                        float offset = state.flat_offset;
-                        if (with_counts)
-                            offset = penalty_offset(
-                                view.count(tile_word + u * kWordsPerStep + word_lane, word,
-                                           bit_lane + j),
-                                state.presence, state.frequency);
-                        x = penalise_with_offset(x, offset, state.repetition);
-                    }
-                    if (is_nonfinite(x)) {
-                        if (kGreedy)
-                            atomicMin(&sh.wild_key, ((unsigned long long)(first_id + j) << 32) |
-                                                        __float_as_uint(x));
-                    } else if (x > tau) {
-                        const uint32_t slot = atomicAdd(&sh.cand.count, 1u);
-                        if (slot < (uint32_t)kCandCap) {
-                            sh.cand.score[slot] = x;
-                            sh.cand.id[slot] = first_id + j;
-                        } else {
-                            sh.overflow = 1;
-                        }
-                        want_cut = want_cut || slot >= cut_at;
-                    }
-                }
-            }
-        }
-        // everyone is done with the stage: it can take the tile kRingStages ahead
-        const bool attention = __syncthreads_or(want_cut);
-        if (tid == 0 && t + kRingStages < full_tiles) {
-            mbarrier_expect(&rs.full[stage], kTileBytes);
-            bulk_copy_to_shared(ring + (size_t)stage * kTileBytes,
-                                columns + (size_t)(t + kRingStages) * kTile, kTileBytes,
-                                &rs.full[stage]);
-        }
-        if (attention) return t | kNeedsAttention;
-    }
-    return full_tiles - 1;
-}
-
-template <typename T>
-__global__ void __launch_bounds__(kThreads, FGK_RING_MIN_CTAS)
-ring_select_kernel(const __grid_constant__ StreamParams p) {
-    extern __shared__ __align__(128) unsigned char ring[];
-    __shared__ RingShared rs;
-    StreamShared &sh = rs.common;
-    constexpr uint32_t kTileBytes = kTile * sizeof(T);
-
-    const uint32_t tid = threadIdx.x;
-    const uint32_t split = blockIdx.x, row = blockIdx.y;
-    const SamplerConfig cfg = p.config_count > 1 ? p.configs[row] : p.config0;
-    const bool shard_mode = p.shard_k != 0;
-    const bool greedy = !shard_mode && cfg.temperature == 0.0f;
-    if (!shard_mode && !greedy && cfg.top_k == 0) return;  // rows without a top-k cut use the nucleus kernel
-
-    const uint32_t lo = split * p.split_len;
-    const T *columns = static_cast<const T *>(p.logits) + (size_t)row * p.row_stride + lo;
-    RowState state;
-    state.n = min(p.split_len, p.vocab - lo);
-    state.id_base = p.vocab_offset + lo;
-    state.k = shard_mode ? p.shard_k : (greedy ? 1u : cfg.top_k);
-    state.greedy = greedy;
-    state.aligned = true;  // the host only sends 16-byte aligned rows here
-    state.flat_offset = penalty_offset(1u, cfg.presence_penalty, cfg.frequency_penalty);
-    state.presence = cfg.presence_penalty;
-    state.frequency = cfg.frequency_penalty;
-    state.repetition = make_repetition(cfg.repetition_penalty);
-    const uint32_t full_tiles = state.n / kTile;
-    const uint32_t tiles = (state.n + kTile - 1) / kTile;
-
-    const size_t unit = (size_t)row * p.splits + split;
-    uint32_t *history = nullptr;
-    state.flags = 0;
-    if (tid == 0) {
-        sh.cand.count = 0;
-        sh.cand.tau_score = __uint_as_float(0xff800000u);
-        sh.cand.tau_id = kPaddingId;
-        sh.bad_history = 0;
-        sh.wild_key = ~0ull;
-        sh.distinct = 0;
-        sh.overflow = 0;
-        rs.ring_error = 0;
-#pragma unroll
-        for (int s = 0; s < kRingStages; s++) mbarrier_init(&rs.full[s], 1);
-        mbarrier_fence_init();
-    }
-    __syncthreads();
-    // tiles 1 .. kRingStages start travelling before anything else happens
-    if (tid == 0) {
-        for (uint32_t i = 1; i <= (uint32_t)kRingStages && i < full_tiles; i++) {
-            mbarrier_expect(&rs.full[i - 1], kTileBytes);
-            bulk_copy_to_shared(ring + (size_t)(i - 1) * kTileBytes, columns + (size_t)i * kTile,
-                                kTileBytes, &rs.full[i - 1]);
-        }
-    }
-    if (p.history_meta != nullptr) {
-        const HistoryMeta meta = reinterpret_cast<const HistoryMeta *>(p.history_meta)[unit];
-        state.flags = meta.flags;
-        if (tid == 0 && meta.bad_history) sh.bad_history = meta.bad_history;
-        history = p.history_global + unit * p.history_stride_words;
-    }
-
-    float tau = careful_tile<T>(p, sh, history, columns, 0, state, __uint_as_float(0xff800000u));
-
-    const bool lowering = !(state.flags & kSeenAny) ||
-                          (cfg.presence_penalty >= 0.0f && cfg.frequency_penalty >= 0.0f &&
-                           cfg.repetition_penalty >= 1.0f && state.repetition.tame);
-    for (uint32_t t = 1; t < full_tiles;) {
-        uint32_t stopped;
-        if (lowering)
-            stopped = greedy ? ring_tiles<T, true, true>(p, rs, history, ring, columns, t, full_tiles, state, tau)
-                             : ring_tiles<T, true, false>(p, rs, history, ring, columns, t, full_tiles, state, tau);
-        else
-            stopped = greedy ? ring_tiles<T, false, true>(p, rs, history, ring, columns, t, full_tiles, state, tau)
-                             : ring_tiles<T, false, false>(p, rs, history, ring, columns, t, full_tiles, state, tau);
-        t = (stopped & ~kNeedsAttention) + 1;
-        if (stopped & kNeedsAttention) {
-            if (sh.overflow) tau = redo_tile<T>(p, sh, history, columns, t - 1, state);
-            else tau = cut_list(sh, state.k);
-        }
-    }
-    for (uint32_t t = full_tiles > 1 ? full_tiles : 1; t < tiles; t++)
-        tau = careful_tile<T>(p, sh, history, columns, t, state, tau);
-
-    if (rs.ring_error && tid == 0) sh.bad_history = kErrLimit;  // a tile never landed: fail the row
-    __syncthreads();
-    finish_split(p, sh, row, split, state.k, greedy, shard_mode, cfg);
 }
 
 // ---------------------------------------------------------------- merge kernel
@@ -1322,13 +1132,6 @@ extern "C" int fgk_stream_prepare(void) {
     if (e == cudaSuccess)
         e = cudaFuncSetAttribute(history_build_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  FGK_STREAM_MAX_DYNAMIC_SMEM);
-    if (e == cudaSuccess)
-        e = cudaFuncSetAttribute(ring_select_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)fgk_ring_dynamic_smem(0));
-    if (e == cudaSuccess)
-        e = cudaFuncSetAttribute(ring_select_kernel<uint16_t>,
-                                 cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)fgk_ring_dynamic_smem(0));
     return (int)e;
 }
 
@@ -1382,33 +1185,6 @@ extern "C" int fgk_launch_history_build(const fgk_stream_launch *l, void *stream
     const StreamParams p = to_stream_params(l);
     const size_t dynamic = fgk_stream_dynamic_smem(l->bitmap_words, l->count_capacity, l->dense_wide);
     history_build_kernel<<<dim3(l->splits, l->rows), kThreads, dynamic, static_cast<cudaStream_t>(stream)>>>(p);
-    return (int)cudaGetLastError();
-}
-
-extern "C" uint64_t fgk_ring_dynamic_smem(uint32_t dtype) {
-    return (uint64_t)kRingStages * kTile * (dtype == 1u ? 2u : 4u);
-}
-
-// History pass (when the batch has penalties and history) followed by the ring kernel;
-// *launched counts the kernels.
-extern "C" int fgk_launch_ring_select(const fgk_stream_launch *l, void *stream, uint32_t *launched) {
-    const StreamParams p = to_stream_params(l);
-    const dim3 grid(l->splits, l->rows);
-    cudaStream_t s = static_cast<cudaStream_t>(stream);
-    *launched = 0;
-    if (l->history_meta != nullptr) {
-        const size_t dynamic = fgk_stream_dynamic_smem(l->bitmap_words, l->count_capacity, l->dense_wide);
-        history_build_kernel<<<grid, kThreads, dynamic, s>>>(p);
-        const cudaError_t e = cudaGetLastError();
-        if (e != cudaSuccess) return (int)e;
-        ++*launched;
-    }
-    const size_t ring_bytes = fgk_ring_dynamic_smem(l->dtype);
-    if (l->dtype == 1u)
-        ring_select_kernel<uint16_t><<<grid, kThreads, ring_bytes, s>>>(p);
-    else
-        ring_select_kernel<float><<<grid, kThreads, ring_bytes, s>>>(p);
-    ++*launched;
     return (int)cudaGetLastError();
 }
 

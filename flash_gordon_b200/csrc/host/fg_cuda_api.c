@@ -95,6 +95,7 @@ fg_status fg_cuda_context_create(int device, fg_cuda_context **out, fg_error *er
     if (!e) e = fgk_device_sm_count(device, &sms);
     if (!e) e = fgk_stream_create(&c->own_stream);
     if (!e) e = fgk_stream_prepare();
+    if (!e) e = fgk_persistent_prepare();
     if (!e) e = fgk_nucleus_prepare();
     if (!e) e = fgk_malloc((void **)&c->first_error, 256u);
     if (e) {
@@ -486,6 +487,7 @@ static bool plan_stream(const fg_cuda_context *c, uint32_t rows, uint32_t vocab,
 
 typedef struct batch_traits {
     bool penalties, counts, sampled, nucleus, topk_rows;
+    bool raising; /* some row's penalties can raise a logit (or its repetition factor is extreme) */
 } batch_traits;
 
 static fg_status check_batch(const fg_cuda_context *c, const fg_cuda_sample_args *a, bool shard,
@@ -507,7 +509,12 @@ static fg_status check_batch(const fg_cuda_context *c, const fg_cuda_sample_args
             fg_error_set(err, FG_ERR_ARGUMENT, "invalid sampler controls");
             return FG_ERR_ARGUMENT;
         }
-        if (fg_sampler_penalties_active(cfg)) traits->penalties = true;
+        if (fg_sampler_penalties_active(cfg)) {
+            traits->penalties = true;
+            if (!(cfg->presence_penalty >= 0.0f && cfg->frequency_penalty >= 0.0f &&
+                  cfg->repetition_penalty >= 1.0f && cfg->repetition_penalty <= 0x1p40f))
+                traits->raising = true;
+        }
         if (cfg->frequency_penalty != 0.0f) traits->counts = true;
         if (cfg->temperature != 0.0f) {
             traits->sampled = true;
@@ -627,34 +634,32 @@ static fg_status run_stream(fg_cuda_context *c, const fg_cuda_sample_args *a,
     l.count_capacity = plan.count_capacity;
     l.dense_wide = plan.dense_wide;
     fill_output(&l.out, c, a);
-    /* Rows the copy engine can fetch (16-byte aligned row starts, at least one whole
-     * tile after the first) go through the shared-memory ring; the rest, and anything
-     * the caller pinned to it, through the register-prefetch kernel. */
+    /* Whole rows the copy engine can fetch (16-byte aligned starts and lengths) whose
+     * penalties cannot raise a logit may go through the persistent ring kernel; the
+     * rest, and anything the caller pinned to it, through the register-prefetch kernel. */
     const size_t element = a->dtype == FG_CUDA_BF16 ? 2u : 4u;
+    const uint32_t whole_bitmap = traits->penalties ? (a->vocab + 31u) / 32u : 0u;
     const bool ring_ok = ((uintptr_t)a->logits % 16u) == 0u && (a->row_stride * element) % 16u == 0u &&
-                         plan.split_len >= 2u * fgk_stream_tile();
+                         ((size_t)a->vocab * element) % 16u == 0u && c->forced_splits <= 1u &&
+                         !(traits->penalties && traits->raising) &&
+                         fgk_persistent_dynamic_smem(whole_bitmap) <= FGK_PERSIST_MAX_DYNAMIC_SMEM;
     if (c->path == FG_CUDA_PATH_RING && !ring_ok) {
-        fg_error_set(err, FG_ERR_ARGUMENT, "the ring path needs 16-byte aligned rows of at least two tiles");
+        fg_error_set(err, FG_ERR_ARGUMENT,
+                     "the ring path needs whole 16-byte aligned rows and penalties that only lower logits");
         return FG_ERR_ARGUMENT;
     }
     /* measured on B200 the register-prefetch kernel is currently the faster one, so it
      * is also what AUTO picks */
     if (ring_ok && (c->path == FG_CUDA_PATH_RING || c->path == FG_CUDA_PATH_RING_IF_POSSIBLE)) {
-        if (traits->penalties) {
-            const size_t stride_words = plan.dynamic_smem / 4u;
-            const size_t history_bytes = slots * stride_words * 4u;
-            const size_t meta_at = (size_t)fg_align_up_u64(history_bytes, 256u);
-            status = fg_cuda_reserve(&c->history, &c->history_bytes, meta_at + slots * 8u, false, c, err);
-            if (status != FG_OK) return status;
-            l.history_global = c->history;
-            l.history_stride_words = stride_words;
-            l.history_meta = (unsigned char *)c->history + meta_at;
-            c->last_scratch_bytes += meta_at + slots * 8u;
-        }
-        uint32_t launched = 0;
-        const int e = fgk_launch_ring_select(&l, c->stream, &launched);
-        c->launches += launched;
-        return e ? fg_cuda_fail(err, e, "ring select kernels") : FG_OK;
+        l.splits = 1u;
+        l.split_len = a->vocab;
+        l.bitmap_words = whole_bitmap;
+        uint32_t per_sm = fgk_persistent_ctas_per_sm(a->dtype, fgk_persistent_dynamic_smem(whole_bitmap));
+        if (per_sm == 0u) per_sm = 1u;
+        const uint32_t most = c->sm_count * per_sm;
+        const int e = fgk_launch_persistent_select(&l, a->rows < most ? a->rows : most, c->stream);
+        c->launches++;
+        return e ? fg_cuda_fail(err, e, "persistent ring kernel") : FG_OK;
     }
     const int e = fgk_launch_stream_select(&l, c->stream);
     c->launches++;
