@@ -128,6 +128,9 @@ struct Shared {
     uint32_t overflow;               // a value found no slot in one of the lists
     uint32_t ring_error;             // a bounded wait ran out
     uint32_t first_key;              // tile 0: the smallest of the warps' j-th largest keys
+    uint32_t attention;              // a list is long or full: every warp comes to attend()
+    uint32_t warps_done;             // warps that have finished the row's tiles
+    uint32_t row_closed;             // the last meeting found them all there
 };
 
 // What the consumers need to know about the row; lives in registers.
@@ -148,60 +151,69 @@ __device__ __forceinline__ bool bounded_wait(uint64_t *barrier, uint32_t parity)
     return false;
 }
 
-// One element that the vector test could not rule out.  kPair compares with the
-// bound as a (score, id) pair -- always right once a cut has produced the pair --
-// otherwise only the score is compared: strictly for tiles after the one(s) the
-// bound came from (their ids are larger, a tie loses), inclusively for tile 0.
-// Returns true when a list wants a cut.
-template <bool kGreedy, bool kPair>
+// Shared words that warps watch while others change them.
+__device__ __forceinline__ uint32_t peek(const uint32_t *word) {
+    return *reinterpret_cast<const volatile uint32_t *>(word);
+}
+__device__ __forceinline__ void poke(uint32_t *word, uint32_t value) {
+    *reinterpret_cast<volatile uint32_t *>(word) = value;
+}
+
+// One element whose raw value reaches the bound.  The bound is a (score, id) pair:
+// the k-th best of some earlier state of the candidate list (or, before the first
+// cut, tile 0's first bound with the padding id, which every id precedes).  What does
+// not precede it can never be among the k best, in whatever order the warps run.
+// Returns false when the list the element belongs on is full (the caller asks for a
+// cut and offers the element again).
+template <bool kGreedy>
 __device__ __forceinline__ bool consider(Shared &sh, const Row &r, float x, uint32_t id, bool seen,
-                                         float tau, uint32_t tau_id, bool inclusive) {
+                                         float tau, uint32_t tau_id) {
     if (seen) {
         const float bound = penalise_with_offset(x, r.flat_offset, r.repetition);
         if (r.with_counts) {
             // the charge grows with the count, so `bound` is the most the id can keep
-            const bool alive = (kPair || inclusive) ? bound >= tau : bound > tau;
+            const bool alive = bound >= tau;
             // greedy rows must also see NaN/Inf, raw or made by the penalty
             const bool wild = kGreedy && (__float_as_uint(x) & 0x7fffffffu) >= 0x6b000000u;
-            if (!(alive || wild)) return false;
+            if (!(alive || wild)) return true;
             const uint32_t slot = atomicAdd(&sh.defer_count, 1u);
-            if (slot < (uint32_t)kDeferCap) {
-                sh.defer_raw[slot] = x;
-                sh.defer_id[slot] = id;
-            } else {
-                sh.overflow = 1;
-            }
-            return slot >= (uint32_t)kDeferCap / 2;
+            if (slot >= (uint32_t)kDeferCap) return false;
+            sh.defer_raw[slot] = x;
+            sh.defer_id[slot] = id;
+            if (slot >= (uint32_t)kDeferCap / 2) poke(&sh.attention, 1u);
+            return true;
         }
         x = bound;
     }
     if (is_nonfinite(x)) {
         if (kGreedy) atomicMin(&sh.wild_key, ((unsigned long long)id << 32) | __float_as_uint(x));
-        return false;
+        return true;
     }
-    const bool take = kPair ? precedes(x, id, tau, tau_id) : (inclusive ? x >= tau : x > tau);
-    if (!take) return false;
+    if (!precedes(x, id, tau, tau_id)) return true;
     const uint32_t slot = atomicAdd(&sh.cand.count, 1u);
-    if (slot < (uint32_t)kCandCap) {
-        sh.cand.score[slot] = x;
-        sh.cand.id[slot] = id;
-    } else {
-        sh.overflow = 1;
-    }
-    return slot >= r.cut_at;
+    if (slot >= (uint32_t)kCandCap) return false;
+    sh.cand.score[slot] = x;
+    sh.cand.id[slot] = id;
+    if (slot >= r.cut_at) poke(&sh.attention, 1u);
+    return true;
 }
 
-// The lists want attention.  Ids that were put aside get their occurrences counted in
-// the row's token list and their exact penalised value, and join the candidates if they
-// precede the bound; then the candidate list is cut back to its k best, which lifts the
-// bound.  Every consumer calls it; returns the new bound's score (the pair is in
-// sh.cand.tau_*).
+// The meeting of all consumer warps.  A warp comes here when it sees sh.attention
+// up or when one of its lanes found a list full (it then raises the flag itself); the
+// last warp to finish the row's tiles raises it for the closing meeting.  Nobody appends to a list while the meeting is
+// on.  Ids that were put aside get their occurrences counted in the row's token list
+// and their exact penalised value, and join the candidates if they precede the bound;
+// a long candidate list is cut back to its k best, which lifts the bound.  When all
+// warps have finished the row everything is settled and the k best are exact.
+// Returns the bound's score (the pair is in sh.cand.tau_*).
 __device__ __noinline__ float attend(Shared &sh, const Row r) {
     const uint32_t tid = threadIdx.x, lane = tid & 31u;
     CB::sync();
-    const uint32_t aside = min(sh.defer_count, (uint32_t)kDeferCap);
+    const bool closing = sh.warps_done == (uint32_t)kConsumerWarps;
+    uint32_t aside = min(sh.defer_count, (uint32_t)kDeferCap);
     uint32_t held = min(sh.cand.count, (uint32_t)kCandCap);
     CB::sync();  // everyone has read the counts before anything rewrites them
+    if (!closing && aside < (uint32_t)kDeferCap / 2) aside = 0;  // not worth a pass yet
     if (aside != 0) {
         if (held + aside > (uint32_t)kCandCap) {  // make room first
             compact_topk<kConsumers, kCandCap, CB>(sh.cand, held, r.k);
@@ -248,99 +260,13 @@ __device__ __noinline__ float attend(Shared &sh, const Row r) {
         held = min(sh.cand.count, (uint32_t)kCandCap);
         CB::sync();
     }
-    compact_topk<kConsumers, kCandCap, CB>(sh.cand, held, r.k);
-    return sh.cand.tau_score;
-}
-
-// Bits of the row's bitmap that belong to vector `g` of the tile starting at bitmap
-// word `tile_word` (tiles start on a word boundary, vectors never straddle one).
-template <typename T>
-__device__ __forceinline__ uint32_t seen_bits(const uint32_t *bitmap, uint32_t tile_word, uint32_t g) {
-    constexpr int kPer = Lanes<T>::kPer;
-    const uint32_t column = g * kPer;
-    return (bitmap[tile_word + (column >> 5)] >> (column & 31u)) & ((1u << kPer) - 1u);
-}
-
-// A tile pushed more values than a list could take (sorted or constant rows do that,
-// or a row whose first tile gave no bound).  Take back what the tile stored, then feed
-// it again from the ring one element per thread at a time with a cut before each, so
-// that no list can overflow: k + 256 <= kCandCap, 256 <= kDeferCap.  The bound may now
-// come from this very tile, so everything is compared as a pair.  Every consumer calls
-// it; returns the new bound.
-template <typename T>
-__device__ __noinline__ float redo_tile(Shared &sh, const uint32_t *bitmap, const uint4 *stage,
-                                        uint32_t t, uint32_t valid_vectors, const Row r) {
-    using L = Lanes<T>;
-    constexpr int kPer = L::kPer;
-    constexpr uint32_t kTile = kStageBytes / sizeof(T);
-    static_assert(kMaxK + kConsumers <= kCandCap && kConsumers <= kDeferCap, "a slice always fits");
-    constexpr int PER = kCandCap / kConsumers;
-    const uint32_t tid = threadIdx.x;
-    const uint32_t first_id = r.id_base + t * kTile;
-
-    CB::sync();
-    const uint32_t held = min(sh.cand.count, (uint32_t)kCandCap);
-    const uint32_t aside = min(sh.defer_count, (uint32_t)kDeferCap);
-    float score[PER];
-    uint32_t id[PER];
-#pragma unroll
-    for (int j = 0; j < PER; j++) {
-        const uint32_t at = j * kConsumers + tid;
-        id[j] = kPaddingId;
-        score[j] = 0.0f;
-        if (at < held) {
-            score[j] = sh.cand.score[at];
-            id[j] = sh.cand.id[at];
-        }
-    }
-    float aside_raw = 0.0f;
-    uint32_t aside_id = kPaddingId;
-    if (tid < aside) {
-        aside_raw = sh.defer_raw[tid];
-        aside_id = sh.defer_id[tid];
-    }
-    CB::sync();
+    if (closing || held >= r.cut_at) compact_topk<kConsumers, kCandCap, CB>(sh.cand, held, r.k);
     if (tid == 0) {
-        sh.cand.count = 0;
-        sh.defer_count = 0;
-        sh.overflow = 0;
+        sh.attention = 0;
+        sh.row_closed = closing ? 1u : 0u;
     }
     CB::sync();
-#pragma unroll
-    for (int j = 0; j < PER; j++) {
-        if (id[j] != kPaddingId && id[j] - first_id >= kTile) {  // not from this tile
-            const uint32_t slot = atomicAdd(&sh.cand.count, 1u);
-            sh.cand.score[slot] = score[j];
-            sh.cand.id[slot] = id[j];
-        }
-    }
-    if (aside_id != kPaddingId && aside_id - first_id >= kTile) {
-        const uint32_t slot = atomicAdd(&sh.defer_count, 1u);
-        sh.defer_raw[slot] = aside_raw;
-        sh.defer_id[slot] = aside_id;
-    }
-    const uint32_t tile_word = t * (kTile / 32);
-    for (int u = 0; u < kVectors; u++) {
-        const uint32_t g = u * kConsumers + tid;
-        float v[kPer];
-        uint32_t bits = 0;
-        const bool live = g < valid_vectors;
-        if (live) {
-            L::unpack(stage[g], v);
-            if (r.seen_any) bits = seen_bits<T>(bitmap, tile_word, g);
-        }
-#pragma unroll
-        for (int j = 0; j < kPer; j++) {
-            const float tau = attend(sh, r);
-            const uint32_t tau_id = sh.cand.tau_id;
-            if (live) {
-                const uint32_t element_id = first_id + g * kPer + j;
-                if (r.greedy) consider<true, true>(sh, r, v[j], element_id, (bits >> j) & 1u, tau, tau_id, true);
-                else consider<false, true>(sh, r, v[j], element_id, (bits >> j) & 1u, tau, tau_id, true);
-            }
-        }
-    }
-    return attend(sh, r);
+    return sh.cand.tau_score;
 }
 
 // Position in the ring; the copy warp and the consumers count tiles the same way.
@@ -354,38 +280,81 @@ struct RingCursor {
     }
 };
 
-constexpr uint32_t kNeedsAttention = 0x80000000u;
-
-// Tile 0 of a row: every element is looked at.  The first bound is the smallest, over
-// the eight warps, of each warp's j-th largest per-thread maximum of unseen finite
-// values, j = ceil(k / 8): at least k distinct elements are that large.  (No bound when
-// some warp has fewer than j such threads; the tile then overflows the list and is fed
-// again in slices.)  Returns the bound; sh.overflow tells whether a list ran over.
+// One logit of a tile in the ring, by its position in the tile.
 template <typename T>
-__device__ __noinline__ float first_tile(Shared &sh, const uint32_t *bitmap, const uint4 *stage,
+__device__ __forceinline__ float tile_element(const unsigned char *stage, uint32_t position);
+template <>
+__device__ __forceinline__ float tile_element<float>(const unsigned char *stage, uint32_t position) {
+    return reinterpret_cast<const float *>(stage)[position];
+}
+template <>
+__device__ __forceinline__ float tile_element<uint16_t>(const unsigned char *stage, uint32_t position) {
+    return __uint_as_float((uint32_t)reinterpret_cast<const uint16_t *>(stage)[position] << 16);
+}
+
+// Offers this lane's pending elements of a tile (bit e = element e % kPer of its vector
+// e / kPer) to the lists, re-reading them from the ring.  Stops at the first one that
+// finds no room; returns what is left.
+template <typename T, bool kGreedy>
+__device__ __forceinline__ uint32_t offer(Shared &sh, const Row &r, const uint32_t *bitmap,
+                                          const unsigned char *stage, uint32_t t, uint32_t pending,
+                                          float tau, uint32_t tau_id) {
+    constexpr int kPer = Lanes<T>::kPer;
+    constexpr uint32_t kTile = kStageBytes / sizeof(T);
+    while (pending != 0) {
+        const uint32_t e = __ffs(pending) - 1;
+        const uint32_t position = ((e / kPer) * kConsumers + threadIdx.x) * kPer + (e % kPer);
+        const uint32_t column = t * kTile + position;
+        const bool seen = r.seen_any && ((bitmap[column >> 5] >> (column & 31u)) & 1u);
+        if (!consider<kGreedy>(sh, r, tile_element<T>(stage, position), r.id_base + column, seen, tau,
+                               tau_id))
+            break;
+        pending &= pending - 1;
+    }
+    return pending;
+}
+
+// Offers until nothing is pending in the warp, meeting the other warps for a cut
+// whenever a list is full.  All lanes of the warp call it together; returns the bound.
+template <typename T, bool kGreedy>
+__device__ __noinline__ float settle(Shared &sh, const Row r, const uint32_t *bitmap,
+                                     const unsigned char *stage, uint32_t t, uint32_t pending,
+                                     float tau) {
+    for (;;) {
+        pending = offer<T, kGreedy>(sh, r, bitmap, stage, t, pending, tau, sh.cand.tau_id);
+        if (!__any_sync(kFullMask, pending != 0)) return tau;
+        poke(&sh.attention, 1u);
+        tau = attend(sh, r);
+    }
+}
+
+// Tile 0 of a row, all warps together: every element is looked at.  The first bound is
+// the smallest, over the warps, of each warp's j-th largest per-thread maximum of
+// unseen finite values, j = ceil(k / warps): at least k distinct elements are that
+// large.  (No bound when some warp has fewer than j such threads; everything finite
+// is then a candidate until the first cut.)  Returns the bound.
+template <typename T>
+__device__ __noinline__ float first_tile(Shared &sh, const uint32_t *bitmap, const unsigned char *stage,
                                          uint32_t valid_vectors, const Row r) {
     using L = Lanes<T>;
     constexpr int kPer = L::kPer;
     const uint32_t tid = threadIdx.x, lane = tid & 31u;
-    float v[kVectors][kPer];
-    uint32_t bits[kVectors];
+    const uint4 *vectors = reinterpret_cast<const uint4 *>(stage);
     float best = __uint_as_float(0xff800000u);
     bool have = false;
 #pragma unroll
     for (int u = 0; u < kVectors; u++) {
         const uint32_t g = u * kConsumers + tid;
-        bits[u] = 0;
-        if (g < valid_vectors) {
-            L::unpack(stage[g], v[u]);
-            if (r.seen_any) bits[u] = seen_bits<T>(bitmap, 0, g);
-        } else {
-#pragma unroll
-            for (int j = 0; j < kPer; j++) v[u][j] = __uint_as_float(0xff800000u);
-        }
+        if (g >= valid_vectors) continue;
+        float v[kPer];
+        L::unpack(vectors[g], v);
+        const uint32_t column = g * kPer;
+        const uint32_t bits =
+            r.seen_any ? (bitmap[column >> 5] >> (column & 31u)) & ((1u << kPer) - 1u) : 0u;
 #pragma unroll
         for (int j = 0; j < kPer; j++) {
-            if (!((bits[u] >> j) & 1u) && !is_nonfinite(v[u][j])) {
-                best = fmaxf(best, v[u][j]);
+            if (!((bits >> j) & 1u) && !is_nonfinite(v[j])) {
+                best = fmaxf(best, v[j]);
                 have = true;
             }
         }
@@ -406,83 +375,108 @@ __device__ __noinline__ float first_tile(Shared &sh, const uint32_t *bitmap, con
         sh.cand.tau_score = tau;
         sh.cand.tau_id = kPaddingId;
     }
+    CB::sync();
+    // everything that reaches the bound raw is offered (greedy rows: and every NaN/Inf
+    // or huge magnitude)
+    uint32_t pending = 0;
 #pragma unroll
     for (int u = 0; u < kVectors; u++) {
         const uint32_t g = u * kConsumers + tid;
         if (g >= valid_vectors) continue;
+        float v[kPer];
+        L::unpack(vectors[g], v);
 #pragma unroll
         for (int j = 0; j < kPer; j++) {
-            const uint32_t id = r.id_base + g * kPer + j;
-            if (r.greedy) consider<true, false>(sh, r, v[u][j], id, (bits[u] >> j) & 1u, tau, kPaddingId, true);
-            else consider<false, false>(sh, r, v[u][j], id, (bits[u] >> j) & 1u, tau, kPaddingId, true);
+            const bool wild = r.greedy && (__float_as_uint(v[j]) & 0x7fffffffu) >= 0x6b000000u;
+            if (v[j] >= tau || wild) pending |= 1u << (u * kPer + j);
         }
     }
-    return tau;
+    return r.greedy ? settle<T, true>(sh, r, bitmap, stage, 0, pending, tau)
+                    : settle<T, false>(sh, r, bitmap, stage, 0, pending, tau);
 }
 
-// The hot loop over tiles first .. tiles-1 of a row.  Calls nothing: whatever is live
-// across a call inside a loop is saved and restored on every trip.  When a list wants
-// attention the loop stops with the stage still held (the caller may have to read the
-// tile again) and says so in the top bit of the tile number it returns.
+// What hot_tiles hands back: the tile it stopped at, why, and this lane's elements of
+// that tile still to be offered.
+constexpr uint32_t kStopDone = 0, kStopBefore = 1, kStopInside = 2;
+struct Stop {
+    uint32_t tile, why, pending;
+};
+
+// The hot loop of one warp over tiles first .. tiles-1 of a row; the warps run it
+// independently of one another, at most a ring's depth apart.  It calls nothing:
+// whatever is live across a call inside a loop is saved and restored on every trip.
+//   kStopBefore  the attention flag is up and the warp has not touched `tile` yet
+//   kStopInside  a lane found a list full; `pending` holds its elements of `tile`
+//                still to be offered, and the warp still holds the stage
 template <typename T, bool kGreedy>
-__device__ __noinline__ uint32_t hot_tiles(Shared &sh, const uint32_t *bitmap, const unsigned char *ring,
-                                           uint32_t first, uint32_t tiles, uint32_t last_vectors,
-                                           const uint32_t row_sequence, const Row r, const float tau) {
+__device__ __noinline__ Stop hot_tiles(Shared &sh, const uint32_t *bitmap, const unsigned char *ring,
+                                       uint32_t first, uint32_t tiles, uint32_t last_vectors,
+                                       const uint32_t row_sequence, const Row r, const float tau) {
     using L = Lanes<T>;
     constexpr int kPer = L::kPer;
-    constexpr uint32_t kTile = kStageBytes / sizeof(T);
-    const uint32_t tid = threadIdx.x;
+    const uint32_t tid = threadIdx.x, lane = tid & 31u;
+    const uint32_t tau_id = sh.cand.tau_id;
+    Stop stop;
+    stop.pending = 0;
     for (uint32_t t = first; t < tiles; t++) {
         const uint32_t at = (row_sequence + t) % kStages, use = (row_sequence + t) / kStages;
-        if (!sh.ring_error && !bounded_wait(&sh.full[at], use & 1u)) sh.ring_error = 1;
-        const uint4 *stage = reinterpret_cast<const uint4 *>(ring + (size_t)at * kStageBytes);
+        stop.tile = t;
+        // ---- wait for the tile, watching the flag ----
+        for (uint32_t polls = 0;; polls++) {
+            if (__any_sync(kFullMask, peek(&sh.attention) != 0)) {
+                stop.why = kStopBefore;
+                return stop;
+            }
+            const bool landed = peek(&sh.ring_error) != 0 || mbarrier_try_wait(&sh.full[at], use & 1u);
+            if (__all_sync(kFullMask, landed)) break;
+            if (polls >= kWaitPolls) poke(&sh.ring_error, 1u);  // values are then garbage; the row fails
+        }
+        const unsigned char *stage = ring + (size_t)at * kStageBytes;
+        const uint4 *vectors = reinterpret_cast<const uint4 *>(stage);
         const uint32_t valid_vectors = t + 1 == tiles ? last_vectors : kStageBytes / 16u;
-        const uint32_t tile_word = t * (kTile / 32);
-        bool want = false;
         uint4 raw[kVectors];
-#ifdef FGK_EXPERIMENT_NO_COMPUTE
-        if (valid_vectors == 12345u) want = stage[tid].x == 77u;
-        if (CB::sync_or(want)) return t | kNeedsAttention;
-        if (tid == 0) mbarrier_arrive(&sh.empty[at]);
-        continue;
-#endif
 #pragma unroll
         for (int u = 0; u < kVectors; u++) {
             const uint32_t g = u * kConsumers + tid;
-            raw[u] = g < valid_vectors ? stage[g]
+            // the filler reads as a NaN in fp32 and as -inf in bf16: never reaches a bound
+            raw[u] = g < valid_vectors ? vectors[g]
                                        : make_uint4(0xff80ff80u, 0xff80ff80u, 0xff80ff80u, 0xff80ff80u);
         }
+        float v[kVectors * kPer];
 #pragma unroll
-        for (int u = 0; u < kVectors; u++) {
-            float v[kPer];
-            L::unpack(raw[u], v);
-            float top = v[0];  // NaN never compares above the bound
+        for (int u = 0; u < kVectors; u++) L::unpack(raw[u], &v[u * kPer]);
+        float top = v[0];  // a NaN never wins a maximum
 #pragma unroll
-            for (int j = 1; j < kPer; j++) top = fmaxf(top, v[j]);
-            bool hot = top > tau;
-            if (kGreedy) {  // the argmax order must see NaN and both infinities, and
-                            // magnitudes a repetition factor of at most 2^40 could push there
-                uint32_t widest = 0;
+        for (int e = 1; e < kVectors * kPer; e++) top = fmaxf(top, v[e]);
+        bool hot = top >= tau;
+        if (kGreedy) {  // the argmax order must see NaN and both infinities, and magnitudes
+                        // a repetition factor of at most 2^40 could push there
+            uint32_t widest = 0;
 #pragma unroll
-                for (int j = 0; j < kPer; j++) widest = max(widest, __float_as_uint(v[j]) & 0x7fffffffu);
-                hot = hot || widest >= 0x6b000000u;
-            }
-            const uint32_t g = u * kConsumers + tid;
-            if (hot && g < valid_vectors) {
-                const uint32_t bits = r.seen_any ? seen_bits<T>(bitmap, tile_word, g) : 0u;
-                const uint32_t first_id = r.id_base + t * kTile + g * kPer;
-#pragma unroll
-                for (int j = 0; j < kPer; j++)
-                    want |= consider<kGreedy, false>(sh, r, v[j], first_id + j, (bits >> j) & 1u, tau,
-                                                     kPaddingId, false);
-            }
+            for (int e = 0; e < kVectors * kPer; e++) widest = max(widest, __float_as_uint(v[e]) & 0x7fffffffu);
+            hot = hot || widest >= 0x6b000000u;
         }
-        // (the filler past the row's end reads as a NaN in fp32 and as -inf in bf16: never
-        // above the bound, and the test on g keeps greedy rows from looking at it)
-        if (CB::sync_or(want)) return t | kNeedsAttention;
-        if (tid == 0) mbarrier_arrive(&sh.empty[at]);
+        uint32_t pending = 0;
+        if (hot) {
+#pragma unroll
+            for (int e = 0; e < kVectors * kPer; e++) {
+                const bool live = (e / kPer) * kConsumers + tid < valid_vectors;
+                const bool wild = kGreedy && (__float_as_uint(v[e]) & 0x7fffffffu) >= 0x6b000000u;
+                if (live && (v[e] >= tau || wild)) pending |= 1u << e;
+            }
+            pending = offer<T, kGreedy>(sh, r, bitmap, stage, t, pending, tau, tau_id);
+        }
+        if (__any_sync(kFullMask, pending != 0)) {
+            stop.why = kStopInside;
+            stop.pending = pending;
+            return stop;
+        }
+        // the warp is done with the stage
+        if (lane == 0) mbarrier_arrive(&sh.empty[at]);
     }
-    return tiles - 1;
+    stop.tile = tiles;
+    stop.why = kStopDone;
+    return stop;
 }
 
 // Phase 1 of a row: bitmap of the history ids that fall into this kernel's columns.
@@ -520,8 +514,7 @@ __device__ __noinline__ void build_bitmap(Shared &sh, uint32_t *bitmap, const Pa
 __device__ __noinline__ void finish_row(Shared &sh, const Params &p, uint32_t row, const Row r,
                                         const SamplerConfig cfg, bool shard_mode) {
     const uint32_t tid = threadIdx.x;
-    attend(sh, r);  // counts what was put aside and leaves the k best
-    const uint32_t held = min(sh.cand.count, r.k);
+    const uint32_t held = min(sh.cand.count, r.k);  // the closing meeting left the k best
     uint32_t bad_history = sh.bad_history;
     if (sh.ring_error) bad_history = kErrLimit;  // a tile never landed
     const uint32_t wild_id = (uint32_t)(sh.wild_key >> 32);  // the padding id when nothing was seen
@@ -602,7 +595,7 @@ persistent_select_kernel(const __grid_constant__ Params p) {
 #pragma unroll
         for (int s = 0; s < kStages; s++) {
             mbarrier_init(&sh.full[s], 1);
-            mbarrier_init(&sh.empty[s], 1);
+            mbarrier_init(&sh.empty[s], kConsumerWarps);
         }
         mbarrier_fence_init();
         sh.ring_error = 0;
@@ -646,6 +639,7 @@ persistent_select_kernel(const __grid_constant__ Params p) {
     }
 
     // -------------------------------------------------------------------- consumers
+    const uint32_t lane = tid & 31u;
     uint32_t row_sequence = 0;  // tiles of earlier rows: tile t of this row is ring tile row_sequence + t
     for (uint32_t row = blockIdx.x; row < p.rows; row += gridDim.x) {
         const SamplerConfig cfg = p.config_count > 1 ? p.configs[row] : p.config0;
@@ -687,38 +681,56 @@ persistent_select_kernel(const __grid_constant__ Params p) {
             sh.defer_count = 0;
             sh.bad_history = bad_history;
             sh.wild_key = ~0ull;
-            sh.overflow = 0;
             sh.first_key = 0xffffffffu;
+            sh.attention = 0;
+            sh.warps_done = 0;
+            sh.row_closed = 0;
         }
         if (r.seen_any) build_bitmap(sh, bitmap, p, r);
         else CB::sync();
 
         const uint32_t last_vectors = (row_bytes - (tiles - 1) * kStageBytes) / 16u;
-        // ---- tile 0 ----
+        // ---- tile 0, all warps together ----
         const uint32_t at0 = row_sequence % kStages;
-        if (!sh.ring_error && !bounded_wait(&sh.full[at0], (row_sequence / kStages) & 1u)) sh.ring_error = 1;
-        const uint4 *stage0 = reinterpret_cast<const uint4 *>(ring + (size_t)at0 * kStageBytes);
-        const uint32_t vectors0 = tiles == 1 ? last_vectors : kStageBytes / 16u;
-        float tau = first_tile<T>(sh, bitmap, stage0, vectors0, r);
-        CB::sync();
-        if (sh.overflow) tau = redo_tile<T>(sh, bitmap, stage0, 0, vectors0, r);
-        if (tid == 0) mbarrier_arrive(&sh.empty[at0]);
+        if (!peek(&sh.ring_error) && !bounded_wait(&sh.full[at0], (row_sequence / kStages) & 1u))
+            poke(&sh.ring_error, 1u);
+        float tau = first_tile<T>(sh, bitmap, ring + (size_t)at0 * kStageBytes,
+                                  tiles == 1 ? last_vectors : kStageBytes / 16u, r);
+        __syncwarp();
+        if (lane == 0) mbarrier_arrive(&sh.empty[at0]);
 
-        // ---- tiles 1 .. ----
+        // ---- tiles 1 .. : each warp at its own pace ----
         for (uint32_t t = 1; t < tiles;) {
-            const uint32_t stopped =
+            const Stop stop =
                 r.greedy ? hot_tiles<T, true>(sh, bitmap, ring, t, tiles, last_vectors, row_sequence, r, tau)
                          : hot_tiles<T, false>(sh, bitmap, ring, t, tiles, last_vectors, row_sequence, r, tau);
-            t = (stopped & ~kNeedsAttention) + 1;
-            if (stopped & kNeedsAttention) {
-                const uint32_t at = (row_sequence + t - 1) % kStages;
-                if (sh.overflow) {
-                    const uint4 *stage = reinterpret_cast<const uint4 *>(ring + (size_t)at * kStageBytes);
-                    tau = redo_tile<T>(sh, bitmap, stage, t - 1, t == tiles ? last_vectors : kStageBytes / 16u, r);
-                } else {
-                    tau = attend(sh, r);
-                }
-                if (tid == 0) mbarrier_arrive(&sh.empty[at]);
+            if (stop.why == kStopDone) break;
+            t = stop.tile;
+            if (stop.why == kStopBefore) {
+                tau = attend(sh, r);
+                continue;
+            }
+            const uint32_t at = (row_sequence + t) % kStages;
+            const unsigned char *stage = ring + (size_t)at * kStageBytes;
+            tau = r.greedy ? settle<T, true>(sh, r, bitmap, stage, t, stop.pending, tau)
+                           : settle<T, false>(sh, r, bitmap, stage, t, stop.pending, tau);
+            __syncwarp();
+            if (lane == 0) mbarrier_arrive(&sh.empty[at]);
+            t++;
+        }
+        // ---- the end of the row ----
+        // A warp that is through keeps answering calls to attend(); the last one through
+        // calls the closing meeting.  (It must not call meetings itself while it waits: a
+        // warp still streaming would see the flag before every tile and never move.)
+        __syncwarp();
+        uint32_t through = 0;
+        if (lane == 0) through = atomicAdd(&sh.warps_done, 1u) + 1u;
+        through = __shfl_sync(kFullMask, through, 0);
+        if (through == (uint32_t)kConsumerWarps) poke(&sh.attention, 1u);
+        for (;;) {
+            if (__any_sync(kFullMask, peek(&sh.attention) != 0)) {
+                attend(sh, r);
+                if (peek(&sh.row_closed)) break;
             }
         }
         finish_row(sh, p, row, r, cfg, shard_mode);
