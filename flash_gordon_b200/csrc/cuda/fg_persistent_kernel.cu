@@ -43,7 +43,7 @@ namespace persist {
 constexpr int kStages = FGK_PERSIST_STAGES;
 constexpr int kConsumers = 256;
 constexpr int kConsumerWarps = kConsumers / 32;
-constexpr int kBlock = kConsumers + 32;  // + the copy warp
+constexpr int kBlock = kConsumers + 64;  // + the copy warp and the closing warp
 constexpr uint32_t kStageBytes = 16384;
 constexpr int kVectors = 4;              // 128-bit vectors per consumer thread and tile
 constexpr int kCandCap = 1024;
@@ -114,23 +114,31 @@ struct Params {
     SelectOutput out;
 };
 
-struct Shared {
+// What the consumers collect for one row.  There are two of these: while the closing
+// warp turns one row's lists into its result the consumers fill the other.
+struct Lists {
     CandidateBuffer<kCandCap> cand;
-    FinishBuffer fin;
     float defer_raw[kDeferCap];      // raw logit of an id put aside
     uint32_t defer_id[kDeferCap];
     uint32_t defer_seen[kDeferCap];  // its occurrences in the history, once counted
-    alignas(8) uint64_t full[kStages];   // "the tile has landed"
-    alignas(8) uint64_t empty[kStages];  // "the consumers are done with the stage"
     unsigned long long wild_key;     // greedy rows: min over NaN/Inf of (id << 32 | value bits)
     uint32_t defer_count;
     uint32_t bad_history;
-    uint32_t overflow;               // a value found no slot in one of the lists
+};
+
+struct Shared {
+    Lists lists[2];
+    FinishBuffer fin;                    // the closing warp's
+    uint32_t closer_hist[256];
+    uint32_t closer_count;
+    alignas(8) uint64_t full[kStages];   // "the tile has landed"
+    alignas(8) uint64_t empty[kStages];  // "the consumers are done with the stage"
+    alignas(8) uint64_t ready[2];        // "the row's lists are complete"
+    alignas(8) uint64_t vacant[2];       // "the closing warp is done with the lists"
+    uint32_t through[2];             // warps that have finished the row's tiles, by row parity
     uint32_t ring_error;             // a bounded wait ran out
     uint32_t first_key;              // tile 0: the smallest of the warps' j-th largest keys
     uint32_t attention;              // a list is long or full: every warp comes to attend()
-    uint32_t warps_done;             // warps that have finished the row's tiles
-    uint32_t row_closed;             // the last meeting found them all there
 };
 
 // What the consumers need to know about the row; lives in registers.
@@ -166,7 +174,7 @@ __device__ __forceinline__ void poke(uint32_t *word, uint32_t value) {
 // Returns false when the list the element belongs on is full (the caller asks for a
 // cut and offers the element again).
 template <bool kGreedy>
-__device__ __forceinline__ bool consider(Shared &sh, const Row &r, float x, uint32_t id, bool seen,
+__device__ __forceinline__ bool consider(Shared &sh, Lists &L, const Row &r, float x, uint32_t id, bool seen,
                                          float tau, uint32_t tau_id) {
     if (seen) {
         const float bound = penalise_with_offset(x, r.flat_offset, r.repetition);
@@ -176,50 +184,47 @@ __device__ __forceinline__ bool consider(Shared &sh, const Row &r, float x, uint
             // greedy rows must also see NaN/Inf, raw or made by the penalty
             const bool wild = kGreedy && (__float_as_uint(x) & 0x7fffffffu) >= 0x6b000000u;
             if (!(alive || wild)) return true;
-            const uint32_t slot = atomicAdd(&sh.defer_count, 1u);
+            const uint32_t slot = atomicAdd(&L.defer_count, 1u);
             if (slot >= (uint32_t)kDeferCap) return false;
-            sh.defer_raw[slot] = x;
-            sh.defer_id[slot] = id;
+            L.defer_raw[slot] = x;
+            L.defer_id[slot] = id;
             if (slot >= (uint32_t)kDeferCap / 2) poke(&sh.attention, 1u);
             return true;
         }
         x = bound;
     }
     if (is_nonfinite(x)) {
-        if (kGreedy) atomicMin(&sh.wild_key, ((unsigned long long)id << 32) | __float_as_uint(x));
+        if (kGreedy) atomicMin(&L.wild_key, ((unsigned long long)id << 32) | __float_as_uint(x));
         return true;
     }
     if (!precedes(x, id, tau, tau_id)) return true;
-    const uint32_t slot = atomicAdd(&sh.cand.count, 1u);
+    const uint32_t slot = atomicAdd(&L.cand.count, 1u);
     if (slot >= (uint32_t)kCandCap) return false;
-    sh.cand.score[slot] = x;
-    sh.cand.id[slot] = id;
+    L.cand.score[slot] = x;
+    L.cand.id[slot] = id;
     if (slot >= r.cut_at) poke(&sh.attention, 1u);
     return true;
 }
 
 // The meeting of all consumer warps.  A warp comes here when it sees sh.attention
-// up or when one of its lanes found a list full (it then raises the flag itself); the
-// last warp to finish the row's tiles raises it for the closing meeting.  Nobody appends to a list while the meeting is
-// on.  Ids that were put aside get their occurrences counted in the row's token list
+// up or when one of its lanes found a list full (it then raises the flag itself).
+// Nobody appends to a list while the meeting is on.  Ids that were put aside get their occurrences counted in the row's token list
 // and their exact penalised value, and join the candidates if they precede the bound;
-// a long candidate list is cut back to its k best, which lifts the bound.  When all
-// warps have finished the row everything is settled and the k best are exact.
-// Returns the bound's score (the pair is in sh.cand.tau_*).
-__device__ __noinline__ float attend(Shared &sh, const Row r) {
+// a long candidate list is cut back to its k best, which lifts the bound.
+// Returns the bound's score (the pair is in L.cand.tau_*).
+__device__ __noinline__ float attend(Shared &sh, Lists &L, const Row r) {
     const uint32_t tid = threadIdx.x, lane = tid & 31u;
     CB::sync();
-    const bool closing = sh.warps_done == (uint32_t)kConsumerWarps;
-    uint32_t aside = min(sh.defer_count, (uint32_t)kDeferCap);
-    uint32_t held = min(sh.cand.count, (uint32_t)kCandCap);
+    uint32_t aside = min(L.defer_count, (uint32_t)kDeferCap);
+    uint32_t held = min(L.cand.count, (uint32_t)kCandCap);
     CB::sync();  // everyone has read the counts before anything rewrites them
-    if (!closing && aside < (uint32_t)kDeferCap / 2) aside = 0;  // not worth a pass yet
+    if (aside < (uint32_t)kDeferCap / 2) aside = 0;  // not worth a pass yet
     if (aside != 0) {
         if (held + aside > (uint32_t)kCandCap) {  // make room first
-            compact_topk<kConsumers, kCandCap, CB>(sh.cand, held, r.k);
+            compact_topk<kConsumers, kCandCap, CB>(L.cand, held, r.k);
             held = min(held, r.k);
         }
-        if (tid < aside) sh.defer_seen[tid] = 0;
+        if (tid < aside) L.defer_seen[tid] = 0;
         CB::sync();
         constexpr int kBatch = 8;
         for (uint32_t base = 0; base < r.history_len; base += kBatch * kConsumers) {
@@ -230,43 +235,40 @@ __device__ __noinline__ float attend(Shared &sh, const Row r) {
                 token[q] = i < r.history_len ? r.tokens[i] : kPaddingId;  // the padding id is nobody's
             }
             for (uint32_t d = 0; d < aside; d++) {
-                const uint32_t id = sh.defer_id[d];
+                const uint32_t id = L.defer_id[d];
                 uint32_t hits = 0;
 #pragma unroll
                 for (int q = 0; q < kBatch; q++) hits += token[q] == id ? 1u : 0u;
                 hits = __reduce_add_sync(kFullMask, hits);
-                if (lane == 0 && hits != 0) atomicAdd(&sh.defer_seen[d], hits);
+                if (lane == 0 && hits != 0) atomicAdd(&L.defer_seen[d], hits);
             }
         }
         CB::sync();
-        const float tau = sh.cand.tau_score;
-        const uint32_t tau_id = sh.cand.tau_id;
+        const float tau = L.cand.tau_score;
+        const uint32_t tau_id = L.cand.tau_id;
         if (tid < aside) {
-            const uint32_t id = sh.defer_id[tid];
+            const uint32_t id = L.defer_id[tid];
             const float x = penalise_with_offset(
-                sh.defer_raw[tid], penalty_offset(sh.defer_seen[tid], r.presence, r.frequency),
+                L.defer_raw[tid], penalty_offset(L.defer_seen[tid], r.presence, r.frequency),
                 r.repetition);
             if (is_nonfinite(x)) {
                 if (r.greedy)
-                    atomicMin(&sh.wild_key, ((unsigned long long)id << 32) | __float_as_uint(x));
+                    atomicMin(&L.wild_key, ((unsigned long long)id << 32) | __float_as_uint(x));
             } else if (precedes(x, id, tau, tau_id)) {
-                const uint32_t slot = atomicAdd(&sh.cand.count, 1u);  // room was made above
-                sh.cand.score[slot] = x;
-                sh.cand.id[slot] = id;
+                const uint32_t slot = atomicAdd(&L.cand.count, 1u);  // room was made above
+                L.cand.score[slot] = x;
+                L.cand.id[slot] = id;
             }
         }
         CB::sync();
-        if (tid == 0) sh.defer_count = 0;
-        held = min(sh.cand.count, (uint32_t)kCandCap);
+        if (tid == 0) L.defer_count = 0;
+        held = min(L.cand.count, (uint32_t)kCandCap);
         CB::sync();
     }
-    if (closing || held >= r.cut_at) compact_topk<kConsumers, kCandCap, CB>(sh.cand, held, r.k);
-    if (tid == 0) {
-        sh.attention = 0;
-        sh.row_closed = closing ? 1u : 0u;
-    }
+    if (held >= r.cut_at) compact_topk<kConsumers, kCandCap, CB>(L.cand, held, r.k);
+    if (tid == 0) sh.attention = 0;
     CB::sync();
-    return sh.cand.tau_score;
+    return L.cand.tau_score;
 }
 
 // Position in the ring; the copy warp and the consumers count tiles the same way.
@@ -296,7 +298,7 @@ __device__ __forceinline__ float tile_element<uint16_t>(const unsigned char *sta
 // e / kPer) to the lists, re-reading them from the ring.  Stops at the first one that
 // finds no room; returns what is left.
 template <typename T, bool kGreedy>
-__device__ __forceinline__ uint32_t offer(Shared &sh, const Row &r, const uint32_t *bitmap,
+__device__ __forceinline__ uint32_t offer(Shared &sh, Lists &L, const Row &r, const uint32_t *bitmap,
                                           const unsigned char *stage, uint32_t t, uint32_t pending,
                                           float tau, uint32_t tau_id) {
     constexpr int kPer = Lanes<T>::kPer;
@@ -306,7 +308,7 @@ __device__ __forceinline__ uint32_t offer(Shared &sh, const Row &r, const uint32
         const uint32_t position = ((e / kPer) * kConsumers + threadIdx.x) * kPer + (e % kPer);
         const uint32_t column = t * kTile + position;
         const bool seen = r.seen_any && ((bitmap[column >> 5] >> (column & 31u)) & 1u);
-        if (!consider<kGreedy>(sh, r, tile_element<T>(stage, position), r.id_base + column, seen, tau,
+        if (!consider<kGreedy>(sh, L, r, tile_element<T>(stage, position), r.id_base + column, seen, tau,
                                tau_id))
             break;
         pending &= pending - 1;
@@ -317,14 +319,14 @@ __device__ __forceinline__ uint32_t offer(Shared &sh, const Row &r, const uint32
 // Offers until nothing is pending in the warp, meeting the other warps for a cut
 // whenever a list is full.  All lanes of the warp call it together; returns the bound.
 template <typename T, bool kGreedy>
-__device__ __noinline__ float settle(Shared &sh, const Row r, const uint32_t *bitmap,
+__device__ __noinline__ float settle(Shared &sh, Lists &L, const Row r, const uint32_t *bitmap,
                                      const unsigned char *stage, uint32_t t, uint32_t pending,
                                      float tau) {
     for (;;) {
-        pending = offer<T, kGreedy>(sh, r, bitmap, stage, t, pending, tau, sh.cand.tau_id);
+        pending = offer<T, kGreedy>(sh, L, r, bitmap, stage, t, pending, tau, L.cand.tau_id);
         if (!__any_sync(kFullMask, pending != 0)) return tau;
         poke(&sh.attention, 1u);
-        tau = attend(sh, r);
+        tau = attend(sh, L, r);
     }
 }
 
@@ -334,10 +336,10 @@ __device__ __noinline__ float settle(Shared &sh, const Row r, const uint32_t *bi
 // large.  (No bound when some warp has fewer than j such threads; everything finite
 // is then a candidate until the first cut.)  Returns the bound.
 template <typename T>
-__device__ __noinline__ float first_tile(Shared &sh, const uint32_t *bitmap, const unsigned char *stage,
+__device__ __noinline__ float first_tile(Shared &sh, Lists &L, const uint32_t *bitmap, const unsigned char *stage,
                                          uint32_t valid_vectors, const Row r) {
-    using L = Lanes<T>;
-    constexpr int kPer = L::kPer;
+    using V = Lanes<T>;
+    constexpr int kPer = V::kPer;
     const uint32_t tid = threadIdx.x, lane = tid & 31u;
     const uint4 *vectors = reinterpret_cast<const uint4 *>(stage);
     float best = __uint_as_float(0xff800000u);
@@ -347,7 +349,7 @@ __device__ __noinline__ float first_tile(Shared &sh, const uint32_t *bitmap, con
         const uint32_t g = u * kConsumers + tid;
         if (g >= valid_vectors) continue;
         float v[kPer];
-        L::unpack(vectors[g], v);
+        V::unpack(vectors[g], v);
         const uint32_t column = g * kPer;
         const uint32_t bits =
             r.seen_any ? (bitmap[column >> 5] >> (column & 31u)) & ((1u << kPer) - 1u) : 0u;
@@ -372,8 +374,8 @@ __device__ __noinline__ float first_tile(Shared &sh, const uint32_t *bitmap, con
     CB::sync();
     const float tau = key_to_float(sh.first_key);
     if (tid == 0) {
-        sh.cand.tau_score = tau;
-        sh.cand.tau_id = kPaddingId;
+        L.cand.tau_score = tau;
+        L.cand.tau_id = kPaddingId;
     }
     CB::sync();
     // everything that reaches the bound raw is offered (greedy rows: and every NaN/Inf
@@ -384,15 +386,15 @@ __device__ __noinline__ float first_tile(Shared &sh, const uint32_t *bitmap, con
         const uint32_t g = u * kConsumers + tid;
         if (g >= valid_vectors) continue;
         float v[kPer];
-        L::unpack(vectors[g], v);
+        V::unpack(vectors[g], v);
 #pragma unroll
         for (int j = 0; j < kPer; j++) {
             const bool wild = r.greedy && (__float_as_uint(v[j]) & 0x7fffffffu) >= 0x6b000000u;
             if (v[j] >= tau || wild) pending |= 1u << (u * kPer + j);
         }
     }
-    return r.greedy ? settle<T, true>(sh, r, bitmap, stage, 0, pending, tau)
-                    : settle<T, false>(sh, r, bitmap, stage, 0, pending, tau);
+    return r.greedy ? settle<T, true>(sh, L, r, bitmap, stage, 0, pending, tau)
+                    : settle<T, false>(sh, L, r, bitmap, stage, 0, pending, tau);
 }
 
 // What hot_tiles hands back: the tile it stopped at, why, and this lane's elements of
@@ -409,13 +411,13 @@ struct Stop {
 //   kStopInside  a lane found a list full; `pending` holds its elements of `tile`
 //                still to be offered, and the warp still holds the stage
 template <typename T, bool kGreedy>
-__device__ __noinline__ Stop hot_tiles(Shared &sh, const uint32_t *bitmap, const unsigned char *ring,
+__device__ __noinline__ Stop hot_tiles(Shared &sh, Lists &L, const uint32_t *bitmap, const unsigned char *ring,
                                        uint32_t first, uint32_t tiles, uint32_t last_vectors,
                                        const uint32_t row_sequence, const Row r, const float tau) {
-    using L = Lanes<T>;
-    constexpr int kPer = L::kPer;
+    using V = Lanes<T>;
+    constexpr int kPer = V::kPer;
     const uint32_t tid = threadIdx.x, lane = tid & 31u;
-    const uint32_t tau_id = sh.cand.tau_id;
+    const uint32_t tau_id = L.cand.tau_id;
     Stop stop;
     stop.pending = 0;
     for (uint32_t t = first; t < tiles; t++) {
@@ -444,7 +446,7 @@ __device__ __noinline__ Stop hot_tiles(Shared &sh, const uint32_t *bitmap, const
         }
         float v[kVectors * kPer];
 #pragma unroll
-        for (int u = 0; u < kVectors; u++) L::unpack(raw[u], &v[u * kPer]);
+        for (int u = 0; u < kVectors; u++) V::unpack(raw[u], &v[u * kPer]);
         float top = v[0];  // a NaN never wins a maximum
 #pragma unroll
         for (int e = 1; e < kVectors * kPer; e++) top = fmaxf(top, v[e]);
@@ -464,7 +466,7 @@ __device__ __noinline__ Stop hot_tiles(Shared &sh, const uint32_t *bitmap, const
                 const bool wild = kGreedy && (__float_as_uint(v[e]) & 0x7fffffffu) >= 0x6b000000u;
                 if (live && (v[e] >= tau || wild)) pending |= 1u << e;
             }
-            pending = offer<T, kGreedy>(sh, r, bitmap, stage, t, pending, tau, tau_id);
+            pending = offer<T, kGreedy>(sh, L, r, bitmap, stage, t, pending, tau, tau_id);
         }
         if (__any_sync(kFullMask, pending != 0)) {
             stop.why = kStopInside;
@@ -480,8 +482,8 @@ __device__ __noinline__ Stop hot_tiles(Shared &sh, const uint32_t *bitmap, const
 }
 
 // Phase 1 of a row: bitmap of the history ids that fall into this kernel's columns.
-// Returns false (and the status in sh.bad_history) when the history is unusable.
-__device__ __noinline__ void build_bitmap(Shared &sh, uint32_t *bitmap, const Params &p, const Row r) {
+// A token outside the vocabulary leaves its status in L.bad_history.
+__device__ __noinline__ void build_bitmap(Lists &L, uint32_t *bitmap, const Params &p, const Row r) {
     const uint32_t tid = threadIdx.x;
     uint4 *wide = reinterpret_cast<uint4 *>(bitmap);
     const uint32_t quads = (p.bitmap_words + 3u) / 4u;  // the host rounds the allocation up
@@ -498,7 +500,7 @@ __device__ __noinline__ void build_bitmap(Shared &sh, uint32_t *bitmap, const Pa
 #pragma unroll
         for (int q = 0; q < kBatch; q++) {
             if (base + q * kConsumers + tid >= r.history_len) continue;
-            if (token[q] >= p.vocab_total) sh.bad_history = kErrFormat;
+            if (token[q] >= p.vocab_total) L.bad_history = kErrFormat;
             const uint32_t local = token[q] - p.vocab_offset;  // wraps for ids below the span
             if (local < p.vocab) {
                 const uint32_t bit = 1u << (local & 31u);
@@ -509,40 +511,194 @@ __device__ __noinline__ void build_bitmap(Shared &sh, uint32_t *bitmap, const Pa
     CB::sync();
 }
 
-// Phase 4: the row's result from the candidate list (shard candidates, the greedy
-// winner, or the select step of src/sampler.c:80-122).  Every consumer calls it.
-__device__ __noinline__ void finish_row(Shared &sh, const Params &p, uint32_t row, const Row r,
-                                        const SamplerConfig cfg, bool shard_mode) {
-    const uint32_t tid = threadIdx.x;
-    const uint32_t held = min(sh.cand.count, r.k);  // the closing meeting left the k best
-    uint32_t bad_history = sh.bad_history;
-    if (sh.ring_error) bad_history = kErrLimit;  // a tile never landed
-    const uint32_t wild_id = (uint32_t)(sh.wild_key >> 32);  // the padding id when nothing was seen
-    const uint32_t wild_bits = (uint32_t)sh.wild_key;
+// ------------------------------------------------------------------ closing warp
+//
+// When the consumers are through with a row they leave its lists behind and go on
+// with the next row on the other pair of lists; this warp turns the lists into the
+// row's result: it counts the occurrences of the ids still put aside, takes the exact
+// k best of both lists (MSB-first radix select over the 64-bit (score, ~id) keys,
+// 8-bit digits, the warp's own histogram), sorts them and runs the select step of
+// src/sampler.c:80-122.
 
-    if (shard_mode) {
-        sort_candidates<kCandCap, CB>(sh.cand, sh.fin, held);
-        if (tid < r.k) {
-            const size_t at = (size_t)row * r.k + tid;
-            const bool live = tid < held && !bad_history;
-            p.shard_scores[at] = live ? sh.fin.score[tid] : __uint_as_float(0xff800000u);
-            p.shard_ids[at] = live ? sh.fin.id[tid] : kPaddingId;
+// Key of entry i of the row's lists (candidates first, then the ids that were put
+// aside, whose defer_raw by now holds the exact penalised value); 0 = no entry.
+__device__ __forceinline__ uint64_t list_key(const Lists &L, uint32_t held, uint32_t i) {
+    if (i < held) return select_key(L.cand.score[i], L.cand.id[i]);
+    const uint32_t d = i - held;
+    return L.defer_id[d] == kPaddingId ? 0ull : select_key(L.defer_raw[d], L.defer_id[d]);
+}
+
+__device__ __noinline__ void close_row(Shared &sh, Lists &L, const Params &p, uint32_t row, const Row r,
+                                       const SamplerConfig cfg, bool shard_mode) {
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t held = min(L.cand.count, (uint32_t)kCandCap);
+    const uint32_t aside = min(L.defer_count, (uint32_t)kDeferCap);
+
+    // ---- exact values of the ids put aside ----
+    if (aside != 0) {
+        for (uint32_t d = lane; d < aside; d += 32) L.defer_seen[d] = 0;
+        __syncwarp();
+        constexpr int kBatch = 8;
+        for (uint32_t base = 0; base < r.history_len; base += kBatch * 32) {
+            uint32_t token[kBatch];
+#pragma unroll
+            for (int q = 0; q < kBatch; q++) {
+                const uint32_t i = base + q * 32 + lane;
+                token[q] = i < r.history_len ? r.tokens[i] : kPaddingId;
+            }
+            for (uint32_t d = 0; d < aside; d++) {
+                const uint32_t id = L.defer_id[d];
+                uint32_t hits = 0;
+#pragma unroll
+                for (int q = 0; q < kBatch; q++) hits += token[q] == id ? 1u : 0u;
+                hits = __reduce_add_sync(kFullMask, hits);
+                if (lane == 0) L.defer_seen[d] += hits;
+            }
         }
-        if (tid == 0) {
+        __syncwarp();
+        for (uint32_t d = lane; d < aside; d += 32) {
+            const uint32_t id = L.defer_id[d];
+            const float x = penalise_with_offset(
+                L.defer_raw[d], penalty_offset(L.defer_seen[d], r.presence, r.frequency), r.repetition);
+            if (is_nonfinite(x)) {
+                if (r.greedy) atomicMin(&L.wild_key, ((unsigned long long)id << 32) | __float_as_uint(x));
+                L.defer_id[d] = kPaddingId;
+            } else {
+                L.defer_raw[d] = x;
+            }
+        }
+        __syncwarp();
+    }
+
+    // ---- the k best of held + aside entries ----
+    const uint32_t entries = held + aside;
+    uint32_t live = 0;
+    for (uint32_t i = lane; i < entries; i += 32) live += list_key(L, held, i) != 0 ? 1u : 0u;
+    live = __reduce_add_sync(kFullMask, live);
+    const uint32_t keep = min(live, r.k);
+    uint64_t prefix = 0;
+    int shift = 64;  // keys whose bits above `shift` exceed `prefix` are in; equal ones fill up
+    uint32_t need = keep;
+    if (live > r.k) {
+        shift = 56;
+        for (int pass = 0; pass < 8; pass++) {
+            for (uint32_t b = lane; b < 256; b += 32) sh.closer_hist[b] = 0;
+            __syncwarp();
+            for (uint32_t i = lane; i < entries; i += 32) {
+                const uint64_t key = list_key(L, held, i);
+                if (key != 0 && (pass == 0 || (key >> (shift + 8)) == prefix))
+                    atomicAdd(&sh.closer_hist[(key >> shift) & 255u], 1u);
+            }
+            __syncwarp();
+            // lane l owns digits 255-8l .. 248-8l, walked from the top
+            uint32_t mine = 0;
+#pragma unroll
+            for (int b = 0; b < 8; b++) mine += sh.closer_hist[255 - 8 * lane - b];
+            uint32_t incl = mine;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const uint32_t up = __shfl_up_sync(kFullMask, incl, d);
+                if (lane >= (uint32_t)d) incl += up;
+            }
+            const unsigned reached = __ballot_sync(kFullMask, incl >= need);
+            const int owner = __ffs(reached) - 1;  // need <= live, so some lane reaches it
+            uint32_t digit = 0, rest = 0, bucket = 0;
+            if ((int)lane == owner) {
+                uint32_t above = incl - mine;
+                for (int b = 0; b < 8; b++) {
+                    const uint32_t candidate = 255 - 8 * lane - b;
+                    const uint32_t here = sh.closer_hist[candidate];
+                    if (above + here >= need) {
+                        digit = candidate;
+                        rest = need - above;
+                        bucket = here;
+                        break;
+                    }
+                    above += here;
+                }
+            }
+            digit = __shfl_sync(kFullMask, digit, owner);
+            rest = __shfl_sync(kFullMask, rest, owner);
+            bucket = __shfl_sync(kFullMask, bucket, owner);
+            prefix = (prefix << 8) | digit;
+            need = rest;
+            __syncwarp();
+            if (bucket == need || shift == 0) break;
+            shift -= 8;
+        }
+    }
+    // unsorted survivors go to the far end of the work arrays, the sort brings them forward
+    float *loose_score = reinterpret_cast<float *>(sh.fin.raw);
+    uint32_t *loose_id = reinterpret_cast<uint32_t *>(sh.fin.tempered);
+    if (lane == 0) sh.closer_count = 0;
+    __syncwarp();
+    for (uint32_t i = lane; i < entries; i += 32) {
+        const uint64_t key = list_key(L, held, i);
+        if (key == 0) continue;
+        // shift == 64: everything live is kept; otherwise compare the examined bits
+        const bool take = shift == 64 || (key >> shift) >= prefix;
+        if (take) {
+            const uint32_t slot = atomicAdd(&sh.closer_count, 1u);
+            if (slot < (uint32_t)kMaxK) {
+                const bool from_cand = i < held;
+                loose_score[slot] = from_cand ? L.cand.score[i] : L.defer_raw[i - held];
+                loose_id[slot] = from_cand ? L.cand.id[i] : L.defer_id[i - held];
+            }
+        }
+    }
+    __syncwarp();
+    const uint32_t kept = min(sh.closer_count, keep);
+    float my_score[2];
+    uint32_t my_id[2], my_rank[2];
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+        const uint32_t e = lane + 32 * h;
+        my_rank[h] = kPaddingId;
+        if (e < kept) {
+            my_score[h] = loose_score[e];
+            my_id[h] = loose_id[e];
+            uint32_t rank = 0;
+            for (uint32_t j = 0; j < kept; j++) rank += precedes(loose_score[j], loose_id[j], my_score[h], my_id[h]) ? 1u : 0u;
+            my_rank[h] = rank;
+        }
+    }
+    __syncwarp();
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+        if (my_rank[h] != kPaddingId) {
+            sh.fin.score[my_rank[h]] = my_score[h];
+            sh.fin.id[my_rank[h]] = my_id[h];
+        }
+    }
+    __syncwarp();
+
+    // ---- the row's result ----
+    uint32_t bad_history = L.bad_history;
+    if (peek(&sh.ring_error)) bad_history = kErrLimit;  // a tile never landed
+    const uint32_t wild_id = (uint32_t)(L.wild_key >> 32);  // the padding id when nothing was seen
+    const uint32_t wild_bits = (uint32_t)L.wild_key;
+    if (shard_mode) {
+        for (uint32_t i = lane; i < r.k; i += 32) {
+            const size_t at = (size_t)row * r.k + i;
+            const bool ok = i < kept && !bad_history;
+            p.shard_scores[at] = ok ? sh.fin.score[i] : __uint_as_float(0xff800000u);
+            p.shard_ids[at] = ok ? sh.fin.id[i] : kPaddingId;
+        }
+        if (lane == 0) {
             p.out.row_status[row] = bad_history;
             if (bad_history) atomicMin(p.out.first_error, ((unsigned long long)row << 8) | bad_history);
         }
         return;
     }
     if (bad_history) {  // "history token ... is outside vocabulary", src/output.c:610-612
-        if (tid == 0) {
+        if (lane == 0) {
             report_row(p.out, row, bad_history, kPaddingId, 0.0f);
             if (p.out.dbg_count) p.out.dbg_count[row] = 0;
         }
         return;
     }
     if (r.greedy) {
-        if (tid == 0) {
+        if (lane == 0) {
             uint32_t status = kOk, token;
             float logit;
             if (wild_id != kPaddingId) {
@@ -551,13 +707,13 @@ __device__ __noinline__ void finish_row(Shared &sh, const Params &p, uint32_t ro
                 status = penalties_active(cfg) ? kErrFormat : kErrMismatch;
                 token = wild_id;
                 logit = __uint_as_float(wild_bits);
-            } else if (held == 0) {
+            } else if (kept == 0) {
                 status = kErrMismatch;
                 token = kPaddingId;
                 logit = 0.0f;
             } else {
-                token = sh.cand.id[0];
-                logit = sh.cand.score[0];
+                token = sh.fin.id[0];
+                logit = sh.fin.score[0];
             }
             report_row(p.out, row, status, token, logit);
             if (p.out.dbg_count) {
@@ -569,8 +725,57 @@ __device__ __noinline__ void finish_row(Shared &sh, const Params &p, uint32_t ro
         }
         return;
     }
-    sort_candidates<kCandCap, CB>(sh.cand, sh.fin, held);
-    if (tid < 32) finish_select(sh.fin, held, cfg, p.uniforms[row], row, p.out);
+    finish_select(sh.fin, kept, cfg, p.uniforms[row], row, p.out);
+}
+
+#ifdef FGK_PHASE_CLOCKS
+__device__ unsigned long long fgk_persist_clocks[8];
+#define FGK_PTICK(slot)                                                            \
+    do {                                                                            \
+        if (threadIdx.x == 0) {                                                     \
+            const long long now = clock64();                                        \
+            atomicAdd(&fgk_persist_clocks[slot], (unsigned long long)(now - tick)); \
+            tick = now;                                                             \
+        }                                                                           \
+    } while (0)
+#else
+#define FGK_PTICK(slot) do { } while (0)
+#endif
+
+// The row as the consumers and the closing warp see it; *bad_history is the status a
+// broken history earns the row (0 when it is fine).
+__device__ __forceinline__ Row make_row(const Params &p, const SamplerConfig &cfg, uint32_t row,
+                                        bool shard_mode, uint32_t *bad_history) {
+    Row r;
+    r.greedy = !shard_mode && cfg.temperature == 0.0f;
+    r.k = shard_mode ? p.shard_k : (r.greedy ? 1u : cfg.top_k);
+    r.cut_at = 4 * r.k + 64;
+    r.id_base = p.vocab_offset;
+    r.flat_offset = penalty_offset(1u, cfg.presence_penalty, cfg.frequency_penalty);
+    r.presence = cfg.presence_penalty;
+    r.frequency = cfg.frequency_penalty;
+    r.repetition = make_repetition(cfg.repetition_penalty);
+    r.tokens = nullptr;
+    r.history_len = 0;
+    *bad_history = 0;
+    if (p.history_tokens != nullptr && p.history_offsets != nullptr && p.bitmap_words != 0 &&
+        penalties_active(cfg)) {
+        const uint64_t begin = p.history_offsets[row], end = p.history_offsets[row + 1];
+        if (end < begin || end - begin > p.history_max) {
+            *bad_history = kErrLimit;
+        } else {
+            r.tokens = p.history_tokens + begin;
+            r.history_len = (uint32_t)(end - begin);
+        }
+    }
+    r.seen_any = r.history_len != 0;
+    r.with_counts = r.seen_any && cfg.frequency_penalty != 0.0f;
+    // the host sends only rows whose penalties cannot raise a logit; a row that
+    // slipped through is failed rather than sampled wrongly
+    if (r.seen_any && !(cfg.presence_penalty >= 0.0f && cfg.frequency_penalty >= 0.0f &&
+                        cfg.repetition_penalty >= 1.0f && r.repetition.tame))
+        *bad_history = kErrLimit;
+    return r;
 }
 
 // Does this kernel sample the row, or is it left to the kernel without a top-k cut?
@@ -597,11 +802,35 @@ persistent_select_kernel(const __grid_constant__ Params p) {
             mbarrier_init(&sh.full[s], 1);
             mbarrier_init(&sh.empty[s], kConsumerWarps);
         }
+        for (int b = 0; b < 2; b++) {
+            mbarrier_init(&sh.ready[b], 1);
+            mbarrier_init(&sh.vacant[b], 1);
+        }
         mbarrier_fence_init();
         sh.ring_error = 0;
     }
     __syncthreads();
 
+    if (tid >= (uint32_t)kConsumers + 32u) {
+        // ------------------------------------------------------------- closing warp
+        uint32_t served = 0;
+        for (uint32_t row = blockIdx.x; row < p.rows; row += gridDim.x) {
+            const SamplerConfig cfg = p.config_count > 1 ? p.configs[row] : p.config0;
+            if (!row_is_ours(cfg, shard_mode)) continue;
+            uint32_t bad_history;
+            const Row r = make_row(p, cfg, row, shard_mode, &bad_history);
+            const uint32_t b = served & 1u;
+            // (a wait that runs out leaves garbage lists: the row is failed through ring_error)
+            if (!peek(&sh.ring_error) && !bounded_wait(&sh.ready[b], (served >> 1) & 1u))
+                poke(&sh.ring_error, 1u);
+            __syncwarp();
+            close_row(sh, sh.lists[b], p, row, r, cfg, shard_mode);
+            __syncwarp();
+            if ((tid & 31u) == 0) mbarrier_arrive(&sh.vacant[b]);
+            served++;
+        }
+        return;
+    }
     if (tid >= (uint32_t)kConsumers) {
         // ---------------------------------------------------------------- copy warp
         if (tid != (uint32_t)kConsumers) return;
@@ -641,101 +870,94 @@ persistent_select_kernel(const __grid_constant__ Params p) {
     // -------------------------------------------------------------------- consumers
     const uint32_t lane = tid & 31u;
     uint32_t row_sequence = 0;  // tiles of earlier rows: tile t of this row is ring tile row_sequence + t
+    uint32_t served = 0;        // rows before this one
+#ifdef FGK_PHASE_CLOCKS
+    long long tick = clock64();
+#endif
     for (uint32_t row = blockIdx.x; row < p.rows; row += gridDim.x) {
         const SamplerConfig cfg = p.config_count > 1 ? p.configs[row] : p.config0;
         if (!row_is_ours(cfg, shard_mode)) continue;
-        Row r;
-        r.greedy = !shard_mode && cfg.temperature == 0.0f;
-        r.k = shard_mode ? p.shard_k : (r.greedy ? 1u : cfg.top_k);
-        r.cut_at = 4 * r.k + 64;
-        r.id_base = p.vocab_offset;
-        r.flat_offset = penalty_offset(1u, cfg.presence_penalty, cfg.frequency_penalty);
-        r.presence = cfg.presence_penalty;
-        r.frequency = cfg.frequency_penalty;
-        r.repetition = make_repetition(cfg.repetition_penalty);
-        r.tokens = nullptr;
-        r.history_len = 0;
-        uint32_t bad_history = 0;
-        if (p.history_tokens != nullptr && p.history_offsets != nullptr && p.bitmap_words != 0 &&
-            penalties_active(cfg)) {
-            const uint64_t begin = p.history_offsets[row], end = p.history_offsets[row + 1];
-            if (end < begin || end - begin > p.history_max) {
-                bad_history = kErrLimit;
-            } else {
-                r.tokens = p.history_tokens + begin;
-                r.history_len = (uint32_t)(end - begin);
-            }
-        }
-        r.seen_any = r.history_len != 0;
-        r.with_counts = r.seen_any && cfg.frequency_penalty != 0.0f;
-        // the host sends only rows whose penalties cannot raise a logit; a row that
-        // slipped through is failed rather than sampled wrongly
-        if (r.seen_any && !(cfg.presence_penalty >= 0.0f && cfg.frequency_penalty >= 0.0f &&
-                            cfg.repetition_penalty >= 1.0f && r.repetition.tame))
-            bad_history = kErrLimit;
-
+        uint32_t bad_history;
+        const Row r = make_row(p, cfg, row, shard_mode, &bad_history);
+        const uint32_t b = served & 1u;
+        Lists &L = sh.lists[b];
+        // the closing warp must be done with these lists (it had them two rows ago)
+        if (served >= 2u && !peek(&sh.ring_error) && !bounded_wait(&sh.vacant[b], ((served >> 1) - 1u) & 1u))
+            poke(&sh.ring_error, 1u);
         if (tid == 0) {
-            sh.cand.count = 0;
-            sh.cand.tau_score = __uint_as_float(0xff800000u);
-            sh.cand.tau_id = kPaddingId;
-            sh.defer_count = 0;
-            sh.bad_history = bad_history;
-            sh.wild_key = ~0ull;
+            L.cand.count = 0;
+            L.cand.tau_score = __uint_as_float(0xff800000u);
+            L.cand.tau_id = kPaddingId;
+            L.defer_count = 0;
+            L.bad_history = bad_history;
+            L.wild_key = ~0ull;
             sh.first_key = 0xffffffffu;
             sh.attention = 0;
-            sh.warps_done = 0;
-            sh.row_closed = 0;
+            sh.through[b] = 0;
         }
-        if (r.seen_any) build_bitmap(sh, bitmap, p, r);
+        FGK_PTICK(5);
+        if (r.seen_any) build_bitmap(L, bitmap, p, r);
         else CB::sync();
+        FGK_PTICK(0);
 
         const uint32_t last_vectors = (row_bytes - (tiles - 1) * kStageBytes) / 16u;
         // ---- tile 0, all warps together ----
         const uint32_t at0 = row_sequence % kStages;
         if (!peek(&sh.ring_error) && !bounded_wait(&sh.full[at0], (row_sequence / kStages) & 1u))
             poke(&sh.ring_error, 1u);
-        float tau = first_tile<T>(sh, bitmap, ring + (size_t)at0 * kStageBytes,
+        float tau = first_tile<T>(sh, L, bitmap, ring + (size_t)at0 * kStageBytes,
                                   tiles == 1 ? last_vectors : kStageBytes / 16u, r);
         __syncwarp();
         if (lane == 0) mbarrier_arrive(&sh.empty[at0]);
+        FGK_PTICK(1);
 
         // ---- tiles 1 .. : each warp at its own pace ----
         for (uint32_t t = 1; t < tiles;) {
             const Stop stop =
-                r.greedy ? hot_tiles<T, true>(sh, bitmap, ring, t, tiles, last_vectors, row_sequence, r, tau)
-                         : hot_tiles<T, false>(sh, bitmap, ring, t, tiles, last_vectors, row_sequence, r, tau);
+                r.greedy ? hot_tiles<T, true>(sh, L, bitmap, ring, t, tiles, last_vectors, row_sequence, r, tau)
+                         : hot_tiles<T, false>(sh, L, bitmap, ring, t, tiles, last_vectors, row_sequence, r, tau);
             if (stop.why == kStopDone) break;
             t = stop.tile;
             if (stop.why == kStopBefore) {
-                tau = attend(sh, r);
+                FGK_PTICK(2);
+                tau = attend(sh, L, r);
+                FGK_PTICK(3);
+#ifdef FGK_PHASE_CLOCKS
+                if (tid == 0) atomicAdd(&fgk_persist_clocks[7], 1ull);
+#endif
                 continue;
             }
             const uint32_t at = (row_sequence + t) % kStages;
             const unsigned char *stage = ring + (size_t)at * kStageBytes;
-            tau = r.greedy ? settle<T, true>(sh, r, bitmap, stage, t, stop.pending, tau)
-                           : settle<T, false>(sh, r, bitmap, stage, t, stop.pending, tau);
+            tau = r.greedy ? settle<T, true>(sh, L, r, bitmap, stage, t, stop.pending, tau)
+                           : settle<T, false>(sh, L, r, bitmap, stage, t, stop.pending, tau);
             __syncwarp();
             if (lane == 0) mbarrier_arrive(&sh.empty[at]);
             t++;
         }
+        FGK_PTICK(2);
         // ---- the end of the row ----
-        // A warp that is through keeps answering calls to attend(); the last one through
-        // calls the closing meeting.  (It must not call meetings itself while it waits: a
-        // warp still streaming would see the flag before every tile and never move.)
+        // A call to attend() that is up must be answered by every warp, so a warp answers
+        // what it sees before it counts itself through, and keeps answering until all
+        // eight are through: from then on nobody can call.  The last one through hands
+        // the lists to the closing warp.
+        while (__any_sync(kFullMask, peek(&sh.attention) != 0)) attend(sh, L, r);
+        __threadfence_block();
         __syncwarp();
         uint32_t through = 0;
-        if (lane == 0) through = atomicAdd(&sh.warps_done, 1u) + 1u;
+        if (lane == 0) through = atomicAdd(&sh.through[b], 1u) + 1u;
         through = __shfl_sync(kFullMask, through, 0);
-        if (through == (uint32_t)kConsumerWarps) poke(&sh.attention, 1u);
-        for (;;) {
-            if (__any_sync(kFullMask, peek(&sh.attention) != 0)) {
-                attend(sh, r);
-                if (peek(&sh.row_closed)) break;
+        if (through == (uint32_t)kConsumerWarps) {
+            if (lane == 0) mbarrier_arrive(&sh.ready[b]);
+        } else {
+            for (;;) {
+                if (__any_sync(kFullMask, peek(&sh.attention) != 0)) attend(sh, L, r);
+                else if (__any_sync(kFullMask, peek(&sh.through[b]) == (uint32_t)kConsumerWarps)) break;
             }
         }
-        finish_row(sh, p, row, r, cfg, shard_mode);
-        CB::sync();  // the lists are free for the next row
+        FGK_PTICK(4);
         row_sequence += tiles;
+        served++;
     }
 }
 
@@ -743,6 +965,17 @@ persistent_select_kernel(const __grid_constant__ Params p) {
 }  // namespace fgk
 
 // ------------------------------------------------------------------ host side
+
+#ifdef FGK_PHASE_CLOCKS
+extern "C" int fgk_read_persist_clocks(unsigned long long *out, int reset) {
+    cudaError_t e = cudaMemcpyFromSymbol(out, fgk::persist::fgk_persist_clocks, sizeof(unsigned long long) * 8);
+    if (e == cudaSuccess && reset) {
+        unsigned long long zero[8] = {0};
+        e = cudaMemcpyToSymbol(fgk::persist::fgk_persist_clocks, zero, sizeof(zero));
+    }
+    return (int)e;
+}
+#endif
 
 using namespace fgk;
 
