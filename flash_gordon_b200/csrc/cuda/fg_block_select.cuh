@@ -206,30 +206,31 @@ __device__ inline void finish_select(FinishBuffer &fin, uint32_t n, const Sample
     const double top_raw = (double)fin.score[0];
     for (uint32_t i = lane; i < n; i += 32) fin.raw[i] = exp((double)fin.score[i] - top_raw);
     __syncwarp();
-    if (lane == 0) {
-        uint32_t status = kOk;
-        double raw_sum = 0.0;
+    // the sums run left to right on one lane, as the C code's loops do; the divisions
+    // are independent of one another and spread over the warp
+    double raw_sum = 0.0;
+    if (lane == 0)
         for (uint32_t i = 0; i < n; i++) raw_sum += fin.raw[i];
+    raw_sum = __shfl_sync(kFullMask, raw_sum, 0);
+    const bool raw_ok = raw_sum > 0.0 && !isinf(raw_sum) && !isnan(raw_sum);
+    if (raw_ok)
+        for (uint32_t i = lane; i < n; i += 32) fin.raw[i] = fin.raw[i] / raw_sum;
+    __syncwarp();
+    if (lane == 0) {
         uint32_t cutoff = n;
-        if (!(raw_sum > 0.0) || isinf(raw_sum) || isnan(raw_sum)) {
-            status = kErrFormat;  // "sampler raw softmax failed"
-        } else {
+        if (raw_ok) {
             double mass = 0.0;
             const double top_p = (double)cfg.top_p;
             for (uint32_t i = 0; i < n; i++) {
-                const double p = fin.raw[i] / raw_sum;
-                fin.raw[i] = p;  // kept for the debug dump
-                mass += p;
+                mass += fin.raw[i];
                 if (mass >= top_p) {
                     cutoff = i + 1;
-                    // the rest of the dump still wants probabilities
-                    for (uint32_t j = i + 1; j < n; j++) fin.raw[j] = fin.raw[j] / raw_sum;
                     break;
                 }
             }
         }
         fin.cutoff = cutoff;
-        fin.status = status;
+        fin.status = raw_ok ? kOk : kErrFormat;  // "sampler raw softmax failed"
     }
     __syncwarp();
     if (fin.status != kOk) {

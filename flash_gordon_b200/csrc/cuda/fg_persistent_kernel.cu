@@ -206,6 +206,100 @@ __device__ __forceinline__ bool consider(Shared &sh, Lists &L, const Row &r, flo
     return true;
 }
 
+// A cut that need not be exact: one histogram pass over the candidates' keys (256 bins
+// between the smallest and the largest key in the list) finds the highest bin edge with
+// at least k candidates at or above it; everything below goes, and the smallest score
+// that stays is the new bound (with the padding id: a tie with it is still admitted).
+// About a third of the barriers of the exact radix select.  Rows whose candidates
+// crowd into one bin (constant rows) keep too many: the caller then cuts exactly.
+// Every consumer calls it with the same `held` > k; returns what is left.
+__device__ __forceinline__ uint32_t quick_cut(Lists &L, uint32_t held, uint32_t k) {
+    constexpr int PER = kCandCap / kConsumers;
+    CandidateBuffer<kCandCap> &buf = L.cand;
+    const uint32_t tid = threadIdx.x, lane = tid & 31u;
+    float score[PER];
+    uint32_t id[PER], key[PER];
+    uint32_t high = 0, low = 0xffffffffu;
+#pragma unroll
+    for (int j = 0; j < PER; j++) {
+        const uint32_t at = j * kConsumers + tid;
+        key[j] = 0;
+        if (at < held) {
+            score[j] = buf.score[at];
+            id[j] = buf.id[at];
+            key[j] = float_key(score[j]);  // finite, so never 0
+            high = max(high, key[j]);
+            low = min(low, key[j]);
+        }
+    }
+    buf.hist[tid] = 0;
+    if (tid == 0) {
+        buf.sel_need = 0;             // largest key
+        buf.sel_bucket = 0xffffffffu; // smallest key
+        buf.out_count = 0;
+        buf.eq_count = 0xffffffffu;   // smallest key that stays
+    }
+    CB::sync();
+    high = __reduce_max_sync(kFullMask, high);
+    low = __reduce_min_sync(kFullMask, low);
+    if (lane == 0) {
+        atomicMax(&buf.sel_need, high);
+        atomicMin(&buf.sel_bucket, low);
+    }
+    CB::sync();
+    const uint32_t base = buf.sel_bucket;
+    const uint32_t range = buf.sel_need - base;
+    const int shift = max(0, 24 - (int)__clz(range | 1u));  // (range >> shift) < 256
+#pragma unroll
+    for (int j = 0; j < PER; j++)
+        if (key[j] != 0) atomicAdd(&buf.hist[(key[j] - base) >> shift], 1u);
+    CB::sync();
+    if (tid < 32) {
+        // lane l owns bins 255-8l .. 248-8l, walked from the top
+        uint32_t mine = 0;
+#pragma unroll
+        for (int b = 0; b < 8; b++) mine += buf.hist[255 - 8 * tid - b];
+        uint32_t incl = mine;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const uint32_t up = __shfl_up_sync(kFullMask, incl, d);
+            if (tid >= (uint32_t)d) incl += up;
+        }
+        const unsigned reached = __ballot_sync(kFullMask, incl >= k);
+        const int owner = __ffs(reached) - 1;  // k < held, so some lane reaches it
+        if ((int)tid == owner) {
+            uint32_t above = incl - mine;
+            for (int b = 0; b < 8; b++) {
+                const uint32_t bin = 255 - 8 * tid - b;
+                above += buf.hist[bin];
+                if (above >= k) {
+                    buf.sel_digit = bin;
+                    break;
+                }
+            }
+        }
+    }
+    CB::sync();
+    const uint32_t edge = buf.sel_digit;
+#pragma unroll
+    for (int j = 0; j < PER; j++) {
+        if (key[j] != 0 && ((key[j] - base) >> shift) >= edge) {
+            const uint32_t slot = atomicAdd(&buf.out_count, 1u);
+            buf.score[slot] = score[j];
+            buf.id[slot] = id[j];
+            atomicMin(&buf.eq_count, key[j]);
+        }
+    }
+    CB::sync();
+    if (tid == 0) {
+        buf.tau_score = key_to_float(buf.eq_count);
+        buf.tau_id = kPaddingId;
+        buf.count = buf.out_count;
+    }
+    CB::sync();
+    return buf.out_count;
+}
+
 // The meeting of all consumer warps.  A warp comes here when it sees sh.attention
 // up or when one of its lanes found a list full (it then raises the flag itself).
 // Nobody appends to a list while the meeting is on.  Ids that were put aside get their occurrences counted in the row's token list
@@ -265,7 +359,11 @@ __device__ __noinline__ float attend(Shared &sh, Lists &L, const Row r) {
         held = min(L.cand.count, (uint32_t)kCandCap);
         CB::sync();
     }
-    if (held >= r.cut_at) compact_topk<kConsumers, kCandCap, CB>(L.cand, held, r.k);
+    if (held >= r.cut_at) {
+        held = quick_cut(L, held, r.k);
+        // (a list the quick cut could not thin out is cut exactly, ties resolved by id)
+        if (held >= (r.k + r.cut_at) / 2) compact_topk<kConsumers, kCandCap, CB>(L.cand, held, r.k);
+    }
     if (tid == 0) sh.attention = 0;
     CB::sync();
     return L.cand.tau_score;
@@ -953,6 +1051,7 @@ persistent_select_kernel(const __grid_constant__ Params p) {
             for (;;) {
                 if (__any_sync(kFullMask, peek(&sh.attention) != 0)) attend(sh, L, r);
                 else if (__any_sync(kFullMask, peek(&sh.through[b]) == (uint32_t)kConsumerWarps)) break;
+                else __nanosleep(100);  // leave the issue slots to the warps that still work
             }
         }
         FGK_PTICK(4);
