@@ -54,9 +54,24 @@ def measured_hbm_peak():
         return FALLBACK_HBM_GBS, "fallback"
 
 
-def recorded_traffic_per_row():
-    """DRAM bytes per row of the streaming kernel, from the committed ncu summary."""
-    path = ROOT / "profiles" / "stream_select_config3_ncu.txt"
+KERNELS = {
+    # kernel name -> the committed ncu summary that holds its DRAM bytes per row
+    "persistent_select_kernel<float>": "persistent_select_config3_ncu.txt",
+    "stream_select_kernel<float>": "stream_select_config3_ncu.txt",
+}
+
+
+def kernel_taken(path: str, rows: int, sm_count: int) -> str:
+    """The kernel the library launches for this workload: the persistent ring kernel when
+    asked for, or by itself once each of its 2 CTAs per SM has two rows to work through."""
+    if path == "ring" or (path == "auto" and rows >= 4 * sm_count):
+        return "persistent_select_kernel<float>"
+    return "stream_select_kernel<float>"
+
+
+def recorded_traffic_per_row(kernel: str):
+    """DRAM bytes per row of the kernel, from its committed ncu summary."""
+    path = ROOT / "profiles" / KERNELS[kernel]
     try:
         found = re.search(r"dram_bytes_per_row\s*=\s*([0-9.]+)", path.read_text())
         return float(found.group(1)) if found else None
@@ -190,6 +205,9 @@ def main():
     parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
     parser.add_argument("--e2e-steps", type=int, default=10)
     parser.add_argument("--splits", type=int, default=0, help="force CTAs per row (0 = automatic)")
+    parser.add_argument("--path", default="auto", choices=["auto", "registers", "ring"],
+                        help="kernel: the library's choice, the register-prefetch kernel, or the "
+                             "persistent ring kernel")
     parser.add_argument("--rows", type=int, default=ROWS)
     parser.add_argument("--skip-cpu", action="store_true")
     args = parser.parse_args()
@@ -220,6 +238,7 @@ def main():
     context = Context(local_rank)
     if args.splits:
         context.set_splits(args.splits)
+    context.set_path({"auto": 0, "registers": 1, "ring": 2}[args.path])
     outs = [(torch.empty(rows, dtype=torch.int32, device=device),
              torch.empty(rows, dtype=torch.float32, device=device),
              torch.empty(rows, dtype=torch.int32, device=device)) for _ in sets]
@@ -295,7 +314,8 @@ def main():
         bytes_per_row = sets[0].algorithmic_bytes_per_row()
         mean_launch_ms = sum(launch_ms) / len(launch_ms)
         achieved = rows * bytes_per_row / (mean_launch_ms * 1e-3) / 1e9
-        traffic_row = recorded_traffic_per_row()
+        kernel = kernel_taken(args.path, rows, torch.cuda.get_device_properties(device).multi_processor_count)
+        traffic_row = recorded_traffic_per_row(kernel)
         line = {
             "metric": METRIC,
             "value": world * rows * args.steps / (elapsed_ms * 1e-3),
@@ -312,7 +332,7 @@ def main():
             "clocks": clocks,
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "peak_source": f"{peak_kind} HBM copy bandwidth",
-                         "kernel": "stream_select_kernel<float>",
+                         "kernel": kernel,
                          "algorithmic_bytes_per_row": bytes_per_row,
                          "launch_ms": {"mean": mean_launch_ms, "median": launch_ms[len(launch_ms) // 2],
                                        "min": launch_ms[0]},

@@ -160,6 +160,21 @@ __device__ __forceinline__ bool mbarrier_try_wait(uint64_t *barrier, uint32_t pa
     return done != 0;
 }
 
+// The same, but the thread may sleep for up to `nanoseconds` while the phase is not
+// complete: a warp that waits this way leaves the issue slots to the warps that work.
+__device__ __forceinline__ bool mbarrier_try_wait_sleeping(uint64_t *barrier, uint32_t parity,
+                                                           uint32_t nanoseconds) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(shared_address(barrier)), "r"(parity), "r"(nanoseconds)
+        : "memory");
+    return done != 0;
+}
+
 // Bounded wait: gives up after about a second's worth of polls and reports false, so
 // a copy that never lands becomes an error status instead of a hung GPU.
 __device__ __forceinline__ bool mbarrier_wait(uint64_t *barrier, uint32_t parity) {

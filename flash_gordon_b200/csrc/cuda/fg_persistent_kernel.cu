@@ -48,7 +48,8 @@ constexpr uint32_t kStageBytes = 16384;
 constexpr int kVectors = 4;              // 128-bit vectors per consumer thread and tile
 constexpr int kCandCap = 1024;
 constexpr int kDeferCap = 256;           // ids put aside until their occurrences are counted
-constexpr uint32_t kWaitPolls = 1u << 22;
+constexpr uint32_t kWaitPolls = 1u << 20;
+constexpr uint32_t kNapNanoseconds = 2000;  // longest sleep inside one poll of an mbarrier
 
 // The eight consumer warps meet at named barrier 1; the copy warp never does.
 struct ConsumerBarrier {
@@ -155,7 +156,7 @@ struct Row {
 
 __device__ __forceinline__ bool bounded_wait(uint64_t *barrier, uint32_t parity) {
     for (uint32_t polls = 0; polls < kWaitPolls; polls++)
-        if (mbarrier_try_wait(barrier, parity)) return true;
+        if (mbarrier_try_wait_sleeping(barrier, parity, kNapNanoseconds)) return true;
     return false;
 }
 
@@ -527,7 +528,8 @@ __device__ __noinline__ Stop hot_tiles(Shared &sh, Lists &L, const uint32_t *bit
                 stop.why = kStopBefore;
                 return stop;
             }
-            const bool landed = peek(&sh.ring_error) != 0 || mbarrier_try_wait(&sh.full[at], use & 1u);
+            const bool landed = peek(&sh.ring_error) != 0 ||
+                                mbarrier_try_wait_sleeping(&sh.full[at], use & 1u, kNapNanoseconds);
             if (__all_sync(kFullMask, landed)) break;
             if (polls >= kWaitPolls) poke(&sh.ring_error, 1u);  // values are then garbage; the row fails
         }
@@ -847,7 +849,10 @@ __device__ __forceinline__ Row make_row(const Params &p, const SamplerConfig &cf
     Row r;
     r.greedy = !shard_mode && cfg.temperature == 0.0f;
     r.k = shard_mode ? p.shard_k : (r.greedy ? 1u : cfg.top_k);
-    r.cut_at = 4 * r.k + 64;
+#ifndef FGK_PERSIST_CUT_AT
+#define FGK_PERSIST_CUT_AT (4 * r.k + 64)
+#endif
+    r.cut_at = FGK_PERSIST_CUT_AT;
     r.id_base = p.vocab_offset;
     r.flat_offset = penalty_offset(1u, cfg.presence_penalty, cfg.frequency_penalty);
     r.presence = cfg.presence_penalty;
