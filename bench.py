@@ -62,11 +62,9 @@ KERNELS = {
 
 
 def kernel_taken(path: str, rows: int, sm_count: int) -> str:
-    """The kernel the library launches for this workload: the persistent ring kernel when
-    asked for, or by itself once each of its 2 CTAs per SM has two rows to work through."""
-    if path == "ring" or (path == "auto" and rows >= 4 * sm_count):
-        return "persistent_select_kernel<float>"
-    return "stream_select_kernel<float>"
+    """The kernel the library launches for this workload (16-byte aligned fp32 rows, penalties
+    that only lower logits): the persistent ring kernel unless the other one is asked for."""
+    return "stream_select_kernel<float>" if path == "registers" else "persistent_select_kernel<float>"
 
 
 def recorded_traffic_per_row(kernel: str):

@@ -95,13 +95,17 @@ int fgk_stream_prepare(void);
 int fgk_launch_stream_select(const fgk_stream_launch *launch, void *stream);
 
 /* ---- persistent ring kernel (fg_persistent_kernel.cu) ----
- * Takes a fgk_stream_launch with splits == 1, rows and row stride multiples of 16 bytes,
- * and only rows whose penalties cannot raise a logit.  Of the history fields it uses
- * bitmap_words alone (the bitmap lives behind the ring in dynamic shared memory). */
+ * Takes a fgk_stream_launch with rows and row stride multiples of 16 bytes and only rows
+ * whose penalties cannot raise a logit.  Work is dealt out in 16 KB tiles: `split_len`
+ * holds the tiles per CTA, `splits` the most CTAs that can share one row; part_* and
+ * tickets as for the streaming kernel.  Of the history fields it uses bitmap_words alone
+ * (the bitmap lives behind the ring in dynamic shared memory). */
 #define FGK_PERSIST_MAX_DYNAMIC_SMEM (200 * 1024)
 uint64_t fgk_persistent_dynamic_smem(uint32_t bitmap_words);
 /* CTAs of the kernel one SM holds at this much dynamic shared memory (0 on error) */
 uint32_t fgk_persistent_ctas_per_sm(uint32_t dtype, uint64_t dynamic_smem);
+uint32_t fgk_persistent_row_tiles(uint32_t dtype, uint32_t vocab);
+uint32_t fgk_persistent_max_parts(void);
 int fgk_persistent_prepare(void);
 int fgk_launch_persistent_select(const fgk_stream_launch *launch, uint32_t ctas, void *stream);
 

@@ -96,6 +96,14 @@ struct Lanes<uint16_t> {  // bf16 bit patterns
     }
 };
 
+// What a CTA that shares a row leaves behind for the merge.
+struct alignas(16) PartRecord {
+    uint32_t count;         // finite candidates kept (<= k)
+    uint32_t wild_id;       // smallest id holding a NaN/Inf (greedy rows), padding if none
+    uint32_t wild_bits;     // its value
+    uint32_t bad_history;   // 0, or the fg_status a broken history earns the row
+};
+
 struct Params {
     const void *logits;
     uint64_t row_stride;  // elements
@@ -112,7 +120,60 @@ struct Params {
     const float *uniforms;
     float *shard_scores;
     uint32_t *shard_ids;
+    // Work is dealt out in 16 KB tiles: CTA c takes tiles [c * tiles_per_cta, (c + 1) *
+    // tiles_per_cta) of the batch's tile sequence (row after row), so a row may be shared
+    // by several CTAs.  Each leaves its part's k best in `parts`; the last to finish
+    // (ticket counter) merges them.
+    // With enough rows for every CTA to have several, whole rows are dealt out instead
+    // (tiles_per_cta == 0): CTA c takes rows [c * rows / ctas, (c + 1) * rows / ctas).
+    uint32_t tiles_per_cta;
+    uint32_t max_parts;             // most CTAs that share one row
+    float *part_scores;             // [rows][max_parts][kMaxK]
+    uint32_t *part_ids;
+    PartRecord *part_meta;          // [rows][max_parts]
+    uint32_t *tickets;              // [rows], zero between launches
     SelectOutput out;
+};
+
+// One CTA's share of one row.
+struct Unit {
+    uint32_t row;
+    uint32_t first, end;    // tiles [first, end) of the row
+    uint32_t part, parts;   // which of how many shares of the row
+};
+
+// Walks the units of this CTA in order.
+struct UnitWalk {
+    uint64_t at, stop;      // position in the batch's tile sequence
+    uint32_t row_tiles, per_cta;
+    __device__ __forceinline__ UnitWalk(const Params &p, uint32_t row_tiles_)
+        : row_tiles(row_tiles_), per_cta(p.tiles_per_cta) {
+        const uint64_t all = (uint64_t)p.rows * row_tiles;
+        if (per_cta == 0) {
+            at = (uint64_t)blockIdx.x * p.rows / gridDim.x * row_tiles;
+            stop = ((uint64_t)blockIdx.x + 1u) * p.rows / gridDim.x * row_tiles;
+        } else {
+            at = min((uint64_t)blockIdx.x * per_cta, all);
+            stop = min(at + per_cta, all);
+        }
+    }
+    __device__ __forceinline__ bool next(Unit &u) {
+        if (at >= stop) return false;
+        u.row = (uint32_t)(at / row_tiles);
+        u.first = (uint32_t)(at % row_tiles);
+        u.end = (uint32_t)min((uint64_t)row_tiles, u.first + (stop - at));
+        u.part = 0;
+        u.parts = 1;
+        if (per_cta != 0) {
+            const uint64_t row_begin = (uint64_t)u.row * row_tiles;
+            const uint32_t first_cta = (uint32_t)(row_begin / per_cta);
+            const uint32_t last_cta = (uint32_t)((row_begin + row_tiles - 1) / per_cta);
+            u.part = blockIdx.x - first_cta;
+            u.parts = last_cta - first_cta + 1;
+        }
+        at += u.end - u.first;
+        return true;
+    }
 };
 
 // What the consumers collect for one row.  There are two of these: while the closing
@@ -429,14 +490,14 @@ __device__ __noinline__ float settle(Shared &sh, Lists &L, const Row r, const ui
     }
 }
 
-// Tile 0 of a row, all warps together: every element is looked at.  The first bound is
+// The first tile of a unit, all warps together: every element is looked at.  The first bound is
 // the smallest, over the warps, of each warp's j-th largest per-thread maximum of
 // unseen finite values, j = ceil(k / warps): at least k distinct elements are that
 // large.  (No bound when some warp has fewer than j such threads; everything finite
 // is then a candidate until the first cut.)  Returns the bound.
 template <typename T>
 __device__ __noinline__ float first_tile(Shared &sh, Lists &L, const uint32_t *bitmap, const unsigned char *stage,
-                                         uint32_t valid_vectors, const Row r) {
+                                         uint32_t t, uint32_t valid_vectors, const Row r) {
     using V = Lanes<T>;
     constexpr int kPer = V::kPer;
     const uint32_t tid = threadIdx.x, lane = tid & 31u;
@@ -449,7 +510,7 @@ __device__ __noinline__ float first_tile(Shared &sh, Lists &L, const uint32_t *b
         if (g >= valid_vectors) continue;
         float v[kPer];
         V::unpack(vectors[g], v);
-        const uint32_t column = g * kPer;
+        const uint32_t column = t * (kStageBytes / (uint32_t)sizeof(T)) + g * kPer;
         const uint32_t bits =
             r.seen_any ? (bitmap[column >> 5] >> (column & 31u)) & ((1u << kPer) - 1u) : 0u;
 #pragma unroll
@@ -492,8 +553,8 @@ __device__ __noinline__ float first_tile(Shared &sh, Lists &L, const uint32_t *b
             if (v[j] >= tau || wild) pending |= 1u << (u * kPer + j);
         }
     }
-    return r.greedy ? settle<T, true>(sh, L, r, bitmap, stage, 0, pending, tau)
-                    : settle<T, false>(sh, L, r, bitmap, stage, 0, pending, tau);
+    return r.greedy ? settle<T, true>(sh, L, r, bitmap, stage, t, pending, tau)
+                    : settle<T, false>(sh, L, r, bitmap, stage, t, pending, tau);
 }
 
 // What hot_tiles hands back: the tile it stopped at, why, and this lane's elements of
@@ -503,7 +564,7 @@ struct Stop {
     uint32_t tile, why, pending;
 };
 
-// The hot loop of one warp over tiles first .. tiles-1 of a row; the warps run it
+// The hot loop of one warp over tiles first .. end-1 of a row (which has `tiles`); the warps run it
 // independently of one another, at most a ring's depth apart.  It calls nothing:
 // whatever is live across a call inside a loop is saved and restored on every trip.
 //   kStopBefore  the attention flag is up and the warp has not touched `tile` yet
@@ -511,7 +572,7 @@ struct Stop {
 //                still to be offered, and the warp still holds the stage
 template <typename T, bool kGreedy>
 __device__ __noinline__ Stop hot_tiles(Shared &sh, Lists &L, const uint32_t *bitmap, const unsigned char *ring,
-                                       uint32_t first, uint32_t tiles, uint32_t last_vectors,
+                                       uint32_t first, uint32_t end, uint32_t tiles, uint32_t last_vectors,
                                        const uint32_t row_sequence, const Row r, const float tau) {
     using V = Lanes<T>;
     constexpr int kPer = V::kPer;
@@ -519,7 +580,7 @@ __device__ __noinline__ Stop hot_tiles(Shared &sh, Lists &L, const uint32_t *bit
     const uint32_t tau_id = L.cand.tau_id;
     Stop stop;
     stop.pending = 0;
-    for (uint32_t t = first; t < tiles; t++) {
+    for (uint32_t t = first; t < end; t++) {
         const uint32_t at = (row_sequence + t) % kStages, use = (row_sequence + t) / kStages;
         stop.tile = t;
         // ---- wait for the tile, watching the flag ----
@@ -576,7 +637,7 @@ __device__ __noinline__ Stop hot_tiles(Shared &sh, Lists &L, const uint32_t *bit
         // the warp is done with the stage
         if (lane == 0) mbarrier_arrive(&sh.empty[at]);
     }
-    stop.tile = tiles;
+    stop.tile = end;
     stop.why = kStopDone;
     return stop;
 }
@@ -628,8 +689,8 @@ __device__ __forceinline__ uint64_t list_key(const Lists &L, uint32_t held, uint
     return L.defer_id[d] == kPaddingId ? 0ull : select_key(L.defer_raw[d], L.defer_id[d]);
 }
 
-__device__ __noinline__ void close_row(Shared &sh, Lists &L, const Params &p, uint32_t row, const Row r,
-                                       const SamplerConfig cfg, bool shard_mode) {
+// The exact k best of a pair of lists, in sampling order, into sh.fin; returns how many.
+__device__ __noinline__ uint32_t settle_lists(Shared &sh, Lists &L, const Row r) {
     const uint32_t lane = threadIdx.x & 31u;
     const uint32_t held = min(L.cand.count, (uint32_t)kCandCap);
     const uint32_t aside = min(L.defer_count, (uint32_t)kDeferCap);
@@ -772,11 +833,70 @@ __device__ __noinline__ void close_row(Shared &sh, Lists &L, const Params &p, ui
     }
     __syncwarp();
 
-    // ---- the row's result ----
+    return kept;
+}
+
+// A unit's lists become its part of the row's result; the CTA that finishes a row's last
+// part merges the parts and writes the result.
+__device__ __noinline__ void close_unit(Shared &sh, Lists &L, const Params &p, const Unit u, const Row r,
+                                        const SamplerConfig cfg, bool shard_mode) {
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t row = u.row;
+    uint32_t kept = settle_lists(sh, L, r);
     uint32_t bad_history = L.bad_history;
     if (peek(&sh.ring_error)) bad_history = kErrLimit;  // a tile never landed
-    const uint32_t wild_id = (uint32_t)(L.wild_key >> 32);  // the padding id when nothing was seen
-    const uint32_t wild_bits = (uint32_t)L.wild_key;
+    uint32_t wild_id = (uint32_t)(L.wild_key >> 32);  // the padding id when nothing was seen
+    uint32_t wild_bits = (uint32_t)L.wild_key;
+    if (u.parts > 1) {
+        const size_t mine = (size_t)row * p.max_parts + u.part;
+        for (uint32_t i = lane; i < (uint32_t)kMaxK; i += 32) {
+            p.part_scores[mine * kMaxK + i] = i < kept ? sh.fin.score[i] : 0.0f;
+            p.part_ids[mine * kMaxK + i] = i < kept ? sh.fin.id[i] : kPaddingId;
+        }
+        if (lane == 0) {
+            PartRecord record;
+            record.count = kept;
+            record.wild_id = wild_id;
+            record.wild_bits = wild_bits;
+            record.bad_history = bad_history;
+            p.part_meta[mine] = record;
+        }
+        __threadfence();
+        __syncwarp();
+        uint32_t ticket = 0;
+        if (lane == 0) ticket = atomicAdd(&p.tickets[row], 1u);
+        ticket = __shfl_sync(kFullMask, ticket, 0);
+        if (ticket != u.parts - 1) return;  // somebody else finishes the row
+        __threadfence();
+        if (lane == 0) p.tickets[row] = 0;  // ready for the next launch
+        // every part's survivors into this slot's candidate list (parts * kMaxK <= kCandCap)
+        uint32_t total = 0;
+        bad_history = 0;
+        wild_id = kPaddingId;
+        wild_bits = 0;
+        for (uint32_t j = 0; j < u.parts; j++) {
+            const size_t from = (size_t)row * p.max_parts + j;
+            const uint4 packed = __ldcg(reinterpret_cast<const uint4 *>(&p.part_meta[from]));
+            const uint32_t count = min(packed.x, (uint32_t)kMaxK);
+            for (uint32_t i = lane; i < count; i += 32) {
+                L.cand.score[total + i] = __ldcg(&p.part_scores[from * kMaxK + i]);
+                L.cand.id[total + i] = __ldcg(&p.part_ids[from * kMaxK + i]);
+            }
+            total += count;
+            if (packed.w) bad_history = packed.w;
+            if (packed.y < wild_id) {
+                wild_id = packed.y;
+                wild_bits = packed.z;
+            }
+        }
+        if (lane == 0) {
+            L.cand.count = total;
+            L.defer_count = 0;
+        }
+        __syncwarp();
+        kept = settle_lists(sh, L, r);
+    }
+    // ---- the row's result ----
     if (shard_mode) {
         for (uint32_t i = lane; i < r.k; i += 32) {
             const size_t at = (size_t)row * r.k + i;
@@ -917,17 +1037,19 @@ persistent_select_kernel(const __grid_constant__ Params p) {
     if (tid >= (uint32_t)kConsumers + 32u) {
         // ------------------------------------------------------------- closing warp
         uint32_t served = 0;
-        for (uint32_t row = blockIdx.x; row < p.rows; row += gridDim.x) {
-            const SamplerConfig cfg = p.config_count > 1 ? p.configs[row] : p.config0;
+        UnitWalk walk(p, tiles);
+        Unit u;
+        while (walk.next(u)) {
+            const SamplerConfig cfg = p.config_count > 1 ? p.configs[u.row] : p.config0;
             if (!row_is_ours(cfg, shard_mode)) continue;
             uint32_t bad_history;
-            const Row r = make_row(p, cfg, row, shard_mode, &bad_history);
+            const Row r = make_row(p, cfg, u.row, shard_mode, &bad_history);
             const uint32_t b = served & 1u;
             // (a wait that runs out leaves garbage lists: the row is failed through ring_error)
             if (!peek(&sh.ring_error) && !bounded_wait(&sh.ready[b], (served >> 1) & 1u))
                 poke(&sh.ring_error, 1u);
             __syncwarp();
-            close_row(sh, sh.lists[b], p, row, r, cfg, shard_mode);
+            close_unit(sh, sh.lists[b], p, u, r, cfg, shard_mode);
             __syncwarp();
             if ((tid & 31u) == 0) mbarrier_arrive(&sh.vacant[b]);
             served++;
@@ -940,12 +1062,14 @@ persistent_select_kernel(const __grid_constant__ Params p) {
         const uint64_t policy = l2_policy_evict_first();
         RingCursor cursor;
         bool gave_up = false;
-        for (uint32_t row = blockIdx.x; row < p.rows && !gave_up; row += gridDim.x) {
-            const SamplerConfig cfg = p.config_count > 1 ? p.configs[row] : p.config0;
+        UnitWalk walk(p, tiles);
+        Unit u;
+        while (!gave_up && walk.next(u)) {
+            const SamplerConfig cfg = p.config_count > 1 ? p.configs[u.row] : p.config0;
             if (!row_is_ours(cfg, shard_mode)) continue;
             const unsigned char *source =
-                static_cast<const unsigned char *>(p.logits) + (size_t)row * p.row_stride * sizeof(T);
-            for (uint32_t t = 0; t < tiles; t++) {
+                static_cast<const unsigned char *>(p.logits) + (size_t)u.row * p.row_stride * sizeof(T);
+            for (uint32_t t = u.first; t < u.end; t++) {
                 if (cursor.use != 0 && !bounded_wait(&sh.empty[cursor.stage], (cursor.use - 1u) & 1u)) {
                     sh.ring_error = 1;  // the consumers see it and fail their rows
                     gave_up = true;
@@ -972,16 +1096,21 @@ persistent_select_kernel(const __grid_constant__ Params p) {
 
     // -------------------------------------------------------------------- consumers
     const uint32_t lane = tid & 31u;
-    uint32_t row_sequence = 0;  // tiles of earlier rows: tile t of this row is ring tile row_sequence + t
-    uint32_t served = 0;        // rows before this one
+    uint32_t consumed = 0;      // tiles of earlier units
+    uint32_t served = 0;        // units before this one
 #ifdef FGK_PHASE_CLOCKS
     long long tick = clock64();
 #endif
-    for (uint32_t row = blockIdx.x; row < p.rows; row += gridDim.x) {
+    UnitWalk walk(p, tiles);
+    Unit u;
+    while (walk.next(u)) {
+        const uint32_t row = u.row;
         const SamplerConfig cfg = p.config_count > 1 ? p.configs[row] : p.config0;
         if (!row_is_ours(cfg, shard_mode)) continue;
         uint32_t bad_history;
         const Row r = make_row(p, cfg, row, shard_mode, &bad_history);
+        // tile t of the row is ring tile row_sequence + t (unsigned arithmetic wraps as it should)
+        const uint32_t row_sequence = consumed - u.first;
         const uint32_t b = served & 1u;
         Lists &L = sh.lists[b];
         // the closing warp must be done with these lists (it had them two rows ago)
@@ -1004,21 +1133,21 @@ persistent_select_kernel(const __grid_constant__ Params p) {
         FGK_PTICK(0);
 
         const uint32_t last_vectors = (row_bytes - (tiles - 1) * kStageBytes) / 16u;
-        // ---- tile 0, all warps together ----
-        const uint32_t at0 = row_sequence % kStages;
-        if (!peek(&sh.ring_error) && !bounded_wait(&sh.full[at0], (row_sequence / kStages) & 1u))
+        // ---- the unit's first tile, all warps together ----
+        const uint32_t at0 = consumed % kStages;
+        if (!peek(&sh.ring_error) && !bounded_wait(&sh.full[at0], (consumed / kStages) & 1u))
             poke(&sh.ring_error, 1u);
-        float tau = first_tile<T>(sh, L, bitmap, ring + (size_t)at0 * kStageBytes,
-                                  tiles == 1 ? last_vectors : kStageBytes / 16u, r);
+        float tau = first_tile<T>(sh, L, bitmap, ring + (size_t)at0 * kStageBytes, u.first,
+                                  u.first + 1 == tiles ? last_vectors : kStageBytes / 16u, r);
         __syncwarp();
         if (lane == 0) mbarrier_arrive(&sh.empty[at0]);
         FGK_PTICK(1);
 
-        // ---- tiles 1 .. : each warp at its own pace ----
-        for (uint32_t t = 1; t < tiles;) {
+        // ---- the further tiles: each warp at its own pace ----
+        for (uint32_t t = u.first + 1; t < u.end;) {
             const Stop stop =
-                r.greedy ? hot_tiles<T, true>(sh, L, bitmap, ring, t, tiles, last_vectors, row_sequence, r, tau)
-                         : hot_tiles<T, false>(sh, L, bitmap, ring, t, tiles, last_vectors, row_sequence, r, tau);
+                r.greedy ? hot_tiles<T, true>(sh, L, bitmap, ring, t, u.end, tiles, last_vectors, row_sequence, r, tau)
+                         : hot_tiles<T, false>(sh, L, bitmap, ring, t, u.end, tiles, last_vectors, row_sequence, r, tau);
             if (stop.why == kStopDone) break;
             t = stop.tile;
             if (stop.why == kStopBefore) {
@@ -1060,7 +1189,7 @@ persistent_select_kernel(const __grid_constant__ Params p) {
             }
         }
         FGK_PTICK(4);
-        row_sequence += tiles;
+        consumed += u.end - u.first;
         served++;
     }
 }
@@ -1103,6 +1232,12 @@ static persist::Params to_persist_params(const fgk_stream_launch *l) {
     p.uniforms = l->uniforms;
     p.shard_scores = l->shard_scores;
     p.shard_ids = l->shard_ids;
+    p.tiles_per_cta = l->split_len;  /* reused: tiles per CTA */
+    p.max_parts = l->splits;         /* reused: most CTAs per row */
+    p.part_scores = l->part_scores;
+    p.part_ids = l->part_ids;
+    p.part_meta = static_cast<persist::PartRecord *>(l->part_meta);
+    p.tickets = l->tickets;
     p.out.tokens = l->out.tokens;
     p.out.token_logits = l->out.token_logits;
     p.out.row_status = l->out.row_status;
@@ -1118,6 +1253,15 @@ static persist::Params to_persist_params(const fgk_stream_launch *l) {
 extern "C" uint64_t fgk_persistent_dynamic_smem(uint32_t bitmap_words) {
     return (uint64_t)persist::kStages * persist::kStageBytes + (((uint64_t)bitmap_words + 3u) / 4u) * 16u;
 }
+
+// 16 KB tiles in a row of `vocab` logits.
+extern "C" uint32_t fgk_persistent_row_tiles(uint32_t dtype, uint32_t vocab) {
+    const uint64_t bytes = (uint64_t)vocab * (dtype == 1u ? 2u : 4u);
+    return (uint32_t)((bytes + persist::kStageBytes - 1) / persist::kStageBytes);
+}
+
+// Most parts of one row the merge can take (parts * 64 survivors fit one candidate list).
+extern "C" uint32_t fgk_persistent_max_parts(void) { return persist::kCandCap / kMaxK; }
 
 extern "C" uint32_t fgk_persistent_ctas_per_sm(uint32_t dtype, uint64_t dynamic_smem) {
     int blocks = 0;

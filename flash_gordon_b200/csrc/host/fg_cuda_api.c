@@ -648,20 +648,46 @@ static fg_status run_stream(fg_cuda_context *c, const fg_cuda_sample_args *a,
                      "the ring path needs whole 16-byte aligned rows and penalties that only lower logits");
         return FG_ERR_ARGUMENT;
     }
-    /* AUTO: the persistent kernel once every one of its CTAs has at least two rows to
-     * work through (measured on B200: 191 us against 258 us for 1024 rows of 151,936
-     * fp32 logits); smaller batches fill the GPU better as column splits of the
-     * register-prefetch kernel. */
+    /* AUTO: the persistent kernel whenever it can take the batch (measured on B200 it is
+     * ahead at every batch size: 29 against 38 us for one row of 151,936 fp32 logits,
+     * 48 against 71 us for 64 rows, 186 against 255 us for 1024). */
     uint32_t per_sm = fgk_persistent_ctas_per_sm(a->dtype, fgk_persistent_dynamic_smem(whole_bitmap));
     if (per_sm == 0u) per_sm = 1u;
     const uint32_t most = c->sm_count * per_sm;
-    const bool take_ring = c->path == FG_CUDA_PATH_RING || c->path == FG_CUDA_PATH_RING_IF_POSSIBLE ||
-                           (c->path == FG_CUDA_PATH_AUTO && a->rows >= 2u * most);
+    const bool take_ring = c->path != FG_CUDA_PATH_REGISTERS;
     if (ring_ok && take_ring) {
-        l.splits = 1u;
-        l.split_len = a->vocab;
+        /* Work goes out in 16 KB tiles, the same number to every CTA, so a row may be shared
+         * by several CTAs; a share is at least so long that no row has more parts than the
+         * merge takes. */
+        const uint32_t row_tiles = fgk_persistent_row_tiles(a->dtype, a->vocab);
+        const uint64_t all_tiles = (uint64_t)a->rows * row_tiles;
+        const uint32_t parts_limit = fgk_persistent_max_parts();
+        uint64_t per_cta = (all_tiles + most - 1u) / most;
+        const uint64_t shortest = (row_tiles + parts_limit - 2u) / (parts_limit - 1u);
+        if (per_cta < shortest) per_cta = shortest;
+        uint32_t ctas = (uint32_t)((all_tiles + per_cta - 1u) / per_cta);
+        uint32_t max_parts = (uint32_t)((row_tiles + per_cta - 1u) / per_cta) + 1u;
+        if (max_parts > parts_limit) max_parts = parts_limit;
+        /* With two or more rows for every CTA whole rows are dealt out: a shared row costs
+         * its fixed work once per part, which on B200 outweighs the better balance. */
+        if (a->rows >= 2u * most) {
+            per_cta = 0u;
+            ctas = most;
+            max_parts = 1u;
+        }
+        const size_t part_slots = (size_t)a->rows * max_parts;
+        status = fg_cuda_reserve(&c->parts, &c->parts_bytes, part_slots * (64u * 8u + 16u), false, c, err);
+        if (status != FG_OK) return status;
+        unsigned char *base = c->parts;
+        l.part_scores = (float *)base;
+        l.part_ids = (uint32_t *)(base + part_slots * 64u * 4u);
+        l.part_meta = base + part_slots * 64u * 8u;
+        l.splits = max_parts;
+        l.split_len = (uint32_t)per_cta;
         l.bitmap_words = whole_bitmap;
-        const int e = fgk_launch_persistent_select(&l, a->rows < most ? a->rows : most, c->stream);
+        c->last_scratch_bytes = part_slots * (64u * 8u + 16u) + (size_t)a->rows * 4u +
+                                (a->config_count > 1u ? (size_t)a->rows * sizeof(fg_sampler_config) : 0u);
+        const int e = fgk_launch_persistent_select(&l, ctas, c->stream);
         c->launches++;
         return e ? fg_cuda_fail(err, e, "persistent ring kernel") : FG_OK;
     }
