@@ -125,7 +125,8 @@ struct Params {
     // by several CTAs.  Each leaves its part's k best in `parts`; the last to finish
     // (ticket counter) merges them.
     // With enough rows for every CTA to have several, whole rows are dealt out instead
-    // (tiles_per_cta == 0): CTA c takes rows [c * rows / ctas, (c + 1) * rows / ctas).
+    // (tiles_per_cta == 0): CTA c takes rows c, c + ctas, c + 2 * ctas, ...  (the two CTAs
+    // of an SM, c and c + SMs, then differ by at most one row between them).
     uint32_t tiles_per_cta;
     uint32_t max_parts;             // most CTAs that share one row
     float *part_scores;             // [rows][max_parts][kMaxK]
@@ -150,8 +151,8 @@ struct UnitWalk {
         : row_tiles(row_tiles_), per_cta(p.tiles_per_cta) {
         const uint64_t all = (uint64_t)p.rows * row_tiles;
         if (per_cta == 0) {
-            at = (uint64_t)blockIdx.x * p.rows / gridDim.x * row_tiles;
-            stop = ((uint64_t)blockIdx.x + 1u) * p.rows / gridDim.x * row_tiles;
+            at = blockIdx.x;  // a row number in this mode
+            stop = p.rows;
         } else {
             at = min((uint64_t)blockIdx.x * per_cta, all);
             stop = min(at + per_cta, all);
@@ -159,18 +160,23 @@ struct UnitWalk {
     }
     __device__ __forceinline__ bool next(Unit &u) {
         if (at >= stop) return false;
+        if (per_cta == 0) {
+            u.row = (uint32_t)at;
+            u.first = 0;
+            u.end = row_tiles;
+            u.part = 0;
+            u.parts = 1;
+            at += gridDim.x;
+            return true;
+        }
         u.row = (uint32_t)(at / row_tiles);
         u.first = (uint32_t)(at % row_tiles);
         u.end = (uint32_t)min((uint64_t)row_tiles, u.first + (stop - at));
-        u.part = 0;
-        u.parts = 1;
-        if (per_cta != 0) {
-            const uint64_t row_begin = (uint64_t)u.row * row_tiles;
-            const uint32_t first_cta = (uint32_t)(row_begin / per_cta);
-            const uint32_t last_cta = (uint32_t)((row_begin + row_tiles - 1) / per_cta);
-            u.part = blockIdx.x - first_cta;
-            u.parts = last_cta - first_cta + 1;
-        }
+        const uint64_t row_begin = (uint64_t)u.row * row_tiles;
+        const uint32_t first_cta = (uint32_t)(row_begin / per_cta);
+        const uint32_t last_cta = (uint32_t)((row_begin + row_tiles - 1) / per_cta);
+        u.part = blockIdx.x - first_cta;
+        u.parts = last_cta - first_cta + 1;
         at += u.end - u.first;
         return true;
     }
