@@ -153,6 +153,39 @@ __device__ __forceinline__ void clear_histogram(NucleusShared &sh, uint32_t buck
     __syncthreads();
 }
 
+// Walks the scratch row: visit(value, index) for every element.  Eight values per thread
+// are in flight (two 128-bit loads) before the first is used: with one scalar load per
+// trip a pass over the row was a chain of L2 latencies.  Rows start 16-byte aligned.
+template <class Visit>
+__device__ __forceinline__ void walk_row(const float *values, uint32_t vocab, Visit visit) {
+    const uint32_t tid = threadIdx.x;
+    const float4 *wide = reinterpret_cast<const float4 *>(values);
+    const uint32_t quads = vocab / 4u;
+    uint32_t q = tid;
+    for (; q + kNucleusThreads < quads; q += 2 * kNucleusThreads) {
+        const float4 a = wide[q], b = wide[q + kNucleusThreads];
+        const uint32_t ia = q * 4u, ib = (q + kNucleusThreads) * 4u;
+        visit(a.x, ia);
+        visit(a.y, ia + 1u);
+        visit(a.z, ia + 2u);
+        visit(a.w, ia + 3u);
+        visit(b.x, ib);
+        visit(b.y, ib + 1u);
+        visit(b.z, ib + 2u);
+        visit(b.w, ib + 3u);
+    }
+    if (q < quads) {
+        const float4 a = wide[q];
+        const uint32_t ia = q * 4u;
+        visit(a.x, ia);
+        visit(a.y, ia + 1u);
+        visit(a.z, ia + 2u);
+        visit(a.w, ia + 3u);
+    }
+    const uint32_t rest = quads * 4u + tid;
+    if (rest < vocab) visit(values[rest], rest);
+}
+
 // Which elements of the scratch row take part in a descent.
 struct Nucleus {
     uint32_t key;     // value key of the last element inside
@@ -400,14 +433,13 @@ __device__ Position locate(NucleusShared &sh, NucleusList &list, const float *va
     Position found;
     found.ok = false;
     clear_histogram(sh, kBuckets);
-    for (uint32_t i = tid; i < vocab; i += kNucleusThreads) {
-        const float v = values[i];
-        if (is_nonfinite(v) || !inside.holds(float_key(v), i)) continue;
+    walk_row(values, vocab, [&](float v, uint32_t i) {
+        if (is_nonfinite(v) || !inside.holds(float_key(v), i)) return;
         const unsigned long long w = exp_fixed(((double)v - (double)top) * inv_t, sh.table);
         const uint32_t b = value_bucket(v, top);
         atomicAdd(&sh.mass[b], w);
         atomicAdd(&sh.count[b], 1u);
-    }
+    });
     __syncthreads();
     const unsigned long long target = find_crossing_up(sh, target_of, strict);
     found.total = sh.total_mass;
@@ -447,14 +479,13 @@ __device__ Position locate(NucleusShared &sh, NucleusList &list, const float *va
     // gather the bucket's members
     if (tid == 0) list.count = 0;
     __syncthreads();
-    for (uint32_t i = tid; i < vocab; i += kNucleusThreads) {
-        const float v = values[i];
-        if (is_nonfinite(v) || !inside.holds(float_key(v), i)) continue;
-        if (value_bucket(v, top) != bucket) continue;
+    walk_row(values, vocab, [&](float v, uint32_t i) {
+        if (is_nonfinite(v) || !inside.holds(float_key(v), i)) return;
+        if (value_bucket(v, top) != bucket) return;
         const uint32_t slot = atomicAdd(&list.count, 1u);
         list.value[slot] = v;
         list.id[slot] = i;
-    }
+    });
     __syncthreads();
     // order them: rank by counting, (value descending, id ascending); -0.0 and +0.0 tie
     for (uint32_t a = tid; a < members; a += kNucleusThreads) {
@@ -546,25 +577,63 @@ __global__ void __launch_bounds__(kNucleusThreads, 1) nucleus_select_kernel(cons
                     const_cast<uint32_t *>(p.history_global) + unit * p.history_stride_words,
                     p.bitmap_words, p.count_capacity, p.dense_wide != 0);
             }
-            for (uint32_t c = tid; c < n; c += kNucleusThreads) {
-                float v;
-                if (sizeof(T) == 2) v = bf16_bits_to_float(reinterpret_cast<const uint16_t *>(columns)[lo + c]);
-                else v = reinterpret_cast<const float *>(columns)[lo + c];
-                if (flags & 1u) {
-                    const uint32_t word = history.bitmap[c >> 5];
-                    if ((word >> (c & 31u)) & 1u) {
-                        float offset = flat_offset;
-                        if (flags & 2u)
-                            offset = penalty_offset(history.count(c >> 5, word, c & 31u),
-                                                    cfg.presence_penalty, cfg.frequency_penalty);
-                        v = penalise_with_offset(v, offset, repetition);
-                    }
+            // one column: penalise if seen, store, fold into the maximum
+            auto take = [&](float v, uint32_t c, uint32_t word) {
+                if ((word >> (c & 31u)) & 1u) {
+                    float offset = flat_offset;
+                    if (flags & 2u)
+                        offset = penalty_offset(history.count(c >> 5, word, c & 31u),
+                                                cfg.presence_penalty, cfg.frequency_penalty);
+                    v = penalise_with_offset(v, offset, repetition);
                 }
-                values[lo + c] = v;
                 if (!is_nonfinite(v)) {
                     best = fmaxf(best, v);
                     finite++;
                 }
+                return v;
+            };
+            const T *source = columns + lo;
+            uint32_t done = 0;
+            if ((reinterpret_cast<uintptr_t>(source) & 15u) == 0 && (lo & 3u) == 0) {
+                // four columns per thread and trip (one vector load, one bitmap word, one
+                // 128-bit store), two trips in flight
+                const uint32_t quads = n / 4u;
+                float4 *out = reinterpret_cast<float4 *>(values + lo);
+                auto load4 = [&](uint32_t q) {
+                    float4 v;
+                    if (sizeof(T) == 2) {
+                        const uint2 raw = reinterpret_cast<const uint2 *>(source)[q];
+                        v = make_float4(__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xffff0000u),
+                                        __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xffff0000u));
+                    } else {
+                        v = reinterpret_cast<const float4 *>(source)[q];
+                    }
+                    return v;
+                };
+                auto take4 = [&](float4 v, uint32_t q) {
+                    const uint32_t c = q * 4u;
+                    const uint32_t word = (flags & 1u) ? history.bitmap[c >> 5] : 0u;
+                    v.x = take(v.x, c, word);
+                    v.y = take(v.y, c + 1u, word);
+                    v.z = take(v.z, c + 2u, word);
+                    v.w = take(v.w, c + 3u, word);
+                    out[q] = v;
+                };
+                uint32_t q = tid;
+                for (; q + kNucleusThreads < quads; q += 2 * kNucleusThreads) {
+                    const float4 a = load4(q), b = load4(q + kNucleusThreads);
+                    take4(a, q);
+                    take4(b, q + kNucleusThreads);
+                }
+                if (q < quads) take4(load4(q), q);
+                done = quads * 4u;
+            }
+            for (uint32_t c = done + tid; c < n; c += kNucleusThreads) {
+                float v;
+                if (sizeof(T) == 2) v = bf16_bits_to_float(reinterpret_cast<const uint16_t *>(source)[c]);
+                else v = reinterpret_cast<const float *>(source)[c];
+                const uint32_t word = (flags & 1u) ? history.bitmap[c >> 5] : 0u;
+                values[lo + c] = take(v, c, word);
             }
         }
 #pragma unroll
