@@ -570,15 +570,52 @@ struct Stop {
     uint32_t tile, why, pending;
 };
 
-// The hot loop of one warp over tiles first .. end-1 of a row (which has `tiles`); the warps run it
+// Largest of three; a NaN loses against a number, as with fmaxf.
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+#ifdef FGK_NO_MAX3
+    return fmaxf(fmaxf(a, b), c);
+#else
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+#endif
+}
+
+// Largest of N values, three at a time (a short tree instead of a chain of N - 1).
+template <int N>
+__device__ __forceinline__ float largest(const float (&v)[N]) {
+    float level[N];
+#pragma unroll
+    for (int i = 0; i < N; i++) level[i] = v[i];
+    int n = N;
+#pragma unroll
+    for (int round = 0; round < 6; round++) {
+        if (n <= 1) break;
+        int m = 0;
+#pragma unroll
+        for (int i = 0; i < N; i += 3) {
+            if (i >= n) break;
+            if (i + 2 < n) level[m++] = fmax3(level[i], level[i + 1], level[i + 2]);
+            else if (i + 1 < n) level[m++] = fmaxf(level[i], level[i + 1]);
+            else level[m++] = level[i];
+        }
+        n = m;
+    }
+    return level[0];
+}
+
+// The hot loop of one warp over tiles first .. end-1 of a row; the warps run it
 // independently of one another, at most a ring's depth apart.  It calls nothing:
 // whatever is live across a call inside a loop is saved and restored on every trip.
+// Per tile and thread: four 128-bit shared loads, a tree of maxima, one compare, one
+// warp reduction that also carries the attention flag.  kRagged: the tiles may end
+// early (`valid_vectors` of them hold data); only a row's last tile needs that.
 //   kStopBefore  the attention flag is up and the warp has not touched `tile` yet
 //   kStopInside  a lane found a list full; `pending` holds its elements of `tile`
 //                still to be offered, and the warp still holds the stage
-template <typename T, bool kGreedy>
+template <typename T, bool kGreedy, bool kRagged>
 __device__ __noinline__ Stop hot_tiles(Shared &sh, Lists &L, const uint32_t *bitmap, const unsigned char *ring,
-                                       uint32_t first, uint32_t end, uint32_t tiles, uint32_t last_vectors,
+                                       uint32_t first, uint32_t end, uint32_t valid_vectors,
                                        const uint32_t row_sequence, const Row r, const float tau) {
     using V = Lanes<T>;
     constexpr int kPer = V::kPer;
@@ -589,35 +626,36 @@ __device__ __noinline__ Stop hot_tiles(Shared &sh, Lists &L, const uint32_t *bit
     for (uint32_t t = first; t < end; t++) {
         const uint32_t at = (row_sequence + t) % kStages, use = (row_sequence + t) / kStages;
         stop.tile = t;
-        // ---- wait for the tile, watching the flag ----
-        for (uint32_t polls = 0;; polls++) {
-            if (__any_sync(kFullMask, peek(&sh.attention) != 0)) {
-                stop.why = kStopBefore;
-                return stop;
+        // ---- the tile is usually there, or lands within one nap ----
+        if (!__all_sync(kFullMask, mbarrier_try_wait_sleeping(&sh.full[at], use & 1u, kNapNanoseconds))) {
+            // otherwise wait for it watching the flag (a warp that holds this stage may be
+            // waiting for this one at a meeting)
+            for (uint32_t polls = 0;; polls++) {
+                if (__any_sync(kFullMask, peek(&sh.attention) != 0)) {
+                    stop.why = kStopBefore;
+                    return stop;
+                }
+                const bool landed = peek(&sh.ring_error) != 0 ||
+                                    mbarrier_try_wait_sleeping(&sh.full[at], use & 1u, kNapNanoseconds);
+                if (__all_sync(kFullMask, landed)) break;
+                if (polls >= kWaitPolls) poke(&sh.ring_error, 1u);  // values are then garbage; the row fails
             }
-            const bool landed = peek(&sh.ring_error) != 0 ||
-                                mbarrier_try_wait_sleeping(&sh.full[at], use & 1u, kNapNanoseconds);
-            if (__all_sync(kFullMask, landed)) break;
-            if (polls >= kWaitPolls) poke(&sh.ring_error, 1u);  // values are then garbage; the row fails
         }
         const unsigned char *stage = ring + (size_t)at * kStageBytes;
         const uint4 *vectors = reinterpret_cast<const uint4 *>(stage);
-        const uint32_t valid_vectors = t + 1 == tiles ? last_vectors : kStageBytes / 16u;
         uint4 raw[kVectors];
 #pragma unroll
         for (int u = 0; u < kVectors; u++) {
             const uint32_t g = u * kConsumers + tid;
-            // the filler reads as a NaN in fp32 and as -inf in bf16: never reaches a bound
-            raw[u] = g < valid_vectors ? vectors[g]
-                                       : make_uint4(0xff80ff80u, 0xff80ff80u, 0xff80ff80u, 0xff80ff80u);
+            // (the filler reads as a NaN in fp32 and as -inf in bf16: never reaches a bound)
+            if (kRagged && g >= valid_vectors) raw[u] = make_uint4(0xff80ff80u, 0xff80ff80u, 0xff80ff80u, 0xff80ff80u);
+            else raw[u] = vectors[g];
         }
+        const uint32_t flagged = peek(&sh.attention);  // read early, used after the tile
         float v[kVectors * kPer];
 #pragma unroll
         for (int u = 0; u < kVectors; u++) V::unpack(raw[u], &v[u * kPer]);
-        float top = v[0];  // a NaN never wins a maximum
-#pragma unroll
-        for (int e = 1; e < kVectors * kPer; e++) top = fmaxf(top, v[e]);
-        bool hot = top >= tau;
+        bool hot = largest(v) >= tau;  // a NaN never wins a maximum
         if (kGreedy) {  // the argmax order must see NaN and both infinities, and magnitudes
                         // a repetition factor of at most 2^40 could push there
             uint32_t widest = 0;
@@ -629,19 +667,26 @@ __device__ __noinline__ Stop hot_tiles(Shared &sh, Lists &L, const uint32_t *bit
         if (hot) {
 #pragma unroll
             for (int e = 0; e < kVectors * kPer; e++) {
-                const bool live = (e / kPer) * kConsumers + tid < valid_vectors;
+                const bool live = !kRagged || (e / kPer) * kConsumers + tid < valid_vectors;
                 const bool wild = kGreedy && (__float_as_uint(v[e]) & 0x7fffffffu) >= 0x6b000000u;
                 if (live && (v[e] >= tau || wild)) pending |= 1u << e;
             }
             pending = offer<T, kGreedy>(sh, L, r, bitmap, stage, t, pending, tau, tau_id);
         }
-        if (__any_sync(kFullMask, pending != 0)) {
+        // one reduction tells the warp both things: somebody still has elements to offer (bit
+        // 0), somebody saw the flag up (bit 1)
+        const uint32_t news = __reduce_or_sync(kFullMask, (pending != 0 ? 1u : 0u) | (flagged != 0 ? 2u : 0u));
+        if (news & 1u) {
             stop.why = kStopInside;
             stop.pending = pending;
             return stop;
         }
-        // the warp is done with the stage
-        if (lane == 0) mbarrier_arrive(&sh.empty[at]);
+        if (lane == 0) mbarrier_arrive(&sh.empty[at]);  // the warp is done with the stage
+        if (news & 2u) {
+            stop.tile = t + 1;
+            stop.why = kStopBefore;
+            return stop;
+        }
     }
     stop.tile = end;
     stop.why = kStopDone;
@@ -1150,12 +1195,21 @@ persistent_select_kernel(const __grid_constant__ Params p) {
         FGK_PTICK(1);
 
         // ---- the further tiles: each warp at its own pace ----
+        // (a row's last tile may hold fewer than a stage's worth: it takes the variant of
+        // the loop that checks, everything before it the one that does not)
+        const uint32_t whole = kStageBytes / 16u;
+        const uint32_t plain_end = (u.end == tiles && last_vectors != whole) ? u.end - 1 : u.end;
         for (uint32_t t = u.first + 1; t < u.end;) {
-            const Stop stop =
-                r.greedy ? hot_tiles<T, true>(sh, L, bitmap, ring, t, u.end, tiles, last_vectors, row_sequence, r, tau)
-                         : hot_tiles<T, false>(sh, L, bitmap, ring, t, u.end, tiles, last_vectors, row_sequence, r, tau);
-            if (stop.why == kStopDone) break;
+            const bool ragged = t >= plain_end;
+            Stop stop;
+            if (ragged)
+                stop = r.greedy ? hot_tiles<T, true, true>(sh, L, bitmap, ring, t, u.end, last_vectors, row_sequence, r, tau)
+                                : hot_tiles<T, false, true>(sh, L, bitmap, ring, t, u.end, last_vectors, row_sequence, r, tau);
+            else
+                stop = r.greedy ? hot_tiles<T, true, false>(sh, L, bitmap, ring, t, plain_end, whole, row_sequence, r, tau)
+                                : hot_tiles<T, false, false>(sh, L, bitmap, ring, t, plain_end, whole, row_sequence, r, tau);
             t = stop.tile;
+            if (stop.why == kStopDone) continue;  // on to the ragged tile, or out
             if (stop.why == kStopBefore) {
                 FGK_PTICK(2);
                 tau = attend(sh, L, r);
