@@ -2,7 +2,7 @@
 
 Run where the reference tree is mounted:
 
-    make -C oracle reference REFERENCE=/root/reference
+    make -C oracle reference REFERENCE=<path of the reference tree>
     python tests/golden/make_golden.py
 
 It drives oracle/_ref/libfgref.so (the reference's src/sampler.c, src/util.c and
