@@ -357,9 +357,12 @@ struct NucleusList {
     uint32_t count;
 };
 
+// (fp32 arithmetic: the bucket edges need not be exact, only the same in every pass and
+// monotone in v, which one rounded subtraction and an exact scaling are; the fp64 pipe is
+// what the histogram passes are short of)
 __device__ __forceinline__ uint32_t value_bucket(float v, float top) {
-    const double below = ((double)top - (double)v) * 256.0;  // exact, >= 0
-    return below >= (double)(kBuckets - 1) ? (uint32_t)(kBuckets - 1) : (uint32_t)below;
+    const float below = __fmul_rn(__fsub_rn(top, v), 256.0f);  // >= 0
+    return below >= (float)(kBuckets - 1) ? (uint32_t)(kBuckets - 1) : (uint32_t)below;
 }
 
 // Like find_crossing but walking the buckets upwards from 0; also leaves the sum of

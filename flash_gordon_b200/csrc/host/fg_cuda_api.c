@@ -675,13 +675,18 @@ static fg_status run_stream(fg_cuda_context *c, const fg_cuda_sample_args *a,
             ctas = most;
             max_parts = 1u;
         }
-        const size_t part_slots = (size_t)a->rows * max_parts;
-        status = fg_cuda_reserve(&c->parts, &c->parts_bytes, part_slots * (64u * 8u + 16u), false, c, err);
-        if (status != FG_OK) return status;
-        unsigned char *base = c->parts;
-        l.part_scores = (float *)base;
-        l.part_ids = (uint32_t *)(base + part_slots * 64u * 4u);
-        l.part_meta = base + part_slots * 64u * 8u;
+        const size_t part_slots = max_parts > 1u ? (size_t)a->rows * max_parts : 0u; /* whole rows leave no parts */
+        l.part_scores = NULL;
+        l.part_ids = NULL;
+        l.part_meta = NULL;
+        if (part_slots != 0u) {
+            status = fg_cuda_reserve(&c->parts, &c->parts_bytes, part_slots * (64u * 8u + 16u), false, c, err);
+            if (status != FG_OK) return status;
+            unsigned char *base = c->parts;
+            l.part_scores = (float *)base;
+            l.part_ids = (uint32_t *)(base + part_slots * 64u * 4u);
+            l.part_meta = base + part_slots * 64u * 8u;
+        }
         l.splits = max_parts;
         l.split_len = (uint32_t)per_cta;
         l.bitmap_words = whole_bitmap;
