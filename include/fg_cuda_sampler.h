@@ -64,11 +64,12 @@ uint64_t fg_cuda_context_launches(const fg_cuda_context *context);
  * 16).  Results never depend on it. */
 fg_status fg_cuda_context_set_splits(fg_cuda_context *context, uint32_t splits, fg_error *err);
 /* Tuning knob, no reference counterpart: which of the two fused kernels a batch
- * takes — the register-prefetch kernel (any alignment) or the one that streams
- * rows through a shared-memory ring fed by bulk copies (rows whose starts are
- * 16-byte aligned).  AUTO is the library's choice, currently the
- * register-prefetch kernel, which measures faster; RING fails with
- * FG_ERR_ARGUMENT on rows it cannot take, RING_IF_POSSIBLE falls back instead.
+ * with a top-k cut takes — the persistent kernel that streams rows through a
+ * shared-memory ring fed by bulk copies (rows whose start, stride and length are
+ * multiples of 16 bytes, penalties that cannot raise a logit), or the
+ * register-prefetch kernel (anything).  AUTO is the library's choice: the ring
+ * kernel whenever it can take the batch.  RING fails with FG_ERR_ARGUMENT on a
+ * batch it cannot take, RING_IF_POSSIBLE falls back instead (as AUTO does).
  * Results never depend on it. */
 #define FG_CUDA_PATH_AUTO             0u
 #define FG_CUDA_PATH_REGISTERS        1u
