@@ -152,6 +152,16 @@ def load_library() -> ctypes.CDLL:
         "fg_cuda_sample_batch_static": (c_int, [c_int, P, POINTER(SampleArgs), E]),
         "fg_cuda_shard_topk": (c_int, [P, POINTER(SampleArgs), u32, u32, u32, P, P, E]),
         "fg_cuda_merge_select": (c_int, [P, POINTER(SampleArgs), P, P, u32, u32, P, P, E]),
+        "fg_dist_unique_id": (c_int, [P, E]),
+        "fg_dist_create": (c_int, [P, u32, u32, P, u32, POINTER(P), E]),
+        "fg_dist_destroy": (None, [P]),
+        "fg_dist_ranks": (u32, [P]),
+        "fg_dist_rank": (u32, [P]),
+        "fg_dist_shard_span": (None, [u32, u32, u32, POINTER(u32), POINTER(u32)]),
+        "fg_dist_sample_vocab_sharded": (c_int, [P, POINTER(SampleArgs), u32, u32, E]),
+        "fg_dist_gather_rows": (c_int, [P, P, P, P, u32, P, P, P, E]),
+        # test seam of the ring kernel (csrc/host/fg_host_internal.h; not in the public headers)
+        "fg_cuda_internal_ring_controls": (c_int, [P, u32, u32, u32, u32, u32]),
     }
     for name, (restype, argtypes) in sig.items():
         fn = getattr(lib, name)

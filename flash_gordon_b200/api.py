@@ -121,6 +121,15 @@ class Context:
         if status != FG_OK:
             raise FgStatusError(status, err.text())
 
+    def ring_controls(self, deal: int = 0, wait_polls: int = 0, withhold: tuple[int, int] | None = None) -> None:
+        """Test seam of the ring kernel: how work is dealt out (0 planner, 1 whole rows,
+        2 tiles), the poll budget of its device-side waits (0 = default), and one tile
+        (CTA, request number of its warp 0) that is never fetched, so that a wait runs out."""
+        armed, cta, issue = (0, 0, 0) if withhold is None else (1, withhold[0], withhold[1])
+        status = self.lib.fg_cuda_internal_ring_controls(self.handle, deal, wait_polls, armed, cta, issue)
+        if status != FG_OK:
+            raise FgStatusError(status, "invalid ring controls")
+
     def set_path(self, path: int) -> None:
         """0 automatic, 1 register-prefetch kernel, 2 shared-memory ring kernel, 3 ring where rows allow."""
         err = FgError()

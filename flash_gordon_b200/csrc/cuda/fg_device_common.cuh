@@ -269,6 +269,6 @@ __device__ __forceinline__ HistoryView make_history_view(uint32_t *memory, uint3
 }
 
 // fg_status values used on the device (include/fg.h).
-constexpr uint32_t kOk = 0u, kErrFormat = 4u, kErrMismatch = 5u, kErrLimit = 8u;
+constexpr uint32_t kOk = 0u, kErrArgument = 2u, kErrFormat = 4u, kErrMismatch = 5u, kErrLimit = 8u;
 
 }  // namespace fgk

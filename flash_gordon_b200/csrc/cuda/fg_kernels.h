@@ -19,8 +19,6 @@ extern "C" {
 
 /* dynamic shared memory a streaming CTA may ask for (static part comes on top) */
 #define FGK_STREAM_MAX_DYNAMIC_SMEM (200 * 1024)
-/* dynamic shared memory that still lets four CTAs share one SM */
-#define FGK_STREAM_COMFORT_DYNAMIC_SMEM (44 * 1024)
 
 /* ---- runtime plumbing (fg_runtime.cu) ---- */
 int fgk_device_count(int *count);
@@ -37,9 +35,6 @@ int fgk_memset_async(void *pointer, int value, size_t bytes, void *stream);
 int fgk_copy_to_device_async(void *device, const void *host, size_t bytes, void *stream);
 int fgk_copy_to_host_async(void *host, const void *device, size_t bytes, void *stream);
 const char *fgk_error_string(int cuda_error);
-/* 1 when `pointer` is device-accessible memory of the current context's device
- * (or its provenance cannot be told), 0 when it is plainly host memory. */
-int fgk_pointer_is_device(const void *pointer);
 
 /* ---- outputs shared by the sampling launches ---- */
 typedef struct fgk_select_output {
@@ -72,6 +67,7 @@ typedef struct fgk_stream_launch {
     const float *uniforms;
     float *shard_scores;
     uint32_t *shard_ids;
+    uint32_t shard_stride; /* elements between consecutive candidates: 0 or 1 separate arrays, 2 (value, id) pairs */
     float *part_scores;
     uint32_t *part_ids;
     void *part_meta;
@@ -83,12 +79,16 @@ typedef struct fgk_stream_launch {
     uint32_t *history_global;
     uint64_t history_stride_words;
     void *history_meta; /* 8 bytes per (row, split); NULL when the batch has no history */
+    /* persistent kernel only: polls before a device-side wait gives up (0 = the default, about
+     * two seconds), and the test seam that makes one wait run out: warp 0 of CTA withhold_cta
+     * never asks the copy engine for its withhold_issue-th tile */
+    uint32_t wait_polls;
+    uint32_t withhold_armed, withhold_cta, withhold_issue;
     fgk_select_output out;
 } fgk_stream_launch;
 
 uint32_t fgk_stream_max_splits(void);
 uint32_t fgk_stream_tile(void);
-uint32_t fgk_stream_threads(void);
 uint64_t fgk_stream_part_meta_bytes(void);
 uint64_t fgk_stream_dynamic_smem(uint32_t bitmap_words, uint32_t count_capacity, uint32_t dense_wide);
 int fgk_stream_prepare(void);
@@ -96,16 +96,17 @@ int fgk_launch_stream_select(const fgk_stream_launch *launch, void *stream);
 
 /* ---- persistent ring kernel (fg_persistent_kernel.cu) ----
  * Takes a fgk_stream_launch with rows and row stride multiples of 16 bytes and only rows
- * whose penalties cannot raise a logit.  Work is dealt out in 16 KB tiles: `split_len`
- * holds the tiles per CTA, `splits` the most CTAs that can share one row; part_* and
- * tickets as for the streaming kernel.  Of the history fields it uses bitmap_words alone
- * (the bitmap lives behind the ring in dynamic shared memory). */
-#define FGK_PERSIST_MAX_DYNAMIC_SMEM (200 * 1024)
-uint64_t fgk_persistent_dynamic_smem(uint32_t bitmap_words);
-/* CTAs of the kernel one SM holds at this much dynamic shared memory (0 on error) */
-uint32_t fgk_persistent_ctas_per_sm(uint32_t dtype, uint64_t dynamic_smem);
+ * whose penalties cannot raise a logit.  Work is dealt out in 4 KB tiles: `split_len`
+ * holds the tiles per CTA (0: whole rows, dealt round-robin), `splits` the most CTAs that
+ * can share one row; part_* and tickets as for the streaming kernel.  Of the history
+ * fields it uses bitmap_words alone (the bitmaps live in dynamic shared memory). */
+/* dynamic shared memory for that bitmap size and how many bitmap buffers fit (2 or 1);
+ * 0 when the kernel cannot take the vocabulary */
+uint64_t fgk_persistent_dynamic_smem(uint32_t bitmap_words, uint32_t *bitmap_buffers);
 uint32_t fgk_persistent_row_tiles(uint32_t dtype, uint32_t vocab);
-uint32_t fgk_persistent_max_parts(void);
+uint32_t fgk_persistent_tiles_abreast(void);
+/* most parts of one row the merge takes when each hands over up to k survivors */
+uint32_t fgk_persistent_max_parts(uint32_t k);
 int fgk_persistent_prepare(void);
 int fgk_launch_persistent_select(const fgk_stream_launch *launch, uint32_t ctas, void *stream);
 
@@ -113,6 +114,7 @@ typedef struct fgk_merge_launch {
     const float *scores;
     const uint32_t *ids;
     uint32_t rows, shards, k_shard;
+    uint32_t stride; /* elements between consecutive candidates: 0 or 1 separate arrays, 2 (value, id) pairs */
     uint32_t check_spans;
     uint32_t span_first[16], span_width[16];
     const void *configs_device;
@@ -153,6 +155,22 @@ int fgk_nucleus_prepare(void);
 int fgk_launch_nucleus_select(const fgk_nucleus_launch *launch, void *stream);
 /* the history pass (fills history_global / history_meta) */
 int fgk_launch_history_build(const fgk_stream_launch *launch, void *stream);
+
+/* ---- NCCL behind plain C (fg_nccl.cu); libnccl.so.2 is opened on first use ---- */
+#define FGK_NCCL_ID_BYTES 128
+#define FGK_NCCL_MISSING (-1) /* the library or one of its symbols could not be loaded */
+#define FGK_NCCL_TIMEOUT (-2) /* a deadline passed while waiting for other ranks */
+#define FGK_NCCL_FAILED  (-3) /* NCCL reported an error */
+int fgk_nccl_load(void);
+int fgk_nccl_version(void); /* 0 when NCCL cannot be loaded */
+int fgk_nccl_unique_id(void *id128);
+int fgk_nccl_create(void **comm, uint32_t ranks, uint32_t rank, const void *id128, uint32_t timeout_ms);
+int fgk_nccl_all_gather(void *comm, const void *send, void *receive, size_t bytes_per_rank, void *stream,
+                        uint32_t timeout_ms);
+void fgk_nccl_abort(void *comm);
+void fgk_nccl_destroy(void *comm);
+/* cudaStreamSynchronize with a deadline: 0, a cudaError_t, or FGK_NCCL_TIMEOUT */
+int fgk_stream_wait_deadline(void *stream, uint32_t timeout_ms);
 
 /* ---- device operators (fg_ops_kernels.cu) ---- */
 int fgk_launch_apply_penalties(float *logits, const uint32_t *counts, uint32_t values,

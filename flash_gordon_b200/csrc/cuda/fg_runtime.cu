@@ -55,13 +55,3 @@ extern "C" int fgk_copy_to_host_async(void *host, const void *device, size_t byt
 extern "C" const char *fgk_error_string(int cuda_error) {
     return cudaGetErrorString(static_cast<cudaError_t>(cuda_error));
 }
-
-extern "C" int fgk_pointer_is_device(const void *pointer) {
-    cudaPointerAttributes attributes;
-    const cudaError_t e = cudaPointerGetAttributes(&attributes, pointer);
-    if (e != cudaSuccess) {
-        (void)cudaGetLastError();
-        return 1;
-    }
-    return attributes.type == cudaMemoryTypeDevice || attributes.type == cudaMemoryTypeManaged;
-}

@@ -53,6 +53,7 @@ struct StreamParams {
     const float *uniforms;
     float *shard_scores;
     uint32_t *shard_ids;
+    uint32_t shard_stride;          // elements between consecutive candidates (2: interleaved pairs)
     float *part_scores;             // [rows][splits][64]
     uint32_t *part_ids;
     PartMeta *part_meta;            // [rows][splits]
@@ -630,11 +631,20 @@ __device__ __noinline__ void finish_split(const StreamParams &p, StreamShared &s
 
     if (shard_mode) {
         sort_candidates(sh.cand, sh.fin, held);
+        // a greedy row's NaN/Inf with the smallest id goes first, as the slice's argmax
+        // cascade of src/output.c:320-344 would report it; the finite ones follow
+        const uint32_t lead = greedy && wild_id != kPaddingId ? 1u : 0u;
         if (tid < k) {
-            const size_t at = (size_t)row * k + tid;
-            const bool live = tid < held && !bad_history;
-            p.shard_scores[at] = live ? sh.fin.score[tid] : __uint_as_float(0xff800000u);
-            p.shard_ids[at] = live ? sh.fin.id[tid] : kPaddingId;
+            const size_t at = ((size_t)row * k + tid) * p.shard_stride;
+            const bool live = tid >= lead && tid - lead < held && !bad_history;
+            float score = live ? sh.fin.score[tid - lead] : __uint_as_float(0xff800000u);
+            uint32_t id = live ? sh.fin.id[tid - lead] : kPaddingId;
+            if (lead && tid == 0 && !bad_history) {
+                score = __uint_as_float(wild_bits);
+                id = wild_id;
+            }
+            p.shard_scores[at] = score;
+            p.shard_ids[at] = id;
         }
         if (tid == 0) {
             p.out.row_status[row] = bad_history;
@@ -842,7 +852,9 @@ stream_select_kernel(const __grid_constant__ StreamParams p) {
 #endif
     const SamplerConfig cfg = p.config_count > 1 ? p.configs[row] : p.config0;
     const bool shard_mode = p.shard_k != 0;
-    const bool greedy = !shard_mode && cfg.temperature == 0.0f;
+    // (a shard of a greedy row keeps k_shard candidates like any other, and on top of them
+    // notes the NaN/Inf the argmax order would put first: the merge must see it)
+    const bool greedy = cfg.temperature == 0.0f;
     if (!shard_mode && !greedy && cfg.top_k == 0) return;  // rows without a top-k cut use the nucleus kernel
 
     const uint32_t lo = split * p.split_len;
@@ -873,10 +885,6 @@ stream_select_kernel(const __grid_constant__ StreamParams p) {
     // ---- 1. history slice -> bitmap / running popcount / offsets ----
     state.flags = build_history(p, sh, dyn_smem, row, lo, state.n, cfg);
     FGK_TICK(0);
-#ifdef FGK_EXPERIMENT_HISTORY_ONLY
-    if (tid == 0) p.out.row_status[row] = 0;
-    return;
-#endif
 
     // ---- 2. stream the columns ----
     // Tiles 1 .. full-1 of a 16-byte aligned row take the fast loop below: 128-bit
@@ -984,6 +992,7 @@ struct MergeParams {
     const float *scores;
     const uint32_t *ids;
     uint32_t rows, shards, k_shard;
+    uint32_t stride;                // elements between consecutive candidates (2: interleaved (value, id) pairs)
     uint32_t check_spans;           // sharded merge: range-check ids, a NaN/Inf finalist is an error
     uint32_t span_first[16], span_width[16];
     const SamplerConfig *configs;
@@ -1009,7 +1018,7 @@ __global__ void __launch_bounds__(kThreads) merge_select_kernel(const MergeParam
     const uint32_t total = p.shards * p.k_shard;  // <= kCandCap, checked by the host
     for (uint32_t i = tid; i < total; i += kThreads) {
         const uint32_t shard = i / p.k_shard, within = i % p.k_shard;
-        const size_t at = ((size_t)shard * p.rows + row) * p.k_shard + within;
+        const size_t at = (((size_t)shard * p.rows + row) * p.k_shard + within) * p.stride;
         const float score = p.scores[at];
         const uint32_t id = p.ids[at];
         if (id == kPaddingId && p.check_spans) continue;  // padding of a short shard
@@ -1027,7 +1036,7 @@ __global__ void __launch_bounds__(kThreads) merge_select_kernel(const MergeParam
     if (greedy && sh.wild_id != kPaddingId) {
         for (uint32_t i = tid; i < total; i += kThreads) {
             const uint32_t shard = i / p.k_shard, within = i % p.k_shard;
-            const size_t at = ((size_t)shard * p.rows + row) * p.k_shard + within;
+            const size_t at = (((size_t)shard * p.rows + row) * p.k_shard + within) * p.stride;
             if (p.ids[at] == sh.wild_id && is_nonfinite(p.scores[at]))
                 sh.wild_bits = __float_as_uint(p.scores[at]);
         }
@@ -1107,7 +1116,6 @@ static SamplerConfig to_device_config(const fg_sampler_config *c) {
 
 extern "C" uint32_t fgk_stream_max_splits(void) { return kMaxSplits; }
 extern "C" uint32_t fgk_stream_tile(void) { return kTile; }
-extern "C" uint32_t fgk_stream_threads(void) { return kThreads; }
 extern "C" uint64_t fgk_stream_part_meta_bytes(void) { return sizeof(PartMeta); }
 
 // bitmap words, then (only when counts are kept) 16-bit running popcounts and the
@@ -1154,6 +1162,7 @@ static StreamParams to_stream_params(const fgk_stream_launch *l) {
     p.uniforms = l->uniforms;
     p.shard_scores = l->shard_scores;
     p.shard_ids = l->shard_ids;
+    p.shard_stride = l->shard_stride ? l->shard_stride : 1u;
     p.part_scores = l->part_scores;
     p.part_ids = l->part_ids;
     p.part_meta = reinterpret_cast<PartMeta *>(l->part_meta);
@@ -1195,6 +1204,7 @@ extern "C" int fgk_launch_merge_select(const fgk_merge_launch *l, void *stream) 
     p.rows = l->rows;
     p.shards = l->shards;
     p.k_shard = l->k_shard;
+    p.stride = l->stride ? l->stride : 1u;
     p.check_spans = l->check_spans;
     for (int i = 0; i < 16; i++) {
         p.span_first[i] = l->span_first[i];
@@ -1230,6 +1240,9 @@ extern "C" int fgk_static_scratch_address(int device, void **address) {
         void *found = nullptr;
         e = cudaGetSymbolAddress(&found, fgk_static_scratch);
         if (e != cudaSuccess) return (int)e;
+        // the kernel's shared-memory opt-in belongs to the same once-per-device set-up
+        const int prepared = fgk_stream_prepare();
+        if (prepared != 0) return prepared;
         known[device] = found;
     }
     *address = known[device];

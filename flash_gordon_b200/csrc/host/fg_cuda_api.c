@@ -167,6 +167,21 @@ fg_status fg_cuda_context_set_path(fg_cuda_context *c, uint32_t path, fg_error *
     return FG_OK;
 }
 
+/* Test seam (declared in fg_host_internal.h only): how the ring kernel deals out work
+ * (0 as the planner likes, 1 whole rows, 2 tiles), how many polls its device-side waits
+ * take before they give up (0 = default), and one tile that is never fetched so that a wait
+ * does run out (armed != 0: warp 0 of CTA `cta` skips its `issue`-th request). */
+fg_status fg_cuda_internal_ring_controls(fg_cuda_context *c, uint32_t deal, uint32_t wait_polls,
+                                         uint32_t armed, uint32_t cta, uint32_t issue) {
+    if (!c || deal > 2u) return FG_ERR_ARGUMENT;
+    c->ring_deal = deal;
+    c->ring_wait_polls = wait_polls;
+    c->ring_withhold_armed = armed;
+    c->ring_withhold_cta = cta;
+    c->ring_withhold_issue = issue;
+    return FG_OK;
+}
+
 fg_status fg_cuda_begin(fg_cuda_context *c, fg_error *err) {
     if (!c || c->batch_active) {
         fg_error_set(err, FG_ERR_ARGUMENT, "invalid CUDA batch begin");
@@ -563,19 +578,22 @@ static fg_status upload_configs(fg_cuda_context *c, const fg_cuda_sample_args *a
     return FG_OK;
 }
 
-/* Waits for the stream and turns the device's first-error word into a status. */
+/* Waits for the stream and turns the device's first-error word into a status.  The word
+ * after it says why a row ended with FG_ERR_LIMIT when it was not the history's length. */
 static fg_status collect_status(fg_cuda_context *c, fg_error *err) {
-    uint64_t word = UINT64_MAX;
-    int e = fgk_copy_to_host_async(&word, c->first_error, 8u, c->stream);
+    uint64_t words[2] = {UINT64_MAX, UINT64_MAX};
+    int e = fgk_copy_to_host_async(words, c->first_error, 16u, c->stream);
     if (!e) e = fgk_stream_synchronize(c->stream);
     if (e) return fg_cuda_fail(err, e, "sampling kernels");
-    if (word == UINT64_MAX) return FG_OK;
-    const fg_status status = (fg_status)(word & 0xffu);
-    const uint64_t row = word >> 8;
+    if (words[0] == UINT64_MAX) return FG_OK;
+    const fg_status status = (fg_status)(words[0] & 0xffu);
+    const uint64_t row = words[0] >> 8;
     const char *why = "row failed";
     if (status == FG_ERR_FORMAT) why = "no finite candidate, invalid penalized finalist, softmax failure or history token outside vocabulary";
     else if (status == FG_ERR_MISMATCH) why = "invalid output finalist";
+    else if (status == FG_ERR_LIMIT && words[1] == 1u) why = "a device-side wait ran out (a tile never landed or a warp never came)";
     else if (status == FG_ERR_LIMIT) why = "history longer than history_max";
+    else if (status == FG_ERR_ARGUMENT) why = "a penalty that can raise a logit reached the kernel for lowering penalties";
     fg_error_set(err, status, "row %llu: %s", (unsigned long long)row, why);
     return status;
 }
@@ -583,7 +601,7 @@ static fg_status collect_status(fg_cuda_context *c, fg_error *err) {
 static fg_status run_stream(fg_cuda_context *c, const fg_cuda_sample_args *a,
                             const batch_traits *traits, uint32_t vocab_offset,
                             uint32_t vocab_total, uint32_t shard_k, float *shard_scores,
-                            uint32_t *shard_ids, fg_error *err) {
+                            uint32_t *shard_ids, uint32_t shard_stride, fg_error *err) {
     stream_plan plan;
     if (!plan_stream(c, a->rows, a->vocab, a->history_max, traits->penalties, traits->counts, &plan)) {
         fg_error_set(err, FG_ERR_LIMIT, "history structure does not fit shared memory");
@@ -593,9 +611,7 @@ static fg_status run_stream(fg_cuda_context *c, const fg_cuda_sample_args *a,
     const size_t slots = (size_t)a->rows * plan.splits;
     const size_t meta_bytes = (size_t)fgk_stream_part_meta_bytes();
     const size_t part_bytes = plan.splits > 1u ? slots * (64u * 8u + meta_bytes) : 0u;
-    if (part_bytes) status = fg_cuda_reserve(&c->parts, &c->parts_bytes, part_bytes, false, c, err);
-    if (status == FG_OK)
-        status = fg_cuda_reserve((void **)&c->tickets, &c->tickets_bytes, (size_t)a->rows * 4u, true, c, err);
+    status = fg_cuda_reserve((void **)&c->tickets, &c->tickets_bytes, (size_t)a->rows * 4u, true, c, err);
     const void *configs_device = NULL;
     if (status == FG_OK) status = upload_configs(c, a, &configs_device, err);
     if (status != FG_OK) return status;
@@ -623,12 +639,7 @@ static fg_status run_stream(fg_cuda_context *c, const fg_cuda_sample_args *a,
     l.uniforms = a->uniforms;
     l.shard_scores = shard_scores;
     l.shard_ids = shard_ids;
-    if (part_bytes) {
-        unsigned char *base = c->parts;
-        l.part_scores = (float *)base;
-        l.part_ids = (uint32_t *)(base + slots * 64u * 4u);
-        l.part_meta = base + slots * 64u * 8u;
-    }
+    l.shard_stride = shard_stride;
     l.tickets = c->tickets;
     l.bitmap_words = plan.bitmap_words;
     l.count_capacity = plan.count_capacity;
@@ -642,37 +653,40 @@ static fg_status run_stream(fg_cuda_context *c, const fg_cuda_sample_args *a,
     const bool ring_ok = ((uintptr_t)a->logits % 16u) == 0u && (a->row_stride * element) % 16u == 0u &&
                          ((size_t)a->vocab * element) % 16u == 0u && c->forced_splits <= 1u &&
                          !(traits->penalties && traits->raising) &&
-                         fgk_persistent_dynamic_smem(whole_bitmap) <= FGK_PERSIST_MAX_DYNAMIC_SMEM;
+                         fgk_persistent_dynamic_smem(whole_bitmap, NULL) != 0u;
     if (c->path == FG_CUDA_PATH_RING && !ring_ok) {
         fg_error_set(err, FG_ERR_ARGUMENT,
                      "the ring path needs whole 16-byte aligned rows and penalties that only lower logits");
         return FG_ERR_ARGUMENT;
     }
-    /* AUTO: the persistent kernel whenever it can take the batch (measured on B200 it is
-     * ahead at every batch size: 29 against 38 us for one row of 151,936 fp32 logits,
-     * 48 against 71 us for 64 rows, 186 against 255 us for 1024). */
-    uint32_t per_sm = fgk_persistent_ctas_per_sm(a->dtype, fgk_persistent_dynamic_smem(whole_bitmap));
-    if (per_sm == 0u) per_sm = 1u;
-    const uint32_t most = c->sm_count * per_sm;
+    /* AUTO: the persistent kernel whenever it can take the batch. */
+    const uint32_t most = c->sm_count; /* one CTA per SM */
     const bool take_ring = c->path != FG_CUDA_PATH_REGISTERS;
     if (ring_ok && take_ring) {
-        /* Work goes out in 16 KB tiles, the same number to every CTA, so a row may be shared
-         * by several CTAs; a share is at least so long that no row has more parts than the
-         * merge takes. */
+        /* Work goes out in 4 KB tiles, the same number to every CTA, so a row may be shared
+         * by several CTAs.  A share is at least as long as the CTA's warps look at side by
+         * side, and so long that no row has more parts than the merge takes. */
+        uint32_t k_most = shard_k;
+        for (uint32_t i = 0; !shard_k && i < a->config_count; i++) {
+            const uint32_t k = a->configs[i].temperature == 0.0f ? 1u : a->configs[i].top_k;
+            if (k > k_most) k_most = k;
+        }
         const uint32_t row_tiles = fgk_persistent_row_tiles(a->dtype, a->vocab);
         const uint64_t all_tiles = (uint64_t)a->rows * row_tiles;
-        const uint32_t parts_limit = fgk_persistent_max_parts();
+        const uint32_t parts_limit = fgk_persistent_max_parts(k_most);
         uint64_t per_cta = (all_tiles + most - 1u) / most;
         const uint64_t shortest = (row_tiles + parts_limit - 2u) / (parts_limit - 1u);
         if (per_cta < shortest) per_cta = shortest;
+        if (per_cta < fgk_persistent_tiles_abreast()) per_cta = fgk_persistent_tiles_abreast();
         uint32_t ctas = (uint32_t)((all_tiles + per_cta - 1u) / per_cta);
         uint32_t max_parts = (uint32_t)((row_tiles + per_cta - 1u) / per_cta) + 1u;
         if (max_parts > parts_limit) max_parts = parts_limit;
-        /* With two or more rows for every CTA whole rows are dealt out: a shared row costs
-         * its fixed work once per part, which on B200 outweighs the better balance. */
-        if (a->rows >= 2u * most) {
+        /* With several rows for every CTA whole rows are dealt out: a shared row costs its
+         * fixed work once per part and a merge. */
+        const bool whole_rows = c->ring_deal == 1u || (c->ring_deal == 0u && a->rows >= 4u * most);
+        if (whole_rows) {
             per_cta = 0u;
-            ctas = most;
+            ctas = a->rows < most ? a->rows : most;
             max_parts = 1u;
         }
         const size_t part_slots = max_parts > 1u ? (size_t)a->rows * max_parts : 0u; /* whole rows leave no parts */
@@ -690,11 +704,24 @@ static fg_status run_stream(fg_cuda_context *c, const fg_cuda_sample_args *a,
         l.splits = max_parts;
         l.split_len = (uint32_t)per_cta;
         l.bitmap_words = whole_bitmap;
+        l.wait_polls = c->ring_wait_polls;
+        l.withhold_armed = c->ring_withhold_armed;
+        l.withhold_cta = c->ring_withhold_cta;
+        l.withhold_issue = c->ring_withhold_issue;
         c->last_scratch_bytes = part_slots * (64u * 8u + 16u) + (size_t)a->rows * 4u +
                                 (a->config_count > 1u ? (size_t)a->rows * sizeof(fg_sampler_config) : 0u);
         const int e = fgk_launch_persistent_select(&l, ctas, c->stream);
         c->launches++;
         return e ? fg_cuda_fail(err, e, "persistent ring kernel") : FG_OK;
+    }
+    /* the streaming kernel's hand-off between the splits of a row, reserved only when it runs */
+    if (part_bytes) {
+        status = fg_cuda_reserve(&c->parts, &c->parts_bytes, part_bytes, false, c, err);
+        if (status != FG_OK) return status;
+        unsigned char *base = c->parts;
+        l.part_scores = (float *)base;
+        l.part_ids = (uint32_t *)(base + slots * 64u * 4u);
+        l.part_meta = base + slots * 64u * 8u;
     }
     const int e = fgk_launch_stream_select(&l, c->stream);
     c->launches++;
@@ -779,7 +806,7 @@ static fg_status run_nucleus(fg_cuda_context *c, const fg_cuda_sample_args *a,
 }
 
 static fg_status arm_first_error(fg_cuda_context *c, fg_error *err) {
-    const int e = fgk_memset_async(c->first_error, 0xff, 8u, c->stream);
+    const int e = fgk_memset_async(c->first_error, 0xff, 16u, c->stream); /* the error word and its cause */
     return e ? fg_cuda_fail(err, e, "arming the error word") : FG_OK;
 }
 
@@ -790,15 +817,17 @@ fg_status fg_cuda_sample_batch(fg_cuda_context *c, const fg_cuda_sample_args *a,
     status = fg_cuda_enter(c, err);
     if (status == FG_OK) status = arm_first_error(c, err);
     if (status == FG_OK && traits.topk_rows)
-        status = run_stream(c, a, &traits, 0u, a->vocab, 0u, NULL, NULL, err);
+        status = run_stream(c, a, &traits, 0u, a->vocab, 0u, NULL, NULL, 1u, err);
     if (status == FG_OK && traits.nucleus) status = run_nucleus(c, a, &traits, err);
     if (status != FG_OK || (a->flags & FG_CUDA_SAMPLE_ASYNC)) return status;
     return collect_status(c, err);
 }
 
-fg_status fg_cuda_shard_topk(fg_cuda_context *c, const fg_cuda_sample_args *a, uint32_t vocab_offset,
-                             uint32_t vocab_total, uint32_t k_shard, float *candidate_scores,
-                             uint32_t *candidate_ids, fg_error *err) {
+/* The shard step with an explicit candidate layout (stride 1: two arrays, 2: interleaved
+ * (value, id) pairs).  Enqueues only. */
+fg_status fg_cuda_shard_topk_layout(fg_cuda_context *c, const fg_cuda_sample_args *a, uint32_t vocab_offset,
+                                    uint32_t vocab_total, uint32_t k_shard, float *candidate_scores,
+                                    uint32_t *candidate_ids, uint32_t stride, fg_error *err) {
     batch_traits traits;
     fg_status status = check_batch(c, a, true, &traits, err);
     if (status != FG_OK) return status;
@@ -811,15 +840,27 @@ fg_status fg_cuda_shard_topk(fg_cuda_context *c, const fg_cuda_sample_args *a, u
     if (status == FG_OK) status = arm_first_error(c, err);
     if (status == FG_OK)
         status = run_stream(c, a, &traits, vocab_offset, vocab_total, k_shard, candidate_scores,
-                            candidate_ids, err);
+                            candidate_ids, stride, err);
+    return status;
+}
+
+fg_status fg_cuda_shard_topk(fg_cuda_context *c, const fg_cuda_sample_args *a, uint32_t vocab_offset,
+                             uint32_t vocab_total, uint32_t k_shard, float *candidate_scores,
+                             uint32_t *candidate_ids, fg_error *err) {
+    const fg_status status = fg_cuda_shard_topk_layout(c, a, vocab_offset, vocab_total, k_shard,
+                                                       candidate_scores, candidate_ids, 1u, err);
     if (status != FG_OK || (a->flags & FG_CUDA_SAMPLE_ASYNC)) return status;
     return collect_status(c, err);
 }
 
-fg_status fg_cuda_merge_select(fg_cuda_context *c, const fg_cuda_sample_args *a,
-                               const float *candidate_scores, const uint32_t *candidate_ids,
-                               uint32_t shards, uint32_t k_shard, const uint32_t *shard_first,
-                               const uint32_t *shard_width, fg_error *err) {
+/* The merge step over [shard][row][k_shard] candidates with an explicit layout.  Enqueues
+ * only; does not re-arm the error word when `keep_errors` (the shard step of the same call
+ * may already have noted a row). */
+fg_status fg_cuda_merge_select_layout(fg_cuda_context *c, const fg_cuda_sample_args *a,
+                                      const float *candidate_scores, const uint32_t *candidate_ids,
+                                      uint32_t stride, uint32_t shards, uint32_t k_shard,
+                                      const uint32_t *shard_first, const uint32_t *shard_width,
+                                      bool keep_errors, fg_error *err) {
     if (!c || !a || !a->rows || !a->configs || (a->config_count != 1u && a->config_count != a->rows) ||
         !a->tokens || !a->token_logits || !a->row_status || !candidate_scores || !candidate_ids ||
         !shards || shards > 16u || k_shard < 1u || k_shard > 64u || !shard_first || !shard_width) {
@@ -847,7 +888,7 @@ fg_status fg_cuda_merge_select(fg_cuda_context *c, const fg_cuda_sample_args *a,
         return FG_ERR_ARGUMENT;
     }
     fg_status status = fg_cuda_enter(c, err);
-    if (status == FG_OK) status = arm_first_error(c, err);
+    if (status == FG_OK && !keep_errors) status = arm_first_error(c, err);
     const void *configs_device = NULL;
     if (status == FG_OK) status = upload_configs(c, a, &configs_device, err);
     if (status != FG_OK) return status;
@@ -858,6 +899,7 @@ fg_status fg_cuda_merge_select(fg_cuda_context *c, const fg_cuda_sample_args *a,
     l.rows = a->rows;
     l.shards = shards;
     l.k_shard = k_shard;
+    l.stride = stride;
     l.check_spans = 1u;
     for (uint32_t s = 0; s < shards; s++) {
         l.span_first[s] = shard_first[s];
@@ -870,10 +912,20 @@ fg_status fg_cuda_merge_select(fg_cuda_context *c, const fg_cuda_sample_args *a,
     fill_output(&l.out, c, a);
     const int e = fgk_launch_merge_select(&l, c->stream);
     c->launches++;
-    if (e) return fg_cuda_fail(err, e, "merge kernel");
-    if (a->flags & FG_CUDA_SAMPLE_ASYNC) return FG_OK;
+    return e ? fg_cuda_fail(err, e, "merge kernel") : FG_OK;
+}
+
+fg_status fg_cuda_merge_select(fg_cuda_context *c, const fg_cuda_sample_args *a,
+                               const float *candidate_scores, const uint32_t *candidate_ids,
+                               uint32_t shards, uint32_t k_shard, const uint32_t *shard_first,
+                               const uint32_t *shard_width, fg_error *err) {
+    const fg_status status = fg_cuda_merge_select_layout(c, a, candidate_scores, candidate_ids, 1u, shards,
+                                                         k_shard, shard_first, shard_width, false, err);
+    if (status != FG_OK || (a->flags & FG_CUDA_SAMPLE_ASYNC)) return status;
     return collect_status(c, err);
 }
+
+fg_status fg_cuda_collect(fg_cuda_context *c, fg_error *err) { return collect_status(c, err); }
 
 /* Host-buffer form: stage in, sample, stage out. */
 fg_status fg_cuda_sample_batch_host(fg_cuda_context *c, const fg_cuda_sample_args *h, fg_error *err) {
@@ -947,12 +999,13 @@ fg_status fg_cuda_sample_batch_static(int device, void *cuda_stream, const fg_cu
     fg_status status = check_batch(&view, a, false, &traits, err);
     if (status != FG_OK) return status;
     if (traits.nucleus) {
-        fg_error_set(err, FG_ERR_UNAVAILABLE, "sampling without a top-k cut is not built yet");
+        fg_error_set(err, FG_ERR_UNAVAILABLE,
+                     "sampling without a top-k cut needs a scratch row per SM; it is offered by fg_cuda_sample_batch only");
         return FG_ERR_UNAVAILABLE;
     }
     void *scratch = NULL;
-    e = fgk_static_scratch_address(device, &scratch); /* first call per device: cudaGetSymbolAddress */
-    if (!e) e = fgk_stream_prepare();
+    /* first call per device: cudaGetSymbolAddress and the kernel's shared-memory opt-in */
+    e = fgk_static_scratch_address(device, &scratch);
     if (e) return fg_cuda_fail(err, e, "preparing the built-in scratch");
 
     stream_plan plan;
@@ -977,8 +1030,12 @@ fg_status fg_cuda_sample_batch_static(int device, void *cuda_stream, const fg_cu
                          a->rows, at_parts + part_bytes, (unsigned)FGK_STATIC_SCRATCH_BYTES);
             return FG_ERR_LIMIT;
         }
+        /* the planner treats a forced count as a starting point and may hand back a larger
+         * one (shared memory, 16-bit counts): only a strictly smaller plan is progress */
+        const uint32_t before = plan.splits;
         view.forced_splits = plan.splits - 1u;
-        if (!plan_stream(&view, a->rows, a->vocab, a->history_max, traits.penalties, traits.counts, &plan)) {
+        if (!plan_stream(&view, a->rows, a->vocab, a->history_max, traits.penalties, traits.counts, &plan) ||
+            plan.splits >= before) {
             fg_error_set(err, FG_ERR_LIMIT, "no split count fits both shared memory and the built-in scratch");
             return FG_ERR_LIMIT;
         }

@@ -14,6 +14,8 @@ struct fg_cuda_context {
     uint64_t launches;
     uint32_t forced_splits;
     uint32_t path;          /* FG_CUDA_PATH_* */
+    /* test seam of the ring kernel (fg_cuda_internal_ring_controls) */
+    uint32_t ring_deal, ring_wait_polls, ring_withhold_armed, ring_withhold_cta, ring_withhold_issue;
 
     /* device scratch, grown on demand and then reused (no allocation on a warm call) */
     void *parts;            /* candidate hand-off between the splits of a row */
@@ -53,6 +55,22 @@ fg_status fg_cuda_reserve_pinned(fg_cuda_context *context, size_t want, fg_error
 fg_status fg_cuda_default_context(fg_cuda_context **out, fg_error *err);
 void fg_cuda_default_lock(void);
 void fg_cuda_default_unlock(void);
+fg_status fg_cuda_internal_ring_controls(fg_cuda_context *context, uint32_t deal, uint32_t wait_polls,
+                                         uint32_t armed, uint32_t cta, uint32_t issue);
+/* The two steps of the vocabulary-sharded mode with an explicit candidate layout (stride 1:
+ * separate score and id arrays; 2: interleaved (value, id) pairs); both only enqueue.  The
+ * multi-GPU layer calls them with its exchange buffers. */
+fg_status fg_cuda_shard_topk_layout(fg_cuda_context *context, const fg_cuda_sample_args *args,
+                                    uint32_t vocab_offset, uint32_t vocab_total, uint32_t k_shard,
+                                    float *candidate_scores, uint32_t *candidate_ids, uint32_t stride,
+                                    fg_error *err);
+fg_status fg_cuda_merge_select_layout(fg_cuda_context *context, const fg_cuda_sample_args *args,
+                                      const float *candidate_scores, const uint32_t *candidate_ids,
+                                      uint32_t stride, uint32_t shards, uint32_t k_shard,
+                                      const uint32_t *shard_first, const uint32_t *shard_width,
+                                      bool keep_errors, fg_error *err);
+/* Waits for the context's stream and turns the device's error word into a status. */
+fg_status fg_cuda_collect(fg_cuda_context *context, fg_error *err);
 /* fg_sampler_config_validate with the optional "top_k == 0" extension. */
 bool fg_cuda_config_ok(const fg_sampler_config *config, bool allow_no_topk);
 

@@ -79,6 +79,9 @@ class CudaBackend:
                                          uniforms)
 
 
+FG_ERR_LIMIT = 8  # include/fg.h
+
+
 @dataclass
 class ShardedResult:
     tokens: torch.Tensor
@@ -86,13 +89,17 @@ class ShardedResult:
     row_status: torch.Tensor
     status: int
     shard_status: torch.Tensor
+    message: str = ""
 
 
 def sample_vocab_sharded(backend, logits_shard: torch.Tensor, configs, uniforms: torch.Tensor,
                          vocab_total: int, k_shard: int = 64, history_tokens=None,
                          history_offsets=None, history_max: int = 0, group=None) -> ShardedResult:
-    """Every rank calls this with its column span of the same rows; every rank gets
-    the same tokens.  The spans follow `shard_span` in rank order."""
+    """The sharded path with torch.distributed doing the exchange (any backend, so CPU ranks
+    over gloo can run it with a stand-in for the two compute steps).  Every rank calls this
+    with its column span of the same rows; every rank gets the same tokens.  The spans follow
+    `shard_span` in rank order.  GPU ranks normally use `Communicator` instead, which does
+    the same through the library's own NCCL communicator without any copy in between."""
     world = dist.get_world_size(group)
     rank = dist.get_rank(group)
     rows = logits_shard.shape[0]
@@ -104,7 +111,17 @@ def sample_vocab_sharded(backend, logits_shard: torch.Tensor, configs, uniforms:
     # one exchange: (fp32 logit, int32 global id) pairs, 8 bytes each, as one buffer
     mine = torch.stack([scores.view(torch.int32), ids.view(torch.int32)], dim=0).contiguous()
     everyone = torch.empty(world, 2, rows, k_shard, dtype=torch.int32, device=mine.device)
-    dist.all_gather_into_tensor(everyone.view(-1), mine.view(-1), group=group)
+    try:
+        dist.all_gather_into_tensor(everyone.view(-1), mine.view(-1), group=group)
+    except RuntimeError as error:
+        # a rank that never joined: the group's timeout ends the exchange, and the step fails
+        # closed with the status the reference gives a partial that misses its deadline
+        # (src/runtime.c:2379-2435)
+        failed = torch.full((rows,), FG_ERR_LIMIT, dtype=torch.int32)
+        result = ShardedResult(torch.full((rows,), -1, dtype=torch.int32), torch.zeros(rows), failed,
+                               FG_ERR_LIMIT, shard_status)
+        result.message = f"not every rank joined the exchange: {error}"
+        return result
     all_scores = everyone[:, 0].contiguous().view(torch.float32)  # [shard][row][k]
     all_ids = everyone[:, 1].contiguous()
     spans = [shard_span(vocab_total, world, s) for s in range(world)]
@@ -112,3 +129,105 @@ def sample_vocab_sharded(backend, logits_shard: torch.Tensor, configs, uniforms:
                                   [s[1] for s in spans], configs, uniforms)
     return ShardedResult(merged.tokens, merged.token_logits, merged.row_status, merged.status,
                          shard_status)
+
+
+class Communicator:
+    """fg_dist: this process's membership in the library's own NCCL communicator, bound to a
+    Context (its GPU and stream).  torch.distributed is used once, to carry the 128-byte
+    communicator id from rank 0 to the others."""
+
+    def __init__(self, context, group=None, timeout_ms: int = 0, ranks: int | None = None,
+                 rank: int | None = None, unique_id: bytes | None = None):
+        """Joins the ranks of `group` (default: torch.distributed's world).  A caller without
+        torch.distributed passes `ranks`, `rank` and the `unique_id` rank 0 made with
+        `Communicator.make_unique_id` (a single rank needs neither)."""
+        import ctypes
+        from . import FG_OK, FgError, FgStatusError
+        self.context = context
+        self.lib = context.lib
+        err = FgError()
+        if ranks is None:
+            self.ranks = dist.get_world_size(group)
+            self.rank = dist.get_rank(group)
+            mine = self.make_unique_id(context.lib) if self.rank == 0 else bytes(128)
+            carrier = torch.tensor(list(mine), dtype=torch.uint8)
+            if dist.get_backend(group) == "nccl":
+                carrier = carrier.to(torch.device("cuda", context.device))
+            dist.broadcast(carrier, src=dist.get_global_rank(group, 0) if group is not None else 0, group=group)
+            unique_id = bytes(carrier.cpu().tolist())
+        else:
+            self.ranks, self.rank = ranks, 0 if rank is None else rank
+            if unique_id is None:
+                if self.ranks != 1:
+                    raise ValueError("more than one rank needs rank 0's unique id")
+                unique_id = self.make_unique_id(context.lib)
+        id_bytes = (ctypes.c_ubyte * 128)(*unique_id)
+        handle = ctypes.c_void_p()
+        status = self.lib.fg_dist_create(context.handle, self.ranks, self.rank, id_bytes, timeout_ms,
+                                         ctypes.byref(handle), ctypes.byref(err))
+        if status != FG_OK:
+            raise FgStatusError(status, err.text())
+        self.handle = handle
+
+    @staticmethod
+    def make_unique_id(lib) -> bytes:
+        """fg_dist_unique_id: the 128 bytes rank 0 hands to every other rank."""
+        import ctypes
+        from . import FG_OK, FgError, FgStatusError
+        id_bytes = (ctypes.c_ubyte * 128)()
+        err = FgError()
+        status = lib.fg_dist_unique_id(id_bytes, ctypes.byref(err))
+        if status != FG_OK:
+            raise FgStatusError(status, err.text())
+        return bytes(id_bytes)
+
+    def close(self) -> None:
+        if getattr(self, "handle", None):
+            self.lib.fg_dist_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def sample_vocab_sharded(self, logits_shard: torch.Tensor, configs, uniforms: torch.Tensor,
+                             vocab_total: int, k_shard: int = 64, history_tokens=None, history_offsets=None,
+                             history_max: int = 0, out=None, asynchronous: bool = False):
+        """fg_dist_sample_vocab_sharded: shard top-k, one all-gather, merge and select."""
+        import ctypes
+        from . import FG_CUDA_SAMPLE_ASYNC, FgError
+        from .api import SampleResult
+        rows = logits_shard.shape[0]
+        device = logits_shard.device
+        if out is None:
+            out = (torch.empty(rows, dtype=torch.int32, device=device),
+                   torch.empty(rows, dtype=torch.float32, device=device),
+                   torch.empty(rows, dtype=torch.int32, device=device))
+        args, keep = self.context._args(logits_shard, configs, uniforms, history_tokens, history_offsets,
+                                        history_max, None, FG_CUDA_SAMPLE_ASYNC if asynchronous else 0, out, None)
+        err = FgError()
+        status = self.lib.fg_dist_sample_vocab_sharded(self.handle, ctypes.byref(args), vocab_total, k_shard,
+                                                       ctypes.byref(err))
+        del keep
+        return SampleResult(out[0], out[1], out[2], status, err.text(), None)
+
+    def gather_rows(self, tokens: torch.Tensor, token_logits: torch.Tensor, row_status: torch.Tensor):
+        """fg_dist_gather_rows: every rank's `rows` results on every rank, in rank order."""
+        import ctypes
+        from . import FG_OK, FgError, FgStatusError
+        rows = tokens.shape[0]
+        device = tokens.device
+        everyone = (torch.empty(self.ranks * rows, dtype=torch.int32, device=device),
+                    torch.empty(self.ranks * rows, dtype=torch.float32, device=device),
+                    torch.empty(self.ranks * rows, dtype=torch.int32, device=device))
+        err = FgError()
+        P = ctypes.c_void_p
+        status = self.lib.fg_dist_gather_rows(self.handle, P(tokens.data_ptr()), P(token_logits.data_ptr()),
+                                              P(row_status.data_ptr()), rows, P(everyone[0].data_ptr()),
+                                              P(everyone[1].data_ptr()), P(everyone[2].data_ptr()),
+                                              ctypes.byref(err))
+        if status != FG_OK:
+            raise FgStatusError(status, err.text())
+        return everyone

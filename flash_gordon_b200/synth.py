@@ -15,7 +15,7 @@ from dataclasses import dataclass, field
 
 import torch
 
-from . import SamplerConfig, uniform_stream
+from . import SamplerConfig
 
 VOCAB = 151_936
 DEFAULT_SEED = 0x9E3779B97F4A7C15
@@ -72,10 +72,26 @@ def _generator(device, seed: int) -> torch.Generator:
     return g
 
 
+def xorshift_uniforms(seed: int, count: int) -> list[float]:
+    """`count` draws of the sampler's xorshift64* stream (src/sampler.c:62-73 of the
+    reference: seed 0 becomes the default seed; x ^= x >> 12, x ^= x << 25, x ^= x >> 27;
+    the top 24 bits of x * 2685821657736338717 scaled by 2^-24).  Written out here so that
+    generating inputs never loads the native library; tests/test_cpu_abi.py holds it equal
+    to fg_sampler_uniform."""
+    mask = (1 << 64) - 1
+    x = (seed & mask) or DEFAULT_SEED
+    out = []
+    for _ in range(count):
+        x ^= x >> 12
+        x = (x ^ (x << 25)) & mask
+        x ^= x >> 27
+        out.append((((x * 2685821657736338717) & mask) >> 40) / 16777216.0)
+    return out
+
+
 def _uniforms(rows: int, seed: int, device) -> torch.Tensor:
-    # drawn on the host with the library's own xorshift64* stream, as the
-    # reference's coordinator does once per token
-    return torch.tensor(uniform_stream(seed, rows), dtype=torch.float32, device=device)
+    # one draw per row on the host, as the reference's coordinator does once per token
+    return torch.tensor(xorshift_uniforms(seed, rows), dtype=torch.float32, device=device)
 
 
 def _zipf_history(rows: int, length: int, vocab: int, exponent: float, g, device):

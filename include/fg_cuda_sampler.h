@@ -246,6 +246,65 @@ fg_status fg_cuda_merge_select(fg_cuda_context *context, const fg_cuda_sample_ar
                                const uint32_t *shard_first, const uint32_t *shard_width,
                                fg_error *err);
 
+/* ---------------------------------------------------------------- multi-GPU */
+
+/* One process per GPU; a fg_dist joins `ranks` of them through one NCCL communicator
+ * bound to the context's GPU and stream.  It stands in for the reference's fabric on the
+ * output path (include/fg_fabric.h; the split head's partials, src/runtime.c:2534-2561):
+ * TCP sockets there, NCCL over NVLink here.  libnccl.so.2 is opened on first use (the
+ * FG_NCCL_LIBRARY variable names another file); FG_ERR_UNAVAILABLE when it is missing.
+ *
+ * Row partition needs none of this on the data path: rows are independent, each
+ * rank samples its own block with fg_cuda_sample_batch.  fg_dist_gather_rows is for
+ * callers that want every rank's results on every rank.
+ *
+ * Every call that waits for other ranks has a deadline (`timeout_ms`, 0 = 30 s).  When
+ * it passes, the communicator is aborted -- which also ends a collective that still
+ * waits on the GPU -- the call returns FG_ERR_LIMIT, and later calls on this fg_dist
+ * return FG_ERR_UNAVAILABLE.  The reference turns a partial that misses its 4 s
+ * deadline into FG_ERR_LIMIT the same way (src/runtime.c:2379-2435). */
+typedef struct fg_dist fg_dist;
+#define FG_DIST_UNIQUE_ID_BYTES 128u
+#define FG_DIST_DEFAULT_TIMEOUT_MS 30000u
+
+/* Rank 0 fills `id` (FG_DIST_UNIQUE_ID_BYTES bytes, HOST) and carries it to the other
+ * ranks by whatever means the processes already share (the reference's ranks know
+ * each other from the manifest); every rank then passes the same bytes to
+ * fg_dist_create. */
+fg_status fg_dist_unique_id(void *id, fg_error *err);
+fg_status fg_dist_create(fg_cuda_context *context, uint32_t ranks, uint32_t rank, const void *id,
+                         uint32_t timeout_ms, fg_dist **out, fg_error *err);
+/* NULL is ignored.  Destroy before the context. */
+void fg_dist_destroy(fg_dist *dist);
+uint32_t fg_dist_ranks(const fg_dist *dist);
+uint32_t fg_dist_rank(const fg_dist *dist);
+
+/* Column span of `shard` when vocab_total columns are split over `shards` GPUs: equal
+ * widths, the last one takes the remainder -- the rule of the reference's 4-way split
+ * (src/protocol.c:93-105). */
+void fg_dist_shard_span(uint32_t vocab_total, uint32_t shards, uint32_t shard, uint32_t *first,
+                        uint32_t *width);
+
+/* Vocabulary-sharded sampling, all three steps, called by every rank with its own
+ * columns of the same rows (`args->logits`: rows x its span's width, `args->vocab` that
+ * width; history ids are global; configs, uniforms and outputs as in
+ * fg_cuda_sample_batch, identical on every rank):
+ *   1. fg_cuda_shard_topk on this rank's columns, written as (fp32 value, uint32 global
+ *      id) pairs straight into the send buffer;
+ *   2. one ncclAllGather of rows * k_shard * 8 bytes per rank;
+ *   3. fg_cuda_merge_select over the gathered [rank][row][k_shard] pairs, on every rank
+ *      (every rank ends with the same tokens).
+ * Nothing is copied between the steps.  sampled rows need top_k <= k_shard. */
+fg_status fg_dist_sample_vocab_sharded(fg_dist *dist, const fg_cuda_sample_args *args,
+                                       uint32_t vocab_total, uint32_t k_shard, fg_error *err);
+
+/* Row partition, optional: all ranks' results on every rank.  Every rank passes `rows`
+ * results (device arrays; the same count on every rank) and gets ranks * rows back in
+ * rank order.  Waits for completion. */
+fg_status fg_dist_gather_rows(fg_dist *dist, const uint32_t *tokens, const float *token_logits,
+                              const uint32_t *row_status, uint32_t rows, uint32_t *all_tokens,
+                              float *all_token_logits, uint32_t *all_row_status, fg_error *err);
+
 /* No counterpart in the reference.  fg_cuda_sample_batch for callers that must not
  * allocate GPU memory: a serving process whose own arena already owns the whole
  * device (so cudaMalloc fails, or may not be called by policy), or a decode loop

@@ -562,6 +562,20 @@ fg_status fgo_shard_topk(const void *logits, uint32_t dtype, uint32_t rows, uint
             } while (produced > k_shard);
             memcpy(dst, cur_scores, (size_t)k_shard * sizeof *dst);
             memcpy(dst_ids, cur_ids, (size_t)k_shard * sizeof *dst_ids);
+            if (config->temperature == 0.0f) {
+                /* A greedy slice reports its argmax-order winner (src/output.c:320-344),
+                 * and that order puts a NaN/Inf before every finite value, smallest id
+                 * first (src/output.c:484-492): it leads the slice's candidates so that the
+                 * fold of src/runtime.c:2458-2463 meets it and rejects the row. */
+                for (uint32_t i = 0; i < shard_vocab; i++) {
+                    if (isfinite(row[i])) continue;
+                    memmove(dst + 1, dst, (size_t)(k_shard - 1u) * sizeof *dst);
+                    memmove(dst_ids + 1, dst_ids, (size_t)(k_shard - 1u) * sizeof *dst_ids);
+                    dst[0] = row[i];
+                    dst_ids[0] = global_ids[i];
+                    break;
+                }
+            }
         } else {
             for (uint32_t i = 0; i < k_shard; i++) {
                 dst[i] = -INFINITY;

@@ -16,8 +16,15 @@ def logits_to_numpy(logits: torch.Tensor) -> np.ndarray:
     return logits.numpy()
 
 
-def run_oracle(workload, kind: str = "port", threads: int = 8, want_candidates: bool = False):
-    lib = oracle.load(kind)
+def oracle_kind() -> str:
+    """The checker the GPU parity tests use: the reference's own sampler objects where
+    that build is present (it travels with the repository), else this repository's
+    port of them (the CPU tests hold the two equal)."""
+    return "reference" if oracle.available("reference") else "port"
+
+
+def run_oracle(workload, kind: str | None = None, threads: int = 8, want_candidates: bool = False):
+    lib = oracle.load(kind or oracle_kind())
     tokens = offsets = None
     if workload.history_tokens is not None:
         tokens = workload.history_tokens.cpu().numpy().view(np.uint32)

@@ -104,6 +104,15 @@ def test_uniform_stream_matches_reference_bits(library):
     assert all(0.0 <= u < 1.0 for u in fg.uniform_stream(123, 1000))
 
 
+def test_input_generator_draws_the_same_stream(library):
+    """synth draws its uniforms without the native library; the bits must be the library's."""
+    from flash_gordon_b200 import synth
+    for seed in (0, 1, 123, 0x9E3779B97F4A7C15, 2**64 - 1):
+        mine = np.array(synth.xorshift_uniforms(seed, 64), dtype=np.float32).view(np.uint32)
+        theirs = np.array(fg.uniform_stream(seed, 64), dtype=np.float32).view(np.uint32)
+        assert np.array_equal(mine, theirs), seed
+
+
 def test_small_helpers(library):
     assert library.fg_align_up_u64(5, 4096) == 4096 and library.fg_align_up_u64(5, 0) == 5
     assert library.fg_is_aligned_u64(8192, 4096) and not library.fg_is_aligned_u64(1, 0)

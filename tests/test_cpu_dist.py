@@ -113,3 +113,54 @@ def test_two_cpu_ranks_sharded_and_partitioned():
         problems.append(failures.get())
     assert not problems, problems
     assert all(worker.exitcode == 0 for worker in workers)
+
+
+def _no_show_worker(rank, world, port, outcomes):
+    import datetime
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=4))
+    try:
+        from flash_gordon_b200 import SamplerConfig
+        from helpers import random_workload
+        w = random_workload(3, 2000, 0, [SamplerConfig.make(0.8, 0.9, 20)], 3)
+        first, width = shard_span(w.vocab, world, rank)
+        if rank == 1:
+            import time
+            time.sleep(8)  # the rank that never calls the exchange
+            outcomes.put((rank, "absent"))
+            return
+        out = sample_vocab_sharded(OracleBackend(), w.logits[:, first:first + width].contiguous(), w.configs,
+                                   w.uniforms, w.vocab, 64)
+        outcomes.put((rank, out.status, out.row_status.tolist(), out.message))
+    except Exception as error:
+        outcomes.put((rank, f"raised {error!r}"))
+    finally:
+        try:
+            dist.destroy_process_group()
+        except Exception:
+            pass
+
+
+def test_a_rank_that_never_joins_ends_the_step_with_the_limit_status():
+    """Host-side fault: rank 1 never calls the exchange.  Rank 0 must come back within the
+    group's timeout with FG_ERR_LIMIT on every row (the reference: a partial that misses its
+    deadline, src/runtime.c:2379-2435) instead of waiting forever.  No GPU is involved."""
+    with socket.socket() as probe:
+        probe.bind(("127.0.0.1", 0))
+        port = probe.getsockname()[1]
+    context = mp.get_context("spawn")
+    outcomes = context.Queue()
+    workers = [context.Process(target=_no_show_worker, args=(rank, 2, port, outcomes)) for rank in range(2)]
+    for worker in workers:
+        worker.start()
+    for worker in workers:
+        worker.join(timeout=120)
+        assert not worker.is_alive(), "a rank hung"
+    seen = {}
+    while not outcomes.empty():
+        item = outcomes.get()
+        seen[item[0]] = item[1:]
+    assert seen[1] == ("absent",)
+    status, row_status, message = seen[0]
+    assert status == 8 and set(row_status) == {8} and "joined" in message  # FG_ERR_LIMIT

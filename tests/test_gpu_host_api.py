@@ -113,3 +113,16 @@ def test_apply_penalties_matches_oracle(context, library, port):
         # returns the canonical quiet NaN); everything else must agree bit for bit
         both_nan = np.isnan(got) & np.isnan(want)
         assert np.array_equal(got.view(np.uint32)[~both_nan], want.view(np.uint32)[~both_nan])
+
+
+def test_the_reference_s_own_sampler_test_passes_against_this_library():
+    """tests/test_sampler.c of the reference, compiled unchanged against include/ and linked
+    with libfgsampler (`make -C oracle drop-in REFERENCE=...`, done where the reference tree is
+    mounted; the binary travels with the repository).  All its checks must pass."""
+    import subprocess
+    from pathlib import Path
+    binary = Path(__file__).resolve().parent.parent / "oracle" / "_ref" / "test_sampler_dropin"
+    if not binary.exists():
+        pytest.skip("oracle/_ref/test_sampler_dropin is built only where the reference tree is mounted")
+    done = subprocess.run([str(binary)], capture_output=True, text=True, timeout=300)
+    assert done.returncode == 0, done.stdout + done.stderr

@@ -9,7 +9,8 @@ import torch
 
 from flash_gordon_b200 import (FG_ERR_ARGUMENT, FG_ERR_FORMAT, FG_ERR_LIMIT, FG_OK, Context,
                                SamplerConfig, synth)
-from helpers import as_u32, assert_candidates_close, assert_rows_equal, run_gpu, run_oracle
+from helpers import (as_u32, assert_candidates_close, assert_rows_equal, oracle_kind, random_workload,
+                     run_gpu, run_oracle)
 
 pytestmark = pytest.mark.gpu
 
@@ -134,7 +135,7 @@ def test_shard_candidates_through_the_ring(context):
     histories = [torch.randint(0, total, (3000,), generator=g).tolist() for _ in range(rows)]
     tokens, offsets, longest = csr(histories)
     cfg = SamplerConfig.make(0.8, 0.9, 64, presence=0.4, frequency=0.2, repetition=1.05)
-    lib = oracle.load("port")
+    lib = oracle.load(oracle_kind())
     _, want_scores, want_ids, want_status = oracle.shard_topk(
         lib, logits.view(torch.int16).numpy().view(np.uint16), [cfg], first, total, k,
         tokens.numpy().view(np.uint32), offsets.numpy().view(np.uint64))
@@ -146,6 +147,49 @@ def test_shard_candidates_through_the_ring(context):
     assert np.array_equal(as_u32(ids), want_ids.reshape(rows, k))
     assert np.array_equal(scores.cpu().numpy().view(np.uint32),
                           want_scores.reshape(rows, k).view(np.uint32))
+
+
+@pytest.mark.parametrize("deal", [1, 2])
+def test_both_ways_of_dealing_out_rows(context, deal):
+    """Whole rows round-robin and equal runs of tiles (rows shared between CTAs, parts merged
+    by the last to finish) give the same bits, for more rows than CTAs and for fewer."""
+    for rows, vocab, history in ((700, 9_000, 300), (40, 151_936, 2_000), (3, 151_936, 64)):
+        cfgs = [SamplerConfig.make(0.0 if r % 6 == 0 else 0.9, 0.9, 1 + (r * 5) % 64, presence=0.2 * (r % 2),
+                                   frequency=0.1 * (r % 4), repetition=1.0 + 0.03 * (r % 3))
+                for r in range(rows)]
+        w = random_workload(rows, vocab, history, cfgs, 1000 + rows, quantize=0.125, specials=1)
+        expected = run_oracle(w)
+        context.ring_controls(deal=deal)
+        try:
+            result = run_gpu(context, w)
+        finally:
+            context.ring_controls()
+        assert_rows_equal(result, expected, f"deal {deal}, {rows} rows")
+
+
+def test_a_wait_that_runs_out_fails_rows_not_the_gpu(context):
+    """One tile of CTA 0 is never asked for, and the waits give up after a few thousand polls:
+    the kernel comes back, the rows of that CTA end with FG_ERR_LIMIT, the others are sampled,
+    and the next call on the same context works."""
+    rows, vocab = 600, 20_000
+    cfg = SamplerConfig.make(0.8, 0.9, 30, presence=0.2, frequency=0.1)
+    w = random_workload(rows, vocab, 200, [cfg], 77)
+    expected = run_oracle(w)
+    context.ring_controls(deal=1, wait_polls=3000, withhold=(0, 5))
+    try:
+        result = run_gpu(context, w)
+    finally:
+        context.ring_controls()
+    status = as_u32(result.row_status)
+    assert result.status == FG_ERR_LIMIT and "wait" in result.message
+    failed = np.nonzero(status == FG_ERR_LIMIT)[0]
+    assert failed.size > 0 and set(np.unique(status)) == {FG_OK, FG_ERR_LIMIT}
+    sms = context.sm_count
+    assert all(r % sms == 0 for r in failed), "only CTA 0's rows (0, SMs, 2 SMs, ...) may fail"
+    ok = status == FG_OK
+    assert np.array_equal(as_u32(result.tokens)[ok], expected[1][ok])
+    again = run_gpu(context, w)
+    assert_rows_equal(again, expected, "after the timeout")
 
 
 def test_ring_refuses_what_it_cannot_take(context):

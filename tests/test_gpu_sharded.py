@@ -9,7 +9,8 @@ import torch
 import oracle
 from flash_gordon_b200 import FG_ERR_ARGUMENT, FG_ERR_MISMATCH, FG_OK, SamplerConfig, synth
 from flash_gordon_b200.dist import shard_span
-from helpers import as_u32, assert_candidates_close, assert_rows_equal, logits_to_numpy, random_workload, run_oracle
+from helpers import (as_u32, assert_candidates_close, assert_rows_equal, logits_to_numpy, oracle_kind,
+                     random_workload, run_oracle)
 
 pytestmark = pytest.mark.gpu
 
@@ -42,7 +43,7 @@ def run_sharded(context, w, shards, k_shard, debug=False):
 
 
 def oracle_sharded(w, shards, k_shard):
-    lib = oracle.load("port")
+    lib = oracle.load(oracle_kind())
     logits = logits_to_numpy(w.logits)
     tokens = offsets = None
     if w.history_tokens is not None:
@@ -91,6 +92,23 @@ def test_sharded_greedy_fold(context):
     merged, _, _ = oracle_sharded(w, 4, 8)
     assert_rows_equal(result, merged, "greedy sharded")
     assert_rows_equal(result, run_oracle(w), "greedy sharded vs unsharded")
+
+
+def test_sharded_greedy_rows_with_nan_or_inf_fail_like_unsharded_ones(context):
+    """A NaN/Inf anywhere in a greedy row wins the argmax order and is then rejected
+    (src/runtime.c:2458-2463 for the split head, src/output.c:593 unsharded): the shard that
+    holds it must hand it on, whichever kernel samples the shard."""
+    cfg = SamplerConfig.make(temperature=0.0, top_p=1.0, top_k=1)
+    w = random_workload(9, 8192, 0, [cfg], 29, quantize=1.0, specials=3)
+    w.logits[4] = torch.round(torch.randn(8192) * 3.0)  # one clean row among them
+    unsharded = run_oracle(w)
+    assert (unsharded[3] == FG_ERR_MISMATCH).sum() >= 4 and unsharded[3][4] == FG_OK
+    result, _, _, _ = run_sharded(context, w, 4, 8)  # (the fixture runs both kernels)
+    merged, _, _ = oracle_sharded(w, 4, 8)
+    assert_rows_equal(result, merged, "greedy sharded with specials")
+    assert np.array_equal(as_u32(result.row_status), unsharded[3]), "sharded status != unsharded status"
+    bad = unsharded[3] != FG_OK
+    assert np.array_equal(as_u32(result.tokens)[bad], unsharded[1][bad]), "the rejected finalist's id"
 
 
 def test_span_check_and_argument_errors(context):
