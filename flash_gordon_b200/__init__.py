@@ -145,6 +145,8 @@ def load_library() -> ctypes.CDLL:
         "fg_cuda_apply_penalties": (c_int, [P, P, P, u32, c_float, c_float, c_float, E]),
         "fg_cuda_argmax_reduce": (c_int, [P, P, P, P, P, u32, POINTER(u32), E]),
         "fg_cuda_topk_select": (c_int, [P, P, P, P, P, u32, u32, POINTER(u32), E]),
+        "fg_cuda_topk_reduce": (c_int, [P, P, P, P, P, u32, POINTER(u32), E]),
+        "fg_cuda_router_topk": (c_int, [P, P, P, P, u32, u32, u32, E]),
         "fg_cuda_history_reset": (c_int, [P, P, u32, P, u32, E]),
         "fg_cuda_history_increment": (c_int, [P, P, u32, u32, E]),
         "fg_cuda_sample_batch": (c_int, [P, POINTER(SampleArgs), E]),
@@ -160,6 +162,16 @@ def load_library() -> ctypes.CDLL:
         "fg_dist_shard_span": (None, [u32, u32, u32, POINTER(u32), POINTER(u32)]),
         "fg_dist_sample_vocab_sharded": (c_int, [P, POINTER(SampleArgs), u32, u32, E]),
         "fg_dist_gather_rows": (c_int, [P, P, P, P, u32, P, P, P, E]),
+        "fg_cuda_output_executor_create": (c_int, [P, u32, u32, u32, POINTER(P), E]),
+        "fg_cuda_output_executor_destroy": (None, [P]),
+        "fg_cuda_output_set_session": (None, [P, u32]),
+        "fg_cuda_output_session": (u32, [P]),
+        "fg_cuda_output_history_length": (u32, [P, u32]),
+        "fg_cuda_output_history_reset": (c_int, [P, P, u32, E]),
+        "fg_cuda_output_history_increment": (c_int, [P, u32, E]),
+        "fg_cuda_output_greedy": (c_int, [P, P, POINTER(u32), POINTER(c_float), E]),
+        "fg_cuda_output_sample": (c_int, [P, P, CFG, c_float, POINTER(u32), POINTER(c_float), E]),
+        "fg_cuda_output_sample_sessions": (c_int, [P, POINTER(SampleArgs), P, E]),
         # test seam of the ring kernel (csrc/host/fg_host_internal.h; not in the public headers)
         "fg_cuda_internal_ring_controls": (c_int, [P, u32, u32, u32, u32, u32]),
     }

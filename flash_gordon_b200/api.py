@@ -209,6 +209,22 @@ class Context:
             in_ids.handle if in_ids is not None else None, count, k, byref(produced), byref(err))
         return status, produced.value
 
+    def topk_reduce(self, out_scores: Tensor, out_ids: Tensor, in_scores: Tensor, in_ids: Tensor | None,
+                    count: int) -> tuple[int, int]:
+        produced = c_uint32(0)
+        err = FgError()
+        status = self.lib.fg_cuda_topk_reduce(
+            self.handle, out_scores.handle, out_ids.handle, in_scores.handle,
+            in_ids.handle if in_ids is not None else None, count, byref(produced), byref(err))
+        return status, produced.value
+
+    def router_topk(self, selected: Tensor, gates: Tensor, logits: Tensor, experts: int, tokens: int,
+                    k: int) -> tuple[int, str]:
+        err = FgError()
+        status = self.lib.fg_cuda_router_topk(self.handle, selected.handle, gates.handle, logits.handle,
+                                              experts, tokens, k, byref(err))
+        return status, err.text()
+
     def history_reset(self, counts: Tensor, vocab: int, history) -> int:
         array = (c_uint32 * max(len(history), 1))(*history)
         err = FgError()
@@ -399,3 +415,77 @@ def select(config: SamplerConfig, scores, ids, uniform: float):
     status = lib.fg_sampler_select(byref(config), score_array, id_array, n, uniform, byref(token),
                                    byref(logit), byref(err))
     return status, token.value, logit.value, err.text()
+
+
+class OutputExecutor:
+    """fg_cuda_output_executor: session slots whose token histories stay on the GPU between
+    decode steps (the reference's fg_output executor, include/fg_output.h:42-66)."""
+
+    def __init__(self, context: Context, vocab: int, session_slots: int, history_capacity: int):
+        self.context = context
+        self.lib = context.lib
+        self.vocab = vocab
+        handle = c_void_p()
+        err = FgError()
+        status = self.lib.fg_cuda_output_executor_create(context.handle, vocab, session_slots,
+                                                         history_capacity, byref(handle), byref(err))
+        if status != FG_OK:
+            raise FgStatusError(status, err.text())
+        self.handle = handle
+
+    def close(self) -> None:
+        if getattr(self, "handle", None) and getattr(self.context, "handle", None):
+            self.lib.fg_cuda_output_executor_destroy(self.handle)
+        self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def set_session(self, slot: int) -> None:
+        self.lib.fg_cuda_output_set_session(self.handle, slot)
+
+    @property
+    def session(self) -> int:
+        return self.lib.fg_cuda_output_session(self.handle)
+
+    def history_length(self, slot: int) -> int:
+        return self.lib.fg_cuda_output_history_length(self.handle, slot)
+
+    def history_reset(self, history) -> int:
+        array = (c_uint32 * max(len(history), 1))(*history)
+        err = FgError()
+        return self.lib.fg_cuda_output_history_reset(self.handle, array, len(history), byref(err))
+
+    def history_increment(self, token: int) -> int:
+        return self.lib.fg_cuda_output_history_increment(self.handle, token, byref(FgError()))
+
+    def sample(self, logits: Tensor, config: SamplerConfig, uniform: float):
+        """fg_cuda_output_sample: (status, token, logit, message) for the current session."""
+        token, logit, err = c_uint32(0), c_float(0.0), FgError()
+        status = self.lib.fg_cuda_output_sample(self.handle, logits.handle, byref(config), uniform,
+                                                byref(token), byref(logit), byref(err))
+        return status, token.value, logit.value, err.text()
+
+    def greedy(self, logits: Tensor):
+        token, logit, err = c_uint32(0), c_float(0.0), FgError()
+        status = self.lib.fg_cuda_output_greedy(self.handle, logits.handle, byref(token), byref(logit), byref(err))
+        return status, token.value, logit.value, err.text()
+
+    def sample_sessions(self, logits: torch.Tensor, configs, uniforms: torch.Tensor | None, slots,
+                        allow_no_topk: bool = False) -> SampleResult:
+        """fg_cuda_output_sample_sessions: one decode step, row r in session slots[r]."""
+        rows = logits.shape[0]
+        device = logits.device
+        out = (torch.empty(rows, dtype=torch.int32, device=device),
+               torch.empty(rows, dtype=torch.float32, device=device),
+               torch.empty(rows, dtype=torch.int32, device=device))
+        flags = FG_CUDA_SAMPLE_ALLOW_NO_TOPK if allow_no_topk else 0
+        args, keep = self.context._args(logits, configs, uniforms, None, None, 0, None, flags, out, None)
+        slot_array = (c_uint32 * rows)(*slots)
+        err = FgError()
+        status = self.lib.fg_cuda_output_sample_sessions(self.handle, byref(args), slot_array, byref(err))
+        del keep
+        return SampleResult(out[0], out[1], out[2], status, err.text(), None)

@@ -27,7 +27,8 @@ CC = os.environ.get("CC", "gcc")
 
 CUDA_SOURCES = ["fg_stream_kernels.cu", "fg_persistent_kernel.cu", "fg_nucleus_kernel.cu", "fg_ops_kernels.cu",
                 "fg_runtime.cu", "fg_nccl.cu"]
-HOST_SOURCES = ["fg_util.c", "fg_sampler_host.c", "fg_cuda_api.c", "fg_dist.c", "fg_output_wire.c"]
+HOST_SOURCES = ["fg_util.c", "fg_sampler_host.c", "fg_cuda_api.c", "fg_dist.c", "fg_output_wire.c",
+                "fg_request.c", "fg_output_exec.c"]
 
 # sm_100a only; -fmad=false so no fp32/fp64 multiply-add is contracted anywhere
 # in the sampling arithmetic (parity with the reference's C code is bit for bit).

@@ -79,6 +79,13 @@ typedef struct fgk_stream_launch {
     uint32_t *history_global;
     uint64_t history_stride_words;
     void *history_meta; /* 8 bytes per (row, split); NULL when the batch has no history */
+    /* persistent kernel only: session tables in place of token lists (the stateful executor):
+     * counts [slots][vocab] and seen-bitmaps [slots][slot_bitmap_words], row r uses session
+     * row_slots[r]; all three NULL otherwise */
+    const uint32_t *slot_counts;
+    const uint32_t *slot_bitmaps;
+    const uint32_t *row_slots;
+    uint32_t slot_bitmap_words;
     /* persistent kernel only: polls before a device-side wait gives up (0 = the default, about
      * two seconds), and the test seam that makes one wait run out: warp 0 of CTA withhold_cta
      * never asks the copy engine for its withhold_issue-th tile */
@@ -183,6 +190,23 @@ int fgk_launch_argmax_reduce(float *out_scores, uint32_t *out_ids, const float *
                              const uint32_t *ids, uint32_t count, void *stream);
 int fgk_launch_topk_select(float *out_scores, uint32_t *out_ids, const float *scores,
                            const uint32_t *ids, uint32_t count, uint32_t k, void *stream);
+/* the best 512 of every 4096-element tile, sorted; writes the first `produced` outputs */
+int fgk_launch_topk_reduce(float *out_scores, uint32_t *out_ids, const float *scores, const uint32_t *ids,
+                           uint32_t count, uint32_t produced, void *stream);
+/* per token the k best of `experts` logits and their gate weights; *bad (device word, armed
+ * with 0xffffffff) gets the lowest token whose logits hold a NaN or +Inf */
+int fgk_launch_router_topk(uint32_t *out_ids, float *out_weights, const float *logits, uint32_t tokens,
+                           uint32_t experts, uint32_t k, uint32_t *bad, void *stream);
+/* The executor's tables after a step: for every row that ended FG_OK and whose penalties are
+ * active, the sampled token's count goes up by one (saturating) and its seen-bit is set in
+ * the row's session (src/output.c:619-628, 742, 752).  `active` holds one byte per row. */
+int fgk_launch_session_increment(uint32_t *slot_counts, uint32_t *slot_bitmaps, uint32_t vocab,
+                                 uint32_t slot_bitmap_words, const uint32_t *row_slots,
+                                 const uint32_t *tokens, const uint32_t *row_status,
+                                 const unsigned char *active, uint32_t rows, void *stream);
+/* one session's bitmap rebuilt from its count table */
+int fgk_launch_session_bitmap(uint32_t *bitmap, const uint32_t *counts, uint32_t vocab,
+                              uint32_t bitmap_words, void *stream);
 /* counts += occurrences of history[0..count); *bad (device word) set when an id >= vocab */
 int fgk_launch_history_add(uint32_t *counts, uint32_t vocab, const uint32_t *history,
                            uint32_t count, uint32_t *bad, void *stream);

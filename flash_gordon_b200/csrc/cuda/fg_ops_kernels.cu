@@ -156,6 +156,163 @@ history_add_kernel(uint32_t *counts, uint32_t vocab, const uint32_t *history, ui
     }
 }
 
+// ---- sorted top-512 of every 4096-element tile ----
+// shaders/fg_topk_reduce_v2.comp:10, 27-85: the best 512 (score, id) pairs of the tile in the
+// order `before`: a padding id (0xffffffff) last; a NaN/Inf before every finite score, smaller
+// id first among them; then larger score, then smaller id.  The shader sorts 64-slot runs
+// and merges them pairwise; here the tile's 4096 64-bit keys are sorted by one bitonic
+// network in shared memory -- the key is the order: class and score in the high word, the
+// inverted id in the low word -- and each key drags along its position in the tile, from
+// which the untouched score bits (NaN payloads, the sign of zero) are fetched at the end.
+constexpr int kReduceTile = 4096, kReduceKeep = 512, kReduceThreads = 1024;
+
+__device__ __forceinline__ uint64_t reduce_key(float score, uint32_t id) {
+    if (id == kPaddingId) return 0ull;
+    const uint32_t high = is_nonfinite(score) ? 0xffffffffu : float_key(score);  // finite keys stop at 0xff7fffff
+    return ((uint64_t)high << 32) | (uint64_t)(~id);
+}
+
+__global__ void __launch_bounds__(kReduceThreads)
+topk_reduce_kernel(float *out_scores, uint32_t *out_ids, const float *scores, const uint32_t *ids,
+                   uint32_t count, uint32_t produced) {
+    __shared__ uint64_t key[kReduceTile];
+    __shared__ uint16_t from[kReduceTile];
+    const uint32_t tid = threadIdx.x, base = blockIdx.x * kReduceTile;
+    const uint32_t here = min((uint32_t)kReduceTile, count - base);
+    for (uint32_t i = tid; i < (uint32_t)kReduceTile; i += kReduceThreads) {
+        key[i] = i < here ? reduce_key(scores[base + i], ids ? ids[base + i] : base + i) : 0ull;
+        from[i] = (uint16_t)i;
+    }
+    __syncthreads();
+    for (uint32_t size = 2; size <= (uint32_t)kReduceTile; size <<= 1) {
+        for (uint32_t stride = size >> 1; stride > 0; stride >>= 1) {
+            for (uint32_t pair = tid; pair < (uint32_t)kReduceTile / 2; pair += kReduceThreads) {
+                // the pair's lower index: `pair` with a zero bit slipped in at `stride`
+                const uint32_t low = ((pair & ~(stride - 1)) << 1) | (pair & (stride - 1));
+                const uint32_t high = low | stride;
+                const bool descending = (low & size) == 0;
+                const uint64_t a = key[low], b = key[high];
+                if ((a < b) == descending) {
+                    key[low] = b;
+                    key[high] = a;
+                    const uint16_t moved = from[low];
+                    from[low] = from[high];
+                    from[high] = moved;
+                }
+            }
+            __syncthreads();
+        }
+    }
+    const uint32_t valid = min((uint32_t)kReduceKeep, here);
+    for (uint32_t i = tid; i < (uint32_t)kReduceKeep; i += kReduceThreads) {
+        const uint32_t at = blockIdx.x * kReduceKeep + i;
+        if (at >= produced) continue;  // (a lone short tile hands back `count` entries, src/vk.c:2235)
+        const uint32_t source = base + from[i];
+        out_scores[at] = i < valid ? scores[source] : __uint_as_float(0xff800000u);
+        out_ids[at] = i < valid ? (ids ? ids[source] : source) : kPaddingId;
+    }
+}
+
+// ---- router: the k best of each token's expert logits and their gate weights ----
+// src/q38_math.c:48-64 (fg_q38_router_topk): softmax over all experts in fp64, the k largest
+// logits (ties: smaller id), their probabilities rounded to fp32 and renormalised by their
+// fp64 sum.  A NaN or +Inf logit makes the token's probabilities meaningless: the ids come
+// back as 0xffffffff and the weights as 0 (shaders/fg_router_top10.glsl:38-51), and the call
+// reports it.  One warp per token.
+__global__ void __launch_bounds__(128)
+router_topk_kernel(uint32_t *out_ids, float *out_weights, const float *logits, uint32_t tokens,
+                   uint32_t experts, uint32_t k, uint32_t *bad) {
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t token = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (token >= tokens) return;
+    const float *row = logits + (size_t)token * experts;
+    float top = __uint_as_float(0xff800000u);
+    bool broken = false;
+    for (uint32_t i = lane; i < experts; i += 32) {
+        const float v = row[i];
+        broken = broken || v != v || v == __uint_as_float(0x7f800000u);
+        top = fmaxf(top, v);
+    }
+    broken = __any_sync(kFullMask, broken);
+#pragma unroll
+    for (int d = 16; d >= 1; d >>= 1) top = fmaxf(top, __shfl_xor_sync(kFullMask, top, d));
+    double total = 0.0;
+    for (uint32_t i = lane; i < experts; i += 32) total += exp((double)row[i] - (double)top);
+#pragma unroll
+    for (int d = 16; d >= 1; d >>= 1) total += __shfl_xor_sync(kFullMask, total, d);
+    if (broken || !(total > 0.0)) {
+        for (uint32_t slot = lane; slot < k; slot += 32) {
+            out_ids[(size_t)token * k + slot] = kPaddingId;
+            out_weights[(size_t)token * k + slot] = 0.0f;
+        }
+        if (lane == 0) atomicMin(bad, token);
+        return;
+    }
+    // k rounds of "the best that is not taken yet"; a lane remembers what it gave away
+    uint64_t floor_key = ~0ull;  // keys at or above this have been taken
+    double picked_sum = 0.0;
+    float my_weight = 0.0f;
+    uint32_t my_id = kPaddingId;
+    for (uint32_t slot = 0; slot < k; slot++) {
+        uint64_t best = 0;
+        for (uint32_t i = lane; i < experts; i += 32) {
+            const uint64_t candidate = ((uint64_t)float_key(row[i]) << 32) | (uint64_t)(~i);
+            if (candidate < floor_key && candidate > best) best = candidate;
+        }
+#pragma unroll
+        for (int d = 16; d >= 1; d >>= 1) {
+            const uint64_t other = __shfl_xor_sync(kFullMask, best, d);
+            best = other > best ? other : best;
+        }
+        floor_key = best;
+        const uint32_t id = ~(uint32_t)best;
+        const float weight = (float)(exp((double)row[id] - (double)top) / total);
+        picked_sum += (double)weight;
+        if (lane == slot % 32u) {  // (k <= 32: one slot per lane)
+            my_id = id;
+            my_weight = weight;
+        }
+    }
+    if (lane < k) {
+        out_ids[(size_t)token * k + lane] = my_id;
+        out_weights[(size_t)token * k + lane] = (float)((double)my_weight / picked_sum);
+    }
+}
+
+// ---- the executor's session tables ----
+// After a step: src/output.c:742, 752 -- a token picked with penalties active joins its
+// session's history; the count saturates as in src/output.c:619-628.
+__global__ void __launch_bounds__(kOpThreads)
+session_increment_kernel(uint32_t *slot_counts, uint32_t *slot_bitmaps, uint32_t vocab,
+                         uint32_t slot_bitmap_words, const uint32_t *row_slots, const uint32_t *tokens,
+                         const uint32_t *row_status, const unsigned char *active, uint32_t rows) {
+    const uint32_t row = blockIdx.x * blockDim.x + threadIdx.x;
+    if (row >= rows || !active[row] || row_status[row] != 0u) return;
+    const uint32_t token = tokens[row];
+    if (token >= vocab) return;
+    uint32_t *counts = slot_counts + (size_t)row_slots[row] * vocab;
+    uint32_t seen = counts[token];
+    while (seen != 0xffffffffu) {  // two rows of a batch may share a session
+        const uint32_t was = atomicCAS(&counts[token], seen, seen + 1u);
+        if (was == seen) break;
+        seen = was;
+    }
+    atomicOr(&slot_bitmaps[(size_t)row_slots[row] * slot_bitmap_words + (token >> 5)], 1u << (token & 31u));
+}
+
+__global__ void __launch_bounds__(kOpThreads)
+session_bitmap_kernel(uint32_t *bitmap, const uint32_t *counts, uint32_t vocab, uint32_t bitmap_words) {
+    const uint32_t stride = gridDim.x * blockDim.x;
+    for (uint32_t word = blockIdx.x * blockDim.x + threadIdx.x; word < bitmap_words; word += stride) {
+        uint32_t bits = 0;
+        for (uint32_t b = 0; b < 32u; b++) {
+            const uint32_t token = word * 32u + b;
+            if (token < vocab && counts[token] != 0u) bits |= 1u << b;
+        }
+        bitmap[word] = bits;
+    }
+}
+
 }  // namespace fgk
 
 using namespace fgk;
@@ -205,5 +362,40 @@ extern "C" int fgk_launch_history_add(uint32_t *counts, uint32_t vocab, const ui
     if (count == 0) return 0;
     history_add_kernel<<<blocks_for(kOpThreads, count), kOpThreads, 0,
                          static_cast<cudaStream_t>(stream)>>>(counts, vocab, history, count, bad);
+    return (int)cudaGetLastError();
+}
+
+extern "C" int fgk_launch_session_increment(uint32_t *slot_counts, uint32_t *slot_bitmaps, uint32_t vocab,
+                                            uint32_t slot_bitmap_words, const uint32_t *row_slots,
+                                            const uint32_t *tokens, const uint32_t *row_status,
+                                            const unsigned char *active, uint32_t rows, void *stream) {
+    if (rows == 0) return 0;
+    session_increment_kernel<<<(rows + kOpThreads - 1) / kOpThreads, kOpThreads, 0,
+                               static_cast<cudaStream_t>(stream)>>>(slot_counts, slot_bitmaps, vocab,
+                                                                    slot_bitmap_words, row_slots, tokens,
+                                                                    row_status, active, rows);
+    return (int)cudaGetLastError();
+}
+
+extern "C" int fgk_launch_session_bitmap(uint32_t *bitmap, const uint32_t *counts, uint32_t vocab,
+                                         uint32_t bitmap_words, void *stream) {
+    session_bitmap_kernel<<<blocks_for(kOpThreads, bitmap_words), kOpThreads, 0,
+                            static_cast<cudaStream_t>(stream)>>>(bitmap, counts, vocab, bitmap_words);
+    return (int)cudaGetLastError();
+}
+
+extern "C" int fgk_launch_topk_reduce(float *out_scores, uint32_t *out_ids, const float *scores,
+                                      const uint32_t *ids, uint32_t count, uint32_t produced, void *stream) {
+    const uint32_t groups = (count + kReduceTile - 1) / kReduceTile;
+    topk_reduce_kernel<<<groups, kReduceThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+        out_scores, out_ids, scores, ids, count, produced);
+    return (int)cudaGetLastError();
+}
+
+extern "C" int fgk_launch_router_topk(uint32_t *out_ids, float *out_weights, const float *logits,
+                                      uint32_t tokens, uint32_t experts, uint32_t k, uint32_t *bad,
+                                      void *stream) {
+    router_topk_kernel<<<(tokens + 3) / 4, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+        out_ids, out_weights, logits, tokens, experts, k, bad);
     return (int)cudaGetLastError();
 }

@@ -52,7 +52,10 @@ constexpr int kWarps = FGK_RING_WARPS;          // consumer warps
 constexpr int kHistoryWarps = 2;
 constexpr int kClosers = 2;
 constexpr int kStages = FGK_RING_STAGES;        // tiles in flight per consumer warp
-constexpr uint32_t kTileLogits = 2048;          // logits per tile: 64 per lane, one bit each in a 64-bit mask
+#ifndef FGK_RING_TILE_LOGITS
+#define FGK_RING_TILE_LOGITS 2048
+#endif
+constexpr uint32_t kTileLogits = FGK_RING_TILE_LOGITS;  // logits per tile: at most 64 per lane, a bit each in a mask
 constexpr uint32_t kStageBytes = kTileLogits * 4;  // a stage holds a tile of the widest type
 constexpr int kListCap = 256;                   // entries of one warp's candidate list
 constexpr int kListWords = kListCap / 32;
@@ -132,6 +135,12 @@ struct Params {
     uint32_t *part_ids;
     PartRecord *part_meta;          // [rows][max_parts]
     uint32_t *tickets;              // [rows], zero between launches
+    // Session tables instead of token lists (the stateful executor): row r uses the counts and
+    // the seen-bitmap of session row_slots[r], both indexed by token id; vocab_offset is 0.
+    const uint32_t *slot_counts;    // [slots][vocab]
+    const uint32_t *slot_bitmaps;   // [slots][slot_bitmap_words], a whole number of uint4 each
+    const uint32_t *row_slots;      // [rows]
+    uint32_t slot_bitmap_words;
     uint32_t wait_polls;            // polls before a wait gives up
     uint32_t withhold_cta, withhold_issue;  // test seam: that CTA's warp 0 never asks for that tile
     SelectOutput out;
@@ -216,6 +225,8 @@ struct Shared {
 // What the warps need to know about the row; lives in registers.
 struct Row {
     const uint32_t *tokens;  // the row's history
+    const uint32_t *counts;        // or: its session's count table (then tokens is null)
+    const uint32_t *table_bitmap;  //     and its session's seen-bitmap in global memory
     uint32_t history_len;
     uint32_t id_base;        // global id of column 0
     uint32_t k;
@@ -298,12 +309,20 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
     return d;
 }
 
-// Largest magnitude of N values, or NaN when one of them is NaN (max.NaN keeps it).
+// max(m, v...) that turns NaN as soon as one operand is NaN.
 template <int N>
-__device__ __forceinline__ float widest(const float (&v)[N]) {
-    float m = fabsf(v[0]);
+__device__ __forceinline__ float propagating_max(float m, const float (&v)[N]) {
 #pragma unroll
-    for (int i = 1; i < N; i++) asm("max.NaN.f32 %0, %0, %1;" : "+f"(m) : "f"(fabsf(v[i])));
+    for (int i = 0; i < N; i++) asm("max.NaN.f32 %0, %0, %1;" : "+f"(m) : "f"(v[i]));
+    return m;
+}
+
+// Smallest of N values; a NaN loses against a number, as with fminf.
+template <int N>
+__device__ __forceinline__ float smallest(const float (&v)[N]) {
+    float m = v[0];
+#pragma unroll
+    for (int i = 1; i < N; i++) m = fminf(m, v[i]);
     return m;
 }
 
@@ -365,15 +384,22 @@ __device__ __forceinline__ uint32_t classify(Lists &L, const Row &r, uint32_t w,
     *value = x;
     if (seen) {
         const float most = penalise_with_offset(x, r.flat_offset, r.repetition);
-        if (r.with_counts) {
+        if (r.with_counts && r.counts != nullptr) {
+            // the session's table holds the exact count: no waiting for a token scan
+            const uint32_t seen_times = __ldg(&r.counts[id - r.id_base]);
+            x = seen_times == 0 ? x
+                : penalise_with_offset(x, penalty_offset(seen_times, r.presence, r.frequency), r.repetition);
+            *value = x;
+        } else if (r.with_counts) {
             // the charge grows with the count, so `most` is the most the id can keep
             const bool alive = !is_nonfinite(most) && select_key(most, id) >= bound;
             // greedy rows must also see NaN/Inf, raw or made by the penalty
             const bool wild = kGreedy && (__float_as_uint(x) & 0x7fffffffu) >= kHugeBits;
             return alive || wild ? 2u : 0u;
+        } else {
+            x = most;
+            *value = most;
         }
-        x = most;
-        *value = most;
     }
     if (is_nonfinite(x)) {
         if (kGreedy) atomicMin(&L.wild_key[w], ((unsigned long long)id << 32) | __float_as_uint(x));
@@ -504,12 +530,13 @@ __device__ __noinline__ uint64_t local_cut(Lists &L, const Row r, uint32_t w) {
 }
 
 // The first bound of a unit.  Each warp that has a tile publishes the j-th largest of its
-// lanes' maxima over finite logits of ids the history has not seen, j = ceil(k / warps
-// with a tile): at least j distinct elements of its tile are that large, so the smallest
-// of the published keys bounds k elements.  (A warp with fewer than j such lanes
-// publishes "no bound"; everything finite is then a candidate until some list is cut.)
-// The warp waits until all have published -- a tile's worth of skew at most, with the
-// next tiles already on their way.  Returns the bound as a key.
+// lanes' maxima, j = ceil(k / warps with a tile); a lane whose maximum is not finite, or
+// belongs to an id the history has seen (whose value the penalty will lower), publishes
+// nothing.  At least j distinct elements of the tile are as large as that key and keep
+// their value, so the smallest of the published keys bounds k elements.  (A warp with fewer
+// than j such lanes publishes "no bound"; everything finite is then a candidate until some
+// list is cut.)  The warp waits until all have published -- a tile's worth of skew at most,
+// with the next tiles already on their way.  Returns the bound as a key.
 template <typename T>
 __device__ __noinline__ uint64_t first_bound(Shared &sh, Lists &L, const Row r, const uint32_t *bitmap,
                                              const unsigned char *tile, uint32_t column0,
@@ -520,20 +547,32 @@ __device__ __noinline__ uint64_t first_bound(Shared &sh, Lists &L, const Row r, 
     const uint32_t lane = lane_id();
     const uint4 *vectors = reinterpret_cast<const uint4 *>(tile);
     float best = __uint_as_float(0xff800000u);
+    uint32_t where = 0;  // the vector that holds the lane's maximum
 #pragma unroll
     for (int u = 0; u < kVectors; u++) {
         const uint32_t g = u * 32 + lane;
         if (g >= valid_vectors) continue;
         float v[kPer];
         V::unpack(vectors[g], v);
-        const uint32_t column = column0 + g * kPer;
-        const uint32_t bits =
-            r.seen_any ? (bitmap[column >> 5] >> (column & 31u)) & ((1u << kPer) - 1u) : 0u;
-#pragma unroll
-        for (int j = 0; j < kPer; j++)  // (what is seen or not finite counts as -inf; fmaxf drops a NaN)
-            best = fmaxf(best, ((bits >> j) & 1u) || is_nonfinite(v[j]) ? __uint_as_float(0xff800000u) : v[j]);
+        const float m = largest(v);  // (a NaN never wins)
+        if (m > best) {
+            best = m;
+            where = g;
+        }
     }
-    uint32_t key = best == __uint_as_float(0xff800000u) ? 0u : float_key(best);
+    uint32_t key = 0;
+    if (!is_nonfinite(best)) {
+        // which element it is, and whether the history has seen its id
+        float v[kPer];
+        V::unpack(vectors[where], v);
+        uint32_t j = 0;
+#pragma unroll
+        for (int e = kPer - 1; e >= 0; e--)
+            if (v[e] == best) j = e;
+        const uint32_t column = column0 + where * kPer + j;
+        const bool seen = r.seen_any && ((bitmap[column >> 5] >> (column & 31u)) & 1u);
+        if (!seen) key = float_key(best);
+    }
     const uint32_t per_warp = (r.k + participants - 1) / participants;
     uint32_t kth = 0;
     if (per_warp <= 32u) {
@@ -562,39 +601,73 @@ __device__ __noinline__ uint64_t first_bound(Shared &sh, Lists &L, const Row r, 
     return (uint64_t)peek(&L.first_key) << 32;
 }
 
-// The elements of a tile that reach the bound go on the warp's list.  `hot` has a bit per
-// 128-bit vector of this lane with such an element.  Slots are handed out by ballot, one
-// element per lane and round, so the list's length lives in a register (`count`) and no
-// atomic is needed; a list that cannot take a round is cut to its k best first, which
-// also lifts the bound.  All lanes call; returns the bound the warp knows afterwards.
+// Entries [from, count) of the warp's list are raw: (logit, id) as they were streamed.
+// Here every lane takes one of them at a time and gives it its place: the penalty of a seen
+// id (src/sampler.c:52-58), or the mark "occurrences not counted yet"; what cannot be among
+// the k best under the bound as it stands now is dropped, the rest moves up.  Greedy rows
+// note a NaN/Inf on the way.  All lanes call; returns the new count.
+template <bool kGreedy>
+__device__ __noinline__ uint32_t refine(Lists &L, const Row r, const uint32_t *bitmap, uint32_t w, uint32_t from,
+                                        uint32_t count, uint64_t bound, uint64_t *best_exact) {
+    const uint32_t lane = lane_id();
+    uint32_t out = from;
+    uint64_t best = 0;  // the largest key among the entries kept with their exact value
+    for (uint32_t base = from; base < count; base += 32) {
+        const uint32_t i = base + lane;
+        const bool valid = i < count;
+        const float x = valid ? L.score[w][i] : 0.0f;
+        const uint32_t id = valid ? L.id[w][i] : kPaddingId;
+        const uint32_t column = id - r.id_base;
+        const bool seen = valid && r.seen_any && ((bitmap[column >> 5] >> (column & 31u)) & 1u);
+        float value = x;
+        const uint32_t kind = valid ? classify<kGreedy>(L, r, w, x, id, seen, bound, &value) : 0u;
+        const uint32_t keeping = __ballot_sync(kFullMask, kind != 0u);  // (every lane has read its entry)
+        if (kind != 0u) {
+            const uint32_t at = out + __popc(keeping & ((1u << lane) - 1u));
+            L.score[w][at] = kind == 2u ? x : value;
+            L.id[w][at] = id;
+            if (kind == 2u) atomicOr(&L.deferred[w][at >> 5], 1u << (at & 31u));
+            else best = max(best, select_key(value, id));
+        }
+        out += __popc(keeping);
+        __syncwarp();
+    }
+    if (best_exact) *best_exact = warp_max_u64(best);
+    return out;
+}
+
+// The elements of a tile that reach the bound's score go on the warp's list as they are,
+// (logit, id); refine() deals with them later, a whole warp's worth at a time.  Only lanes
+// that hold such an element look for it, in the vectors the scan marked (`hot`, a bit per
+// vector of the lane), element by element.  Slots are handed out by ballot, one element per lane
+// and round, so the list's length lives in registers and no atomic is needed.  A list that
+// cannot take a round is refined, and cut to its k best if that was not enough, which also
+// lifts the bound.  All lanes call; returns the bound the warp knows afterwards.
 template <typename T, bool kGreedy>
 __device__ __noinline__ uint64_t collect(Lists &L, const Row r, const uint32_t *bitmap, const unsigned char *tile,
-                                         uint32_t column0, uint32_t w, uint32_t hot, uint64_t bound,
-                                         uint32_t *count_io) {
+                                         uint32_t column0, uint32_t valid_vectors, uint32_t w, uint32_t hot,
+                                         uint64_t bound, uint32_t *refined_io, uint32_t *count_io) {
     using V = Lanes<T>;
     constexpr int kPer = V::kPer;
     const uint32_t lane = lane_id();
     const uint4 *vectors = reinterpret_cast<const uint4 *>(tile);
     const float tau = key_to_float((uint32_t)(bound >> 32));
-    uint32_t count = *count_io;
-    // which of this lane's elements go on the list (bit u * kPer + j: element j of vector u)
-    uint64_t take = 0;
-    for (uint32_t rest = hot; rest != 0; rest &= rest - 1) {
-        const uint32_t u = __ffs(rest) - 1;
-        const uint32_t g = u * 32 + lane;
-        float v[kPer];
-        V::unpack(vectors[g], v);
-        const uint32_t column = column0 + g * kPer;
-        const uint32_t bits =
-            r.seen_any ? (bitmap[column >> 5] >> (column & 31u)) & ((1u << kPer) - 1u) : 0u;
+    uint32_t count = *count_io, refined = *refined_io;
+    uint64_t take = 0;  // bit u * kPer + j: element j of this lane's vector u
+    for (uint32_t rest = hot; rest != 0; rest &= rest - 1) {  // bit u: vector u of this lane is worth a look
+        {
+            const uint32_t u = __ffs(rest) - 1;
+            const uint32_t g = u * 32 + lane;
+            if (g >= valid_vectors) break;
+            float v[kPer];
+            V::unpack(vectors[g], v);
+            uint32_t bits = 0;
 #pragma unroll
-        for (int j = 0; j < kPer; j++) {
-            const bool wild = kGreedy && (__float_as_uint(v[j]) & 0x7fffffffu) >= kHugeBits;
-            if (v[j] >= tau || wild) {
-                float value;
-                if (classify<kGreedy>(L, r, w, v[j], r.id_base + column + j, (bits >> j) & 1u, bound, &value))
-                    take |= 1ull << (u * kPer + j);
+            for (int j = 0; j < kPer; j++) {
+                const bool wild = kGreedy && (__float_as_uint(v[j]) & 0x7fffffffu) >= kHugeBits;
+                bits |= (v[j] >= tau || wild ? 1u : 0u) << j;
             }
+            take |= (uint64_t)bits << (u * kPer);
         }
     }
     for (;;) {
@@ -602,31 +675,29 @@ __device__ __noinline__ uint64_t collect(Lists &L, const Row r, const uint32_t *
         if (offering == 0) break;
         const uint32_t round = __popc(offering);
         if (count + round > (uint32_t)kListCap) {
-            if (lane == 0) L.count[w] = count;
-            __syncwarp();
-            const uint64_t mine = local_cut(L, r, w);
-            bound = max(bound, mine);
+            count = refine<kGreedy>(L, r, bitmap, w, refined, count, bound, nullptr);
+            refined = count;
+            if (count + round > (uint32_t)kListCap) {
+                if (lane == 0) L.count[w] = count;
+                __syncwarp();
+                const uint64_t mine = local_cut(L, r, w);
+                bound = max(bound, mine);
+                count = refined = L.count[w];
+            }
             bound = max(bound, (uint64_t)peek64(&L.bound));
-            count = L.count[w];
         }
         if (take != 0) {
             const uint32_t e = __ffsll((long long)take) - 1;
             take &= take - 1;
             const uint32_t position = ((e / kPer) * 32 + lane) * kPer + (e % kPer);
-            const uint32_t column = column0 + position;
-            const bool seen = r.seen_any && ((bitmap[column >> 5] >> (column & 31u)) & 1u);
-            const uint32_t id = r.id_base + column;
-            float value;
-            // (once more: a cut may have lifted the bound since the element was picked)
-            const uint32_t kind = classify<kGreedy>(L, r, w, tile_element<T>(tile, position), id, seen, bound, &value);
             const uint32_t slot = count + __popc(offering & ((1u << lane) - 1u));
-            L.score[w][slot] = kind == 2u ? tile_element<T>(tile, position) : value;
-            L.id[w][slot] = kind != 0u ? id : kPaddingId;  // a slot that turned out useless stays dead
-            if (kind == 2u) atomicOr(&L.deferred[w][slot >> 5], 1u << (slot & 31u));
+            L.score[w][slot] = tile_element<T>(tile, position);
+            L.id[w][slot] = r.id_base + column0 + position;
         }
         count += round;
     }
     *count_io = count;
+    *refined_io = refined;
     return bound;
 }
 
@@ -645,9 +716,15 @@ __device__ __forceinline__ Row make_row(const Params &p, const SamplerConfig &cf
     r.frequency = cfg.frequency_penalty;
     r.repetition = make_repetition(cfg.repetition_penalty);
     r.tokens = nullptr;
+    r.counts = nullptr;
+    r.table_bitmap = nullptr;
     r.history_len = 0;
     *bad_history = 0;
-    if (p.history_tokens != nullptr && p.history_offsets != nullptr && p.bitmap_words != 0 &&
+    if (p.slot_counts != nullptr && penalties_active(cfg)) {
+        const uint32_t session = p.row_slots[row];
+        r.counts = p.slot_counts + (size_t)session * p.vocab_total;
+        r.table_bitmap = p.slot_bitmaps + (size_t)session * p.slot_bitmap_words;
+    } else if (p.history_tokens != nullptr && p.history_offsets != nullptr && p.bitmap_words != 0 &&
         penalties_active(cfg)) {
         const uint64_t begin = p.history_offsets[row], end = p.history_offsets[row + 1];
         if (end < begin || end - begin > p.history_max) {
@@ -657,7 +734,7 @@ __device__ __forceinline__ Row make_row(const Params &p, const SamplerConfig &cf
             r.history_len = (uint32_t)(end - begin);
         }
     }
-    r.seen_any = r.history_len != 0;
+    r.seen_any = r.history_len != 0 || r.counts != nullptr;
     r.with_counts = r.seen_any && cfg.frequency_penalty != 0.0f;
     // the host sends only rows whose penalties cannot raise a logit; a row that
     // slipped through is failed rather than sampled wrongly
@@ -716,7 +793,8 @@ struct Feeder {
 };
 
 // One consumer warp's share of one unit: its tiles against the bound, candidates onto its
-// list.  Returns the number of tiles it looked at.
+// list.  Per tile and lane: the 128-bit vectors of the tile, a maximum of each, the largest of
+// those against the bound's score.  Returns the number of tiles it has looked at.
 template <typename T, bool kGreedy>
 __device__ __noinline__ uint32_t consume_unit(const Params &p, Shared &sh, Lists &L, const Row r, const Unit u,
                                               const uint32_t *bitmap, unsigned char *stages, Feeder &feeder,
@@ -734,7 +812,7 @@ __device__ __noinline__ uint32_t consume_unit(const Params &p, Shared &sh, Lists
     const uint32_t last_vectors = (row_bytes - (tiles - 1) * tile_bytes<T>()) / 16u;
     const uint32_t participants = min((uint32_t)kWarps, u.end - u.first);
     uint64_t bound = 0;
-    uint32_t count = 0;  // entries on this warp's list
+    uint32_t count = 0, refined = 0;  // entries on this warp's list; how many of them refine() has seen
     bool first = true;
     for (uint32_t t = u.first + w; t < u.end; t += kWarps) {
         const uint32_t stage = consumed % kStages;
@@ -751,26 +829,60 @@ __device__ __noinline__ uint32_t consume_unit(const Params &p, Shared &sh, Lists
         bound = max(bound, (uint64_t)peek64(&L.bound));
         const float tau = key_to_float((uint32_t)(bound >> 32));
         const uint4 *vectors = reinterpret_cast<const uint4 *>(tile);
-        uint32_t hot = 0;  // bit u: this lane's vector u holds something at or above the bound
+        // which of the lane's vectors hold something at or above the bound's score (a NaN never
+        // wins a maximum).  Greedy rows: the argmax order must also see NaN, both infinities
+        // and magnitudes a repetition factor of at most 2^40 could push there -- the lane's
+        // NaN-keeping maximum and its minimum tell, and then all its vectors are looked at.
+        uint32_t hot = 0;
+        if (kGreedy) {
+            float top = __uint_as_float(0xff800000u), low = __uint_as_float(0x7f800000u);
+            for (uint32_t g = lane; g < valid_vectors; g += 32) {
+                float v[kPer];
+                V::unpack(vectors[g], v);
+                top = propagating_max(top, v);
+                low = fminf(low, smallest(v));
+            }
+            // (`top` is NaN when the lane holds one, and NaN is not below anything)
+            if (!(top < tau) || low <= -__uint_as_float(kHugeBits)) hot = 0xffffffffu;
+        } else if (valid_vectors == whole) {
 #pragma unroll
-        for (int v8 = 0; v8 < kVectors; v8++) {
-            const uint32_t g = v8 * 32 + lane;
-            float v[kPer];
-            V::unpack(vectors[g], v);  // (beyond a ragged tile's end: stale bytes, masked below)
-            bool above = largest(v) >= tau;  // a NaN never wins a maximum
-            if (kGreedy)  // the argmax order must see NaN and both infinities, and magnitudes
-                          // a repetition factor of at most 2^40 could push there
-                above = above || !(widest(v) < __uint_as_float(kHugeBits));
-            hot |= (above && g < valid_vectors ? 1u : 0u) << v8;
+            for (int v8 = 0; v8 < kVectors; v8++) {
+                float v[kPer];
+                V::unpack(vectors[v8 * 32 + lane], v);
+                hot |= (largest(v) >= tau ? 1u : 0u) << v8;
+            }
+        } else {
+#pragma unroll
+            for (int v8 = 0; v8 < kVectors; v8++) {
+                float v[kPer];
+                V::unpack(vectors[v8 * 32 + lane], v);  // (beyond the row's end: stale bytes, masked)
+                hot |= (largest(v) >= tau && (uint32_t)(v8 * 32) + lane < valid_vectors ? 1u : 0u) << v8;
+            }
         }
-        if (__any_sync(kFullMask, hot != 0))
-            bound = collect<T, kGreedy>(L, r, bitmap, tile, column0, w, hot, bound, &count);
+        if (__any_sync(kFullMask, hot != 0)) {
+            bound = collect<T, kGreedy>(L, r, bitmap, tile, column0, valid_vectors, w, hot, bound, &refined, &count);
+            if (r.k == 1u && count != refined) {
+                // one candidate bounds a row that wants one: the best exact value so far is
+                // the bound, and most later tiles are then not worth a second look
+                uint64_t best = 0;
+                count = refine<kGreedy>(L, r, bitmap, w, refined, count, bound, &best);
+                refined = count;
+                if (best > bound) {
+                    bound = best;
+                    if (lane == 0) atomicMax(&L.bound, (unsigned long long)best);
+                }
+            }
+        }
         __syncwarp();
         FGK_PTICK(3);
         consumed++;
         feeder.template issue<T>(p, stages + (size_t)stage * kStageBytes, &sh.full[w][stage], row_bytes, w,
                                  shard_mode, policy);
         FGK_PTICK(4);
+    }
+    if (count != refined) {
+        bound = max(bound, (uint64_t)peek64(&L.bound));
+        count = refine<kGreedy>(L, r, bitmap, w, refined, count, bound, nullptr);
     }
     if (lane == 0) L.count[w] = count;
     return consumed;
@@ -1150,8 +1262,14 @@ __global__ void __launch_bounds__(kBlock, 1) persistent_select_kernel(const __gr
                 const uint32_t column_end = min(p.vocab, u.end * kTileLogits);
                 uint4 *wide = reinterpret_cast<uint4 *>(bitmap);
                 const uint32_t quad_end = (column_end + 127u) / 128u;
-                for (uint32_t q = column_begin / 128u + helper * 32 + lane; q < quad_end; q += 32 * kHistoryWarps)
-                    wide[q] = make_uint4(0, 0, 0, 0);
+                if (r.table_bitmap != nullptr) {  // the session keeps its bitmap: fetch the unit's part of it
+                    const uint4 *kept = reinterpret_cast<const uint4 *>(r.table_bitmap);
+                    for (uint32_t q = column_begin / 128u + helper * 32 + lane; q < quad_end; q += 32 * kHistoryWarps)
+                        wide[q] = __ldg(&kept[q]);
+                } else {
+                    for (uint32_t q = column_begin / 128u + helper * 32 + lane; q < quad_end; q += 32 * kHistoryWarps)
+                        wide[q] = make_uint4(0, 0, 0, 0);
+                }
                 asm volatile("bar.sync 2, %0;" ::"n"(kHistoryWarps * 32) : "memory");
                 constexpr int kBatch = 16;  // tokens per lane and trip, loaded before any is used
                 uint32_t bad = 0;
@@ -1295,6 +1413,10 @@ static persist::Params to_persist_params(const fgk_stream_launch *l) {
     p.part_ids = l->part_ids;
     p.part_meta = static_cast<persist::PartRecord *>(l->part_meta);
     p.tickets = l->tickets;
+    p.slot_counts = l->slot_counts;
+    p.slot_bitmaps = l->slot_bitmaps;
+    p.row_slots = l->row_slots;
+    p.slot_bitmap_words = l->slot_bitmap_words;
     p.wait_polls = l->wait_polls;
     p.withhold_cta = l->withhold_armed ? l->withhold_cta : 0xffffffffu;
     p.withhold_issue = l->withhold_issue;

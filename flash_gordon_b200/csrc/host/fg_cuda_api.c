@@ -400,6 +400,60 @@ fg_status fg_cuda_topk_select(fg_cuda_context *c, fg_cuda_tensor *out_scores,
     return FG_OK;
 }
 
+fg_status fg_cuda_topk_reduce(fg_cuda_context *c, fg_cuda_tensor *out_scores, fg_cuda_tensor *out_ids,
+                              const fg_cuda_tensor *in_scores, const fg_cuda_tensor *in_ids, uint32_t count,
+                              uint32_t *output_count, fg_error *err) {
+    /* src/vk.c:2235 */
+    const uint64_t groups = ((uint64_t)count + 4095u) / 4096u;
+    uint64_t produced = groups * 512u;
+    if (groups == 1u && count < 512u) produced = count;
+    if (!c || !count || !output_count || !tensor_range(in_scores, 0, (uint64_t)count * 4u) ||
+        (in_ids && !tensor_range(in_ids, 0, (uint64_t)count * 4u)) ||
+        !tensor_range(out_scores, 0, produced * 4u) || !tensor_range(out_ids, 0, produced * 4u)) {
+        fg_error_set(err, FG_ERR_ARGUMENT, "invalid top-k reduction dispatch");
+        return FG_ERR_ARGUMENT;
+    }
+    fg_status status = fg_cuda_enter(c, err);
+    if (status != FG_OK) return status;
+    const int e = fgk_launch_topk_reduce((float *)out_scores->base, (uint32_t *)out_ids->base,
+                                         (const float *)in_scores->base,
+                                         in_ids ? (const uint32_t *)in_ids->base : NULL, count,
+                                         (uint32_t)produced, c->stream);
+    c->launches++;
+    if (e) return fg_cuda_fail(err, e, "top-k reduction kernel");
+    *output_count = (uint32_t)produced;
+    return FG_OK;
+}
+
+fg_status fg_cuda_router_topk(fg_cuda_context *c, fg_cuda_tensor *selected, fg_cuda_tensor *gates,
+                              const fg_cuda_tensor *logits, uint32_t experts, uint32_t tokens, uint32_t k,
+                              fg_error *err) {
+    /* src/vk.c:2257 (fixed at 512 experts and k = 10 there); src/q38_math.c:49 */
+    const uint64_t pairs = (uint64_t)tokens * k;
+    if (!c || !experts || !tokens || !k || k > experts || k > 32u ||
+        !tensor_range(logits, 0, (uint64_t)tokens * experts * 4u) || !tensor_range(selected, 0, pairs * 4u) ||
+        !tensor_range(gates, 0, pairs * 4u)) {
+        fg_error_set(err, FG_ERR_ARGUMENT, "invalid GPU router top-k dispatch");
+        return FG_ERR_ARGUMENT;
+    }
+    fg_status status = fg_cuda_enter(c, err);
+    if (status != FG_OK) return status;
+    uint32_t *bad = (uint32_t *)c->first_error + 8; /* a word of the context's 256-byte block */
+    int e = fgk_memset_async(bad, 0xff, 4u, c->stream);
+    if (!e) e = fgk_launch_router_topk((uint32_t *)selected->base, (float *)gates->base,
+                                       (const float *)logits->base, tokens, experts, k, bad, c->stream);
+    c->launches++;
+    uint32_t first_bad = UINT32_MAX;
+    if (!e) e = fgk_copy_to_host_async(&first_bad, bad, 4u, c->stream);
+    if (!e) e = fgk_stream_synchronize(c->stream);
+    if (e) return fg_cuda_fail(err, e, "router kernel");
+    if (first_bad != UINT32_MAX) {  /* src/q38_math.c:61 */
+        fg_error_set(err, FG_ERR_FORMAT, "router probabilities are not finite (token %u)", first_bad);
+        return FG_ERR_FORMAT;
+    }
+    return FG_OK;
+}
+
 fg_status fg_cuda_history_reset(fg_cuda_context *c, fg_cuda_tensor *counts, uint32_t vocab,
                                 const uint32_t *history, uint32_t count, fg_error *err) {
     /* src/output.c:604-606 */
@@ -544,7 +598,8 @@ static fg_status check_batch(const fg_cuda_context *c, const fg_cuda_sample_args
         fg_error_set(err, FG_ERR_ARGUMENT, "sampled rows need one uniform draw each");
         return FG_ERR_ARGUMENT;
     }
-    if (!a->history_tokens || a->history_max == 0u) traits->penalties = traits->counts = false;
+    if ((!a->history_tokens || a->history_max == 0u) && !c->session_counts)
+        traits->penalties = traits->counts = false;
     return FG_OK;
 }
 
@@ -654,6 +709,11 @@ static fg_status run_stream(fg_cuda_context *c, const fg_cuda_sample_args *a,
                          ((size_t)a->vocab * element) % 16u == 0u && c->forced_splits <= 1u &&
                          !(traits->penalties && traits->raising) &&
                          fgk_persistent_dynamic_smem(whole_bitmap, NULL) != 0u;
+    if (c->session_counts && !(ring_ok && c->path != FG_CUDA_PATH_REGISTERS && vocab_offset == 0u)) {
+        /* (the executor then falls back to token lists) */
+        fg_error_set(err, FG_ERR_UNAVAILABLE, "session tables are read by the ring kernel only");
+        return FG_ERR_UNAVAILABLE;
+    }
     if (c->path == FG_CUDA_PATH_RING && !ring_ok) {
         fg_error_set(err, FG_ERR_ARGUMENT,
                      "the ring path needs whole 16-byte aligned rows and penalties that only lower logits");
@@ -704,6 +764,10 @@ static fg_status run_stream(fg_cuda_context *c, const fg_cuda_sample_args *a,
         l.splits = max_parts;
         l.split_len = (uint32_t)per_cta;
         l.bitmap_words = whole_bitmap;
+        l.slot_counts = c->session_counts;
+        l.slot_bitmaps = c->session_bitmaps;
+        l.row_slots = c->session_rows;
+        l.slot_bitmap_words = c->session_bitmap_words;
         l.wait_polls = c->ring_wait_polls;
         l.withhold_armed = c->ring_withhold_armed;
         l.withhold_cta = c->ring_withhold_cta;

@@ -17,6 +17,14 @@ struct fg_cuda_context {
     /* test seam of the ring kernel (fg_cuda_internal_ring_controls) */
     uint32_t ring_deal, ring_wait_polls, ring_withhold_armed, ring_withhold_cta, ring_withhold_issue;
 
+    /* Set by the stateful executor around a call: the batch's penalties come from session
+     * tables (counts [slots][vocab], seen-bitmaps [slots][words], one session index per row)
+     * instead of token lists.  Only the ring kernel reads them. */
+    const uint32_t *session_counts;
+    const uint32_t *session_bitmaps;
+    const uint32_t *session_rows;
+    uint32_t session_bitmap_words;
+
     /* device scratch, grown on demand and then reused (no allocation on a warm call) */
     void *parts;            /* candidate hand-off between the splits of a row */
     size_t parts_bytes;

@@ -142,6 +142,28 @@ fg_status fg_cuda_topk_select(fg_cuda_context *context, fg_cuda_tensor *out_scor
                               const fg_cuda_tensor *in_ids, uint32_t count, uint32_t k,
                               uint32_t *output_count, fg_error *err);
 
+/* fg_vk_topk_reduce (src/vk.c:2235) + shaders/fg_topk_reduce_v2.comp: the 512 best
+ * (score, id) pairs of every 4096-element tile, SORTED by the order of that shader: a padding
+ * id last, a NaN/Inf before every finite score (smaller id first among them), then larger
+ * score, then smaller id.  The reference's long-context block selection cascades it
+ * (src/qsa.c:833-855).  *output_count = ceil(count / 4096) * 512, or `count` when a lone tile
+ * holds fewer than 512; short tiles are padded with (-inf, 0xffffffff).  in_ids == NULL means
+ * ids are 0..count-1. */
+fg_status fg_cuda_topk_reduce(fg_cuda_context *context, fg_cuda_tensor *out_scores,
+                              fg_cuda_tensor *out_ids, const fg_cuda_tensor *in_scores,
+                              const fg_cuda_tensor *in_ids, uint32_t count, uint32_t *output_count,
+                              fg_error *err);
+
+/* fg_vk_router_top10 (src/vk.c:2257) generalised to any k <= 32, with the arithmetic of the
+ * reference's CPU statement fg_q38_router_topk (src/q38_math.c:48-64): per token the k
+ * largest of `experts` logits (ties: smaller id) into selected[tokens][k], and into
+ * gates[tokens][k] their softmax probabilities over ALL experts (fp64), rounded to fp32 and
+ * renormalised by their sum.  A token with a NaN or +Inf logit gets ids 0xffffffff and
+ * weights 0 (as the shader leaves them) and the call returns FG_ERR_FORMAT naming it. */
+fg_status fg_cuda_router_topk(fg_cuda_context *context, fg_cuda_tensor *selected, fg_cuda_tensor *gates,
+                              const fg_cuda_tensor *logits, uint32_t experts, uint32_t tokens, uint32_t k,
+                              fg_error *err);
+
 /* fg_output_history_reset (src/output.c:601-617) for a device-resident table:
  * counts[0..vocab) = occurrences of each id in history[0..count) (host
  * pointer), saturating at UINT32_MAX.  count <= FG_NATIVE_CONTEXT; an id
@@ -245,6 +267,50 @@ fg_status fg_cuda_merge_select(fg_cuda_context *context, const fg_cuda_sample_ar
                                uint32_t shards, uint32_t k_shard,
                                const uint32_t *shard_first, const uint32_t *shard_width,
                                fg_error *err);
+
+/* ------------------------------------------------------- stateful executor */
+
+/* Session slots whose token history stays on the GPU between decode steps: the shape of
+ * the reference's output executor (include/fg_output.h:42-66), which keeps one occurrence
+ * table per session (src/output.c:525, 601-628) and adds every token it picks with
+ * penalties active (src/output.c:742, 752).  Logits come from the caller (the lm_head that
+ * produces them is not part of this library); everything after them is here.
+ *   vocab             logits per row (fp32 for the one-row calls)
+ *   session_slots     sessions the executor can hold (the reference has 2)
+ *   history_capacity  most tokens one session's history may hold (<= FG_NATIVE_CONTEXT) */
+typedef struct fg_cuda_output_executor fg_cuda_output_executor;
+/* fg_output_executor_create / _destroy (include/fg_output.h:42-43). */
+fg_status fg_cuda_output_executor_create(fg_cuda_context *context, uint32_t vocab, uint32_t session_slots,
+                                         uint32_t history_capacity, fg_cuda_output_executor **out,
+                                         fg_error *err);
+void fg_cuda_output_executor_destroy(fg_cuda_output_executor *executor);
+/* fg_output_set_session / fg_output_session (include/fg_output.h:49-50): the session the
+ * one-row calls below serve.  A slot outside the table is ignored. */
+void fg_cuda_output_set_session(fg_cuda_output_executor *executor, uint32_t session_slot);
+uint32_t fg_cuda_output_session(const fg_cuda_output_executor *executor);
+uint32_t fg_cuda_output_history_length(const fg_cuda_output_executor *executor, uint32_t session_slot);
+/* fg_output_history_reset (include/fg_output.h:44-46; src/output.c:601-617): the current
+ * session's history becomes history[0..count) (HOST).  A token >= vocab: FG_ERR_FORMAT. */
+fg_status fg_cuda_output_history_reset(fg_cuda_output_executor *executor, const uint32_t *history,
+                                       uint32_t count, fg_error *err);
+/* fg_output_history_increment (include/fg_output.h:51-52; src/output.c:619-628). */
+fg_status fg_cuda_output_history_increment(fg_cuda_output_executor *executor, uint32_t token, fg_error *err);
+/* fg_output_greedy (include/fg_output.h:55-56; src/output.c:560-599) on a row of fp32 logits:
+ * argmax of the raw logits; a NaN/Inf finalist is FG_ERR_MISMATCH. */
+fg_status fg_cuda_output_greedy(fg_cuda_output_executor *executor, const fg_cuda_tensor *logits,
+                                uint32_t *token, float *logit, fg_error *err);
+/* fg_output_sample (include/fg_output.h:64-66; src/output.c:702-755) on a row of fp32 logits
+ * with the current session's history; when the config's penalties are active the picked
+ * token joins that history. */
+fg_status fg_cuda_output_sample(fg_cuda_output_executor *executor, const fg_cuda_tensor *logits,
+                                const fg_sampler_config *config, float uniform, uint32_t *token,
+                                float *logit, fg_error *err);
+/* The same for a whole decode step (no reference counterpart: it decodes one row per call):
+ * args as for fg_cuda_sample_batch with history_tokens / history_offsets NULL and without
+ * FG_CUDA_SAMPLE_ASYNC; row r belongs to session slots[r] (HOST array).  Rows whose
+ * penalties are active and that end FG_OK add their token to their session. */
+fg_status fg_cuda_output_sample_sessions(fg_cuda_output_executor *executor, const fg_cuda_sample_args *args,
+                                         const uint32_t *slots, fg_error *err);
 
 /* ---------------------------------------------------------------- multi-GPU */
 

@@ -81,6 +81,8 @@ def load(kind: str = "port") -> ctypes.CDLL:
         "fgo_apply_penalties_shader": (None, [P, P, u32, c_float, c_float, c_float]),
         "fgo_argmax_reduce": (u32, [P, P, P, P, u32]),
         "fgo_topk_select": (u32, [P, P, P, P, u32, u32]),
+        "fgo_topk_reduce": (u32, [P, P, P, P, u32]),
+        "fgo_router_topk": (c_int, [P, u32, u32, P, P]),
         "fgo_select_general": (c_int, [CFG, c_bool, P, P, u32, c_float, POINTER(u32),
                                        POINTER(c_float), POINTER(u32), POINTER(c_double), E]),
         "fgo_sample_batch": (c_int, [P, u32, u32, u32, u64, P, P, CFG, u32, c_bool, P, P, P, P,
@@ -172,6 +174,33 @@ def topk_select(lib, scores, ids, k: int):
     out_ids = np.zeros(groups * k, dtype=np.uint32)
     lib.fgo_topk_select(_ptr(out_scores), _ptr(out_ids), _ptr(scores), _ptr(ids), len(scores), k)
     return out_scores, out_ids
+
+
+def topk_reduce(lib, scores, ids=None):
+    """Sorted top-512 of every 4096-element tile (fg_vk_topk_reduce)."""
+    scores = np.ascontiguousarray(scores, dtype=np.float32)
+    ids = None if ids is None else np.ascontiguousarray(ids, dtype=np.uint32)
+    groups = (len(scores) + 4095) // 4096
+    out_scores = np.zeros(groups * 512, dtype=np.float32)
+    out_ids = np.zeros(groups * 512, dtype=np.uint32)
+    produced = lib.fgo_topk_reduce(_ptr(out_scores), _ptr(out_ids), _ptr(scores), _ptr(ids), len(scores))
+    return out_scores[:produced], out_ids[:produced]
+
+
+def router_topk(lib, logits, k: int, reference: bool = False):
+    """(status, ids, weights) of one token's router logits; `reference` calls the reference's
+    own fg_q38_router_topk (only in the reference build of the oracle)."""
+    logits = np.ascontiguousarray(logits, dtype=np.float32)
+    ids = np.zeros(k, dtype=np.uint32)
+    weights = np.zeros(k, dtype=np.float32)
+    if reference:
+        fn = lib.fg_q38_router_topk
+        fn.restype = c_int
+        fn.argtypes = [c_void_p, c_uint32, c_uint32, c_void_p, c_void_p, POINTER(OracleError)]
+        status = fn(_ptr(logits), len(logits), k, _ptr(ids), _ptr(weights), byref(OracleError()))
+    else:
+        status = lib.fgo_router_topk(_ptr(logits), len(logits), k, _ptr(ids), _ptr(weights))
+    return status, ids, weights
 
 
 def sample_batch(lib, logits: np.ndarray, configs, uniforms=None, history_tokens=None,

@@ -43,6 +43,11 @@ uint32_t fgo_argmax_reduce(float *out_scores, uint32_t *out_ids, const float *sc
                            const uint32_t *ids, uint32_t count);
 /* shaders/fg_topk_select_fallback.comp:22-43; ids == NULL means 0..count-1.
  * Returns ceil(count/1024)*k. */
+/* shaders/fg_topk_reduce_v2.comp + src/vk.c:2235: sorted top-512 of every 4096-element tile */
+uint32_t fgo_topk_reduce(float *out_scores, uint32_t *out_ids, const float *scores,
+                         const uint32_t *ids, uint32_t count);
+/* src/q38_math.c:48-64 restated */
+fg_status fgo_router_topk(const float *logits, uint32_t count, uint32_t k, uint32_t *ids, float *weights);
 uint32_t fgo_topk_select(float *out_scores, uint32_t *out_ids, const float *scores,
                          const uint32_t *ids, uint32_t count, uint32_t k);
 

@@ -134,6 +134,86 @@ uint32_t fgo_topk_select(float *out_scores, uint32_t *out_ids, const float *scor
     return groups * k;
 }
 
+/* shaders/fg_topk_reduce_v2.comp:10: the order of the sorted top-512 kernel.  Unlike the
+ * generation selector above, a NaN/Inf comes BEFORE every finite score here. */
+static bool reduce_before(float a, uint32_t a_id, float b, uint32_t b_id) {
+    const bool a_pad = a_id == FGO_PADDING_ID, b_pad = b_id == FGO_PADDING_ID;
+    if (a_pad || b_pad) return !a_pad && b_pad;
+    const bool a_wild = !isfinite(a), b_wild = !isfinite(b);
+    if (a_wild || b_wild) return a_wild != b_wild ? a_wild : a_id < b_id;
+    return a > b || (a == b && a_id < b_id);
+}
+
+/* shaders/fg_topk_reduce_v2.comp:27-85 + src/vk.c:2235: the best 512 of every 4096-element
+ * tile, sorted; a short tile is padded with (-inf, padding id); a lone tile with fewer
+ * than 512 entries hands back just those.  (The shader sorts 64-slot runs and merges them;
+ * an insertion into a sorted prefix gives the same sequence, the order being total.) */
+uint32_t fgo_topk_reduce(float *out_scores, uint32_t *out_ids, const float *scores,
+                         const uint32_t *ids, uint32_t count) {
+    const uint32_t tile = 4096u, keep = 512u;
+    const uint32_t groups = (count + tile - 1u) / tile;
+    uint32_t produced = groups * keep;
+    if (groups == 1u && count < keep) produced = count;
+    for (uint32_t g = 0; g < groups; g++) {
+        const uint32_t begin = g * tile;
+        const uint32_t here = count - begin < tile ? count - begin : tile;
+        float top[512];
+        uint32_t top_id[512];
+        uint32_t held = 0;
+        for (uint32_t i = 0; i < here; i++) {
+            const float value = scores[begin + i];
+            const uint32_t id = ids ? ids[begin + i] : begin + i;
+            if (held == keep && !reduce_before(value, id, top[keep - 1u], top_id[keep - 1u])) continue;
+            uint32_t slot = held < keep ? held++ : keep - 1u;
+            while (slot > 0u && reduce_before(value, id, top[slot - 1u], top_id[slot - 1u])) {
+                top[slot] = top[slot - 1u];
+                top_id[slot] = top_id[slot - 1u];
+                slot--;
+            }
+            top[slot] = value;
+            top_id[slot] = id;
+        }
+        for (uint32_t i = 0; i < keep; i++) {
+            const size_t at = (size_t)g * keep + i;
+            if (at >= produced) break;
+            out_scores[at] = i < held ? top[i] : -INFINITY;
+            out_ids[at] = i < held ? top_id[i] : FGO_PADDING_ID;
+        }
+    }
+    return produced;
+}
+
+/* src/q38_math.c:48-64 (fg_q38_router_topk), restated: softmax over all experts in fp64,
+ * the k largest logits (ties: smaller id), their probabilities rounded to fp32 and
+ * renormalised by their fp64 sum. */
+fg_status fgo_router_topk(const float *logits, uint32_t count, uint32_t k, uint32_t *ids, float *weights) {
+    if (!logits || !ids || !weights || count == 0u || k == 0u || k > count) return FG_ERR_ARGUMENT;
+    float top = -INFINITY;
+    for (uint32_t i = 0; i < count; i++)
+        if (logits[i] > top) top = logits[i];
+    double total = 0.0;
+    for (uint32_t i = 0; i < count; i++) total += exp((double)logits[i] - top);
+    double picked = 0.0;
+    for (uint32_t slot = 0; slot < k; slot++) {
+        uint32_t best = UINT32_MAX;
+        float best_value = -INFINITY;
+        for (uint32_t i = 0; i < count; i++) {
+            bool taken = false;
+            for (uint32_t j = 0; j < slot && !taken; j++) taken = ids[j] == i;
+            if (!taken && (logits[i] > best_value || (logits[i] == best_value && i < best))) {
+                best = i;
+                best_value = logits[i];
+            }
+        }
+        ids[slot] = best;
+        weights[slot] = (float)(exp((double)best_value - top) / total);
+        picked += weights[slot];
+    }
+    if (!(picked > 0.0)) return FG_ERR_FORMAT;
+    for (uint32_t slot = 0; slot < k; slot++) weights[slot] = (float)(weights[slot] / picked);
+    return FG_OK;
+}
+
 /* ------------------------------------------------- generalised select (A.5) */
 
 typedef struct ranked {

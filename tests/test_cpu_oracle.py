@@ -238,3 +238,90 @@ def test_sharded_oracle_equals_unsharded():
     bad = oracle.merge_select(lib, scores, ids, [s * width for s in range(shards)], [width] * shards,
                               [cfg], uniforms)
     assert bad[3][2] == 5 and bad[3][0] == 0
+
+
+def _reduce_before(a, ai, b, bi):
+    """tests/test_fg_vk.c:1223-1229 of the reference (topk_before)."""
+    ap, bp = ai == 0xFFFFFFFF, bi == 0xFFFFFFFF
+    if ap or bp:
+        return (not ap) and bp
+    an, bn = not np.isfinite(a), not np.isfinite(b)
+    if an or bn:
+        return an if an != bn else ai < bi
+    return a > b or (a == b and ai < bi)
+
+
+def reduce_chunked_inputs(count):
+    """The input generator of tests/test_fg_vk.c:1243-1252 (zeros, NaN, +-Inf sprinkled in)."""
+    scores = np.zeros(count, dtype=np.float32)
+    seed = 12345
+    for i in range(count):
+        seed = (seed * 1664525 + 1013904223) & 0xFFFFFFFF
+        value = np.float32(((seed >> 8) % 2000) * 0.5)
+        if i % 97 == 0:
+            value = np.float32(0.0)
+        if i % 257 == 0:
+            value = np.float32(np.nan)
+        if i % 389 == 0:
+            value = np.float32(np.inf)
+        if i % 521 == 0:
+            value = np.float32(-np.inf)
+        scores[i] = value
+    return scores
+
+
+def test_sorted_top512_oracle_has_the_reference_tests_properties(port):
+    """tests/test_fg_vk.c:1231-1272 (topk_reduce_chunked) and :1202 (output_topk), on the oracle's
+    restatement of shaders/fg_topk_reduce_v2.comp."""
+    everything = reduce_chunked_inputs(8200)
+    for count in (1, 2, 7, 63, 64, 65, 100, 511, 512, 513, 1000, 1024, 1091, 2048, 4032, 4096, 4097, 5000,
+                  8192, 8200):
+        scores = everything[:count]
+        got_scores, got_ids = oracle.topk_reduce(port, scores)
+        groups = (count + 4095) // 4096
+        expected = count if groups == 1 and count < 512 else groups * 512
+        assert len(got_scores) == expected, count
+        for i in range(expected):
+            group, within = divmod(i, 512)
+            remaining = max(count - group * 4096, 0)
+            valid = min(remaining, 512)
+            if within >= valid:
+                assert got_scores[i] == -np.inf and got_ids[i] == 0xFFFFFFFF
+                continue
+            ident = int(got_ids[i])
+            assert ident < count and got_scores[i:i + 1].view(np.uint32)[0] == scores[ident:ident + 1].view(np.uint32)[0]
+            if within + 1 < valid:
+                assert not _reduce_before(got_scores[i + 1], int(got_ids[i + 1]), got_scores[i], ident), (count, i)
+    # the vocabulary-sized cascade: a NaN sorts first, then the three spikes
+    vocab = 248_320
+    scores = -np.arange(vocab, dtype=np.float32)
+    scores[12345], scores[23456], scores[34567], scores[45678] = 100.0, 99.0, 98.0, np.nan
+    cur_scores, cur_ids = scores, None
+    while len(cur_scores) > 512:
+        cur_scores, cur_ids = oracle.topk_reduce(port, cur_scores, cur_ids)
+    assert cur_ids[:4].tolist() == [45678, 12345, 23456, 34567] and not np.isfinite(cur_scores[0])
+    assert cur_scores[1:4].tolist() == [100.0, 99.0, 98.0]
+
+
+def test_router_topk_port_equals_the_reference(port):
+    rng = np.random.default_rng(77)
+    have_reference = oracle.available("reference")
+    ref = oracle.load("reference") if have_reference else None
+    for trial in range(60):
+        count = [512, 512, 64, 17][trial % 4]
+        k = [10, 10, 8, 17][trial % 4]
+        logits = (rng.standard_normal(count) * (0.1 + trial % 5)).astype(np.float32)
+        if trial % 3 == 0:
+            logits[rng.integers(0, count, 6)] = logits[3]  # ties: the smaller id wins
+        status, ids, weights = oracle.router_topk(port, logits, k)
+        assert status == 0 and len(set(ids.tolist())) == k
+        order = sorted(range(count), key=lambda i: (-logits[i], i))[:k]
+        assert ids.tolist() == order
+        assert abs(float(weights.sum()) - 1.0) < 1e-5
+        if have_reference:
+            ref_status, ref_ids, ref_weights = oracle.router_topk(ref, logits, k, reference=True)
+            assert ref_status == status and np.array_equal(ref_ids, ids)
+            assert np.array_equal(ref_weights.view(np.uint32), weights.view(np.uint32))
+    bad = np.zeros(16, dtype=np.float32)
+    bad[3] = np.nan
+    assert oracle.router_topk(port, bad, 4)[0] == 4  # FG_ERR_FORMAT, src/q38_math.c:61

@@ -175,3 +175,80 @@ def test_history_table(context, port):
     assert context.history_reset(counts, vocab, [1, 2, 1000]) == FG_ERR_FORMAT
     assert context.history_reset(counts, vocab, []) == FG_OK
     assert not _words(counts.read()).any()
+
+
+# ---- sorted top-512 per tile (fg_vk_topk_reduce) and router top-k: the kernels next door ----
+
+def test_topk_reduce_chunked_sizes(context, port):
+    """tests/test_fg_vk.c:1231-1272 of the reference restated: 39 sizes from 1 to 8200 with zeros,
+    NaN and both infinities sprinkled in; every output bit-equal to the oracle's."""
+    from test_cpu_oracle import reduce_chunked_inputs
+    everything = reduce_chunked_inputs(8200)
+    ids = np.arange(8200, dtype=np.uint32)
+    for count in (1, 2, 7, 63, 64, 65, 100, 127, 128, 129, 192, 320, 448, 511, 512, 513, 576, 640, 704, 768, 1000,
+                  1024, 1088, 1090, 1091, 1152, 1216, 2048, 2112, 3000, 4032, 4096, 4097, 4160, 4224, 5000, 8000,
+                  8192, 8200):
+        want_scores, want_ids = oracle.topk_reduce(port, everything[:count], ids[:count])
+        groups = (count + 4095) // 4096
+        out_scores, out_ids = context.tensor(groups * 512 * 4), context.tensor(groups * 512 * 4)
+        in_scores = context.tensor_from(torch.from_numpy(everything[:count].copy()))
+        for explicit in (True, False):
+            in_ids = context.tensor_from(torch.from_numpy(ids[:count].view(np.int32).copy())) if explicit else None
+            status, produced = context.topk_reduce(out_scores, out_ids, in_scores, in_ids, count)
+            assert status == FG_OK and produced == len(want_scores), count
+            got_scores = np.frombuffer(out_scores.read(produced * 4), dtype=np.uint32)
+            got_ids = np.frombuffer(out_ids.read(produced * 4), dtype=np.uint32)
+            assert np.array_equal(got_ids, want_ids), count
+            assert np.array_equal(got_scores, want_scores.view(np.uint32)), count
+
+
+def test_topk_reduce_vocabulary_cascade_puts_the_nan_first(context):
+    """tests/test_fg_vk.c:1202 of the reference: the cascade over 248,320 scores; a NaN sorts
+    first, then the three spikes."""
+    scores = -np.arange(REFERENCE_VOCAB, dtype=np.float32)
+    scores[12345], scores[23456], scores[34567], scores[45678] = 100.0, 99.0, 98.0, np.nan
+    first = (REFERENCE_VOCAB + 4095) // 4096 * 512
+    source_scores = context.tensor_from(torch.from_numpy(scores))
+    source_ids = None
+    scratch = [(context.tensor(first * 4), context.tensor(first * 4)) for _ in range(2)]
+    count, slot = REFERENCE_VOCAB, 0
+    while count > 512:
+        status, count = context.topk_reduce(scratch[slot][0], scratch[slot][1], source_scores, source_ids, count)
+        assert status == FG_OK
+        source_scores, source_ids = scratch[slot]
+        slot ^= 1
+    assert count == 512
+    top_scores = np.frombuffer(source_scores.read(16), dtype=np.float32)
+    top_ids = np.frombuffer(source_ids.read(16), dtype=np.uint32)
+    assert top_ids.tolist() == [45678, 12345, 23456, 34567] and not np.isfinite(top_scores[0])
+    assert top_scores[1:].tolist() == [100.0, 99.0, 98.0]
+    assert context.topk_reduce(scratch[0][0], scratch[0][1], source_scores, source_ids, 0)[0] == FG_ERR_ARGUMENT
+
+
+def test_router_topk_matches_the_reference_s_cpu_statement(context, port):
+    """fg_q38_router_topk (src/q38_math.c:48-64): ids bit-exact, gate weights within 1e-6
+    relative (exp() comes from another library here)."""
+    rng = np.random.default_rng(5)
+    experts, tokens, k = 512, 37, 10
+    logits = (rng.standard_normal((tokens, experts)) * 2.0).astype(np.float32)
+    logits[3, 100:110] = logits[3, 5]       # ties: smaller ids first
+    logits[9, :] = 0.25                      # all equal
+    logits[11, 7] = -np.inf                  # a -inf expert simply never wins
+    device_logits = context.tensor_from(torch.from_numpy(logits))
+    selected, gates = context.tensor(tokens * k * 4), context.tensor(tokens * k * 4)
+    status, message = context.router_topk(selected, gates, device_logits, experts, tokens, k)
+    assert status == FG_OK, message
+    got_ids = np.frombuffer(selected.read(), dtype=np.uint32).reshape(tokens, k)
+    got_weights = np.frombuffer(gates.read(), dtype=np.float32).reshape(tokens, k)
+    for t in range(tokens):
+        want_status, want_ids, want_weights = oracle.router_topk(port, logits[t], k)
+        assert want_status == FG_OK and np.array_equal(got_ids[t], want_ids), t
+        np.testing.assert_allclose(got_weights[t], want_weights, rtol=1e-6, atol=0)
+    # a NaN or +Inf logit: that token's outputs are blanked and the call says which token
+    logits[20, 3] = np.nan
+    status, message = context.router_topk(selected, gates, context.tensor_from(torch.from_numpy(logits)),
+                                          experts, tokens, k)
+    assert status == FG_ERR_FORMAT and "token 20" in message
+    got_ids = np.frombuffer(selected.read(), dtype=np.uint32).reshape(tokens, k)
+    assert (got_ids[20] == 0xFFFFFFFF).all() and (got_ids[19] != 0xFFFFFFFF).all()
+    assert context.router_topk(selected, gates, device_logits, experts, tokens, 33)[0] == FG_ERR_ARGUMENT

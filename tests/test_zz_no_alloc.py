@@ -12,18 +12,18 @@ import numpy as np
 import pytest
 import torch
 
-from flash_gordon_b200 import (FG_CUDA_F32, FG_ERR_ARGUMENT, FG_ERR_LIMIT, FG_OK, FgError, SampleArgs,
-                               SamplerConfig, config_array, synth)
-from helpers import as_u32, random_workload
+from flash_gordon_b200 import (FG_CUDA_BF16, FG_CUDA_F32, FG_ERR_ARGUMENT, FG_ERR_LIMIT, FG_ERR_UNAVAILABLE, FG_OK,
+                               FgError, SampleArgs, SamplerConfig, config_array, synth)
+from helpers import as_u32, assert_rows_equal, random_workload, run_oracle
 
 pytestmark = pytest.mark.gpu
 
 
-def call_static(library, w, out, stream=0):
+def call_static(library, w, out, stream=0, flags=0):
     cfgs = config_array(w.configs)
     args = SampleArgs()
     args.logits = w.logits.data_ptr()
-    args.dtype = FG_CUDA_F32
+    args.dtype = FG_CUDA_BF16 if w.logits.dtype == torch.bfloat16 else FG_CUDA_F32
     args.rows, args.vocab = w.rows, w.vocab
     args.row_stride = w.logits.stride(0)
     args.history_tokens = w.history_tokens.data_ptr() if w.history_tokens is not None else None
@@ -32,6 +32,7 @@ def call_static(library, w, out, stream=0):
     args.config_count = len(cfgs)
     args.configs = ctypes.cast(cfgs, POINTER(SamplerConfig))
     args.uniforms = w.uniforms.data_ptr()
+    args.flags = flags
     args.tokens, args.token_logits, args.row_status = (t.data_ptr() for t in out)
     err = FgError()
     status = library.fg_cuda_sample_batch_static(0, c_void_p(stream), byref(args), byref(err))
@@ -71,6 +72,41 @@ def test_static_scratch_entry_matches_the_context_entry_twice(library, context):
                               want.token_logits.cpu().numpy().view(np.uint32)[ok])
 
 
+class _Result:
+    """The outputs of the static entry in the shape the comparison helpers take."""
+
+    def __init__(self, out, status):
+        self.tokens, self.token_logits, self.row_status = out
+        ok = as_u32(out[2])
+        failing = np.nonzero(ok)[0]
+        self.status = int(ok[failing[0]]) if failing.size else status
+
+
+def test_static_scratch_entry_against_the_oracle_without_allocating(library, context):
+    """The entry's own results against the CPU oracle (not only against the other entry
+    point), for fp32 and bf16 rows, and the promise itself: free device memory is the same
+    before and after the calls (the first call on the device has been made by then)."""
+    cfg = SamplerConfig.make(temperature=0.8, top_p=0.9, top_k=33, presence=0.2, frequency=0.3, repetition=1.05)
+    cases = [random_workload(12, 30_000, 500, [cfg], 81, quantize=0.25, specials=2),
+             random_workload(9, 20_001, 300, [cfg], 82, quantize=0.5, dtype=torch.bfloat16)]
+    warm = cases[0].to("cuda")
+    assert call_static(library, warm, fresh_outputs(warm.rows))[0] == FG_OK  # first call: symbol lookup
+    torch.cuda.synchronize()
+    stream = torch.cuda.current_stream().cuda_stream
+    for w in cases:
+        want = run_oracle(w)
+        on_gpu = w.to("cuda")
+        out = fresh_outputs(w.rows)
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]
+        for _ in range(2):
+            status, message = call_static(library, on_gpu, out, stream)
+            assert status == FG_OK, message
+        torch.cuda.synchronize()
+        assert torch.cuda.mem_get_info()[0] == free_before, "the entry that allocates nothing allocated"
+        assert_rows_equal(_Result(out, 0), want, f"static entry, {w.logits.dtype}")
+
+
 def test_static_scratch_entry_rejects_what_does_not_fit(library):
     cfg = SamplerConfig.make()
     w = synth.Workload("tiny", torch.zeros(2, 64, device="cuda"), [cfg], torch.zeros(2, device="cuda"),
@@ -79,11 +115,9 @@ def test_static_scratch_entry_rejects_what_does_not_fit(library):
     assert call_static(library, w, out)[0] == FG_OK
     torch.cuda.synchronize()
     # more rows than the built-in scratch can track: a clear refusal, nothing launched
-    huge = synth.Workload("huge", torch.zeros(2, 64, device="cuda").expand(2, 64), [cfg],
-                          torch.zeros(2, device="cuda"), None, None, 0)
     cfgs = config_array([cfg])
     args = SampleArgs()
-    args.logits = huge.logits.data_ptr()
+    args.logits = w.logits.data_ptr()
     args.dtype = FG_CUDA_F32
     args.rows, args.vocab, args.row_stride = 1_200_000, 64, 0
     args.config_count = 1
@@ -95,3 +129,20 @@ def test_static_scratch_entry_rejects_what_does_not_fit(library):
     args.row_stride = 64  # now well-formed, but 1.2 M rows need more than 4 MiB of counters
     status = library.fg_cuda_sample_batch_static(0, None, byref(args), byref(err))
     assert status == FG_ERR_LIMIT and "scratch" in err.text()
+    # sizes whose history structure forces several CTAs per row while the hand-off of that many
+    # does not fit the scratch: the entry must say so and return (it used to replan forever).
+    # Only the arguments are read: nothing is launched, so the pointers may be small buffers.
+    penalised = config_array([SamplerConfig.make(temperature=0.9, top_p=0.9, top_k=20, frequency=0.5)])
+    args.rows, args.vocab, args.row_stride = 2100, 151_936, 151_936
+    args.history_max = 262_144
+    tokens = torch.zeros(8, dtype=torch.int32, device="cuda")
+    offsets = torch.zeros(8, dtype=torch.int64, device="cuda")
+    args.history_tokens, args.history_offsets = tokens.data_ptr(), offsets.data_ptr()
+    args.configs = ctypes.cast(penalised, POINTER(SamplerConfig))
+    status = library.fg_cuda_sample_batch_static(0, None, byref(args), byref(err))
+    assert status == FG_ERR_LIMIT and "fits both" in err.text()
+    # rows without a top-k cut are offered by the context entry only, and the text says so
+    w5 = synth.Workload("nucleus", torch.zeros(2, 64, device="cuda"), [SamplerConfig.make(1.0, 0.9, 0)],
+                        torch.zeros(2, device="cuda"), None, None, 0, allow_no_topk=True)
+    status, message = call_static(library, w5, fresh_outputs(2), flags=2)
+    assert status == FG_ERR_UNAVAILABLE and "fg_cuda_sample_batch" in message
