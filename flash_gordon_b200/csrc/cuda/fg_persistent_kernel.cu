@@ -57,7 +57,10 @@ constexpr int kStages = FGK_RING_STAGES;        // tiles in flight per consumer 
 #endif
 constexpr uint32_t kTileLogits = FGK_RING_TILE_LOGITS;  // logits per tile: at most 64 per lane, a bit each in a mask
 constexpr uint32_t kStageBytes = kTileLogits * 4;  // a stage holds a tile of the widest type
-constexpr int kListCap = 256;                   // entries of one warp's candidate list
+#ifndef FGK_RING_LIST_CAP
+#define FGK_RING_LIST_CAP 256
+#endif
+constexpr int kListCap = FGK_RING_LIST_CAP;     // entries of one warp's candidate list (a multiple of 32, > 64)
 constexpr int kListWords = kListCap / 32;
 constexpr int kBlock = (kWarps + kHistoryWarps + kClosers) * 32;
 constexpr uint32_t kDefaultPolls = 1u << 20;

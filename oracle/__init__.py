@@ -44,7 +44,8 @@ class OracleState(Structure):
 
 class OracleCandidates(Structure):
     _fields_ = [("count", c_uint32), ("ids", c_uint32 * 64), ("scores", c_float * 64),
-                ("raw_probability", c_double * 64), ("tempered_probability", c_double * 64)]
+                ("raw_probability", c_double * 64), ("tempered_probability", c_double * 64),
+                ("nucleus", c_uint32), ("edge_margin", c_double)]
 
 
 _handles: dict[str, ctypes.CDLL] = {}

@@ -59,6 +59,12 @@ typedef struct fgo_candidates {
     float scores[64];
     double raw_probability[64];
     double tempered_probability[64];
+    /* rows without a top-k cut only: how many candidates the nucleus kept, and the smallest
+     * distance (in units of the total mass) of top_p and of the draw from an edge of the
+     * cumulative distribution -- a result can depend on the summation order only when this
+     * is within rounding of zero */
+    uint32_t nucleus;
+    double edge_margin;
 } fgo_candidates;
 
 /* The reference's select generalised to any candidate count and to

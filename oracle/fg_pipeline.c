@@ -459,8 +459,15 @@ fg_status fgo_sample_row(float *logits, uint32_t vocab, const uint32_t *history,
 
     if (config->top_k == 0u) {
         /* Generalisation: no top-k cut, every finite logit is a candidate. */
-        return fgo_select_general(config, true, logits, iota, vocab, uniform, token, logit, NULL,
-                                  NULL, err);
+        uint32_t nucleus = 0;
+        double margin = INFINITY;
+        const fg_status status = fgo_select_general(config, true, logits, iota, vocab, uniform, token,
+                                                    logit, &nucleus, &margin, err);
+        if (candidates) {  /* (no candidate dump beyond 64; the nucleus size and the edge margin) */
+            candidates->nucleus = nucleus;
+            candidates->edge_margin = margin;
+        }
+        return status;
     }
 
     /* output.c:681-700: tile top-k cascade until at most k entries remain. */

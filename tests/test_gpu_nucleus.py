@@ -24,6 +24,45 @@ def test_config5_reduced_rows(context):
     assert (sizes > 20_000).all(), sizes  # near-flat logits: the nucleus spans tens of thousands
 
 
+def test_config5_a_wave_of_rows_with_their_edge_margins(context, capsys):
+    """More rows than the GPU has SMs (the kernel is one CTA per SM), full vocabulary, the
+    benchmark's 32,768-token histories.  The oracle also reports, per row, how far top_p and
+    the draw lie from the nearest edge of the cumulative distribution (in units of the total
+    mass): ids can only differ where that is within the rounding of a sum -- about 1e-12 for
+    the 2^-40 fixed point here, 1e-16 per term for the oracle's doubles -- so the smallest
+    margin of the run is printed and must be far above it."""
+    w = synth.config5(rows=160)
+    expected = run_oracle(w, want_candidates=True)
+    assert expected[0] == FG_OK
+    margins = np.array([c.edge_margin for c in expected[4]])
+    sizes = np.array([c.nucleus for c in expected[4]])
+    with capsys.disabled():
+        print(f"\nconfig5, {w.rows} rows: smallest edge margin {margins.min():.3e} (median {np.median(margins):.3e}), "
+              f"nucleus {sizes.min()}..{sizes.max()} tokens")
+    assert margins.min() > 1e-10
+    result = run_gpu(context, w, debug=True)
+    assert_rows_equal(result, expected, "config5, 160 rows")
+    assert np.array_equal(as_u32(result.debug["count"]), sizes)
+
+
+def test_on_an_edge_the_pick_is_the_oracle_s_or_its_neighbour(context):
+    """3000 equal logits and top_p = 0.75: the cut falls exactly on an edge of the cumulative
+    distribution (2250 / 3000).  The oracle's running sum of 1/3000 in doubles and an exact
+    sum may part ways there by one candidate, and that is all they may part by."""
+    vocab = 3000
+    logits = torch.full((3, vocab), 0.5)
+    cfg = SamplerConfig.make(temperature=1.0, top_p=0.75, top_k=0)
+    uniforms = torch.tensor([0.99999994, 0.5, 0.0])
+    w = synth.Workload("edge", logits, [cfg], uniforms, None, None, 0, allow_no_topk=True)
+    expected = run_oracle(w, want_candidates=True)
+    assert min(c.edge_margin for c in expected[4]) < 1e-12   # it is on the edge
+    result = run_gpu(context, w)
+    assert result.status == FG_OK
+    got = as_u32(result.tokens).astype(np.int64)
+    assert (np.abs(got - expected[1].astype(np.int64)) <= 1).all(), (got, expected[1])
+    assert got[2] == 0 and abs(int(got[0]) - 2249) <= 1
+
+
 @pytest.mark.parametrize("temperature,top_p", [(1.0, 0.9), (0.7, 0.5), (1.2, 0.99), (2.0, 1.0), (0.3, 0.05)])
 def test_random_rows_with_ties_and_specials(context, temperature, top_p):
     cfg = SamplerConfig.make(temperature=temperature, top_p=top_p, top_k=0, presence=0.4, frequency=0.3,
