@@ -161,6 +161,7 @@ def load_library() -> ctypes.CDLL:
         "fg_dist_rank": (u32, [P]),
         "fg_dist_shard_span": (None, [u32, u32, u32, POINTER(u32), POINTER(u32)]),
         "fg_dist_sample_vocab_sharded": (c_int, [P, POINTER(SampleArgs), u32, u32, E]),
+        "fg_dist_sample_vocab_sharded_fused": (c_int, [P, POINTER(SampleArgs), u32, u32, E]),
         "fg_dist_gather_rows": (c_int, [P, P, P, P, u32, P, P, P, E]),
         "fg_cuda_output_executor_create": (c_int, [P, u32, u32, u32, POINTER(P), E]),
         "fg_cuda_output_executor_destroy": (None, [P]),

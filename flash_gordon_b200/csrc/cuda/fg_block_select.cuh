@@ -169,6 +169,23 @@ __device__ void sort_candidates(const CandidateBuffer<CAP> &buf, FinishBuffer &f
     Bar::sync();
 }
 
+// The fused exchange of the vocabulary-sharded mode, device side (layout: fg_kernels.h).
+struct PushTargets {
+    unsigned char *window[16];
+    uint32_t ranks, rank, half, pair_capacity, row_capacity;
+
+    // where this rank's pair i of `row` lands in rank t's window
+    __device__ __forceinline__ uint2 *pair(uint32_t t, uint32_t row, uint32_t k, uint32_t i) const {
+        uint2 *pairs = reinterpret_cast<uint2 *>(window[t]);
+        return pairs + ((size_t)half * ranks + rank) * pair_capacity + (size_t)row * k + i;
+    }
+    __device__ __forceinline__ uint32_t *arrived(uint32_t t, uint32_t row) const {
+        uint32_t *counters = reinterpret_cast<uint32_t *>(
+            window[t] + (size_t)2 * ranks * pair_capacity * sizeof(uint2));
+        return counters + (size_t)half * row_capacity + row;
+    }
+};
+
 struct SelectOutput {
     uint32_t *tokens;
     float *token_logits;

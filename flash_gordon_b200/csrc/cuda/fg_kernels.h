@@ -49,6 +49,22 @@ typedef struct fgk_select_output {
     double *dbg_tempered;
 } fgk_select_output;
 
+/* ---- the fused exchange of the vocabulary-sharded mode ----
+ * Instead of leaving its candidates in local memory for an all-gather, a shard kernel stores
+ * its block of every row -- shard_k (value, id) pairs -- straight into the window of every
+ * rank (its own included) over NVLink, then adds one to that row's arrival counter there.
+ * A window is laid out  pairs[2][ranks][pair_capacity]  then  arrived[2][row_capacity]
+ * (two halves, used by alternate calls); the merge kernel of a rank reads only its own
+ * window, after the row's counter says that every rank's block has landed.  Plain stores
+ * and system-scope atomics on peer pointers: no multicast, no TMA. */
+typedef struct fgk_push {
+    void *window[16];        /* every rank's window as mapped into this process; NULL when off */
+    uint32_t ranks, rank;
+    uint32_t half;           /* which half of the windows this call uses */
+    uint32_t pair_capacity;  /* pairs per (half, rank) */
+    uint32_t row_capacity;
+} fgk_push;
+
 /* ---- streaming select (fg_stream_kernels.cu) ---- */
 typedef struct fgk_stream_launch {
     const void *logits;
@@ -68,6 +84,7 @@ typedef struct fgk_stream_launch {
     float *shard_scores;
     uint32_t *shard_ids;
     uint32_t shard_stride; /* elements between consecutive candidates: 0 or 1 separate arrays, 2 (value, id) pairs */
+    fgk_push push;         /* ranks != 0: the shard's candidates go to the ranks' windows instead */
     float *part_scores;
     uint32_t *part_ids;
     void *part_meta;
@@ -122,6 +139,13 @@ typedef struct fgk_merge_launch {
     const uint32_t *ids;
     uint32_t rows, shards, k_shard;
     uint32_t stride; /* elements between consecutive candidates: 0 or 1 separate arrays, 2 (value, id) pairs */
+    uint64_t shard_pitch; /* candidates between consecutive shards' blocks (0: rows * k_shard) */
+    /* fused exchange: row r may be read once arrived[r] >= arrival_target (NULL: at once), and
+     * the kernel then sets the counter back to zero; the wait gives up after wait_polls polls
+     * (0: about two seconds) and fails the row */
+    uint32_t *arrived;
+    uint32_t arrival_target;
+    uint32_t wait_polls;
     uint32_t check_spans;
     uint32_t span_first[16], span_width[16];
     const void *configs_device;
@@ -178,6 +202,11 @@ void fgk_nccl_abort(void *comm);
 void fgk_nccl_destroy(void *comm);
 /* cudaStreamSynchronize with a deadline: 0, a cudaError_t, or FGK_NCCL_TIMEOUT */
 int fgk_stream_wait_deadline(void *stream, uint32_t timeout_ms);
+/* device memory of another process on this machine (CUDA IPC): 64-byte handles */
+#define FGK_IPC_HANDLE_BYTES 64
+int fgk_ipc_handle(void *device_pointer, void *handle64);
+int fgk_ipc_open(const void *handle64, void **device_pointer);
+int fgk_ipc_close(void *device_pointer);
 
 /* ---- device operators (fg_ops_kernels.cu) ---- */
 int fgk_launch_apply_penalties(float *logits, const uint32_t *counts, uint32_t values,

@@ -148,3 +148,16 @@ extern "C" int fgk_stream_wait_deadline(void *stream, uint32_t timeout_ms) {
         nap();
     }
 }
+
+extern "C" int fgk_ipc_handle(void *device_pointer, void *handle64) {
+    static_assert(sizeof(cudaIpcMemHandle_t) == FGK_IPC_HANDLE_BYTES, "IPC handle size");
+    return (int)cudaIpcGetMemHandle(static_cast<cudaIpcMemHandle_t *>(handle64), device_pointer);
+}
+
+extern "C" int fgk_ipc_open(const void *handle64, void **device_pointer) {
+    cudaIpcMemHandle_t handle;
+    memcpy(&handle, handle64, sizeof(handle));
+    return (int)cudaIpcOpenMemHandle(device_pointer, handle, cudaIpcMemLazyEnablePeerAccess);
+}
+
+extern "C" int fgk_ipc_close(void *device_pointer) { return (int)cudaIpcCloseMemHandle(device_pointer); }

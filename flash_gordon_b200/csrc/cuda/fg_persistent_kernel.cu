@@ -63,8 +63,8 @@ constexpr uint32_t kStageBytes = kTileLogits * 4;  // a stage holds a tile of th
 constexpr int kListCap = FGK_RING_LIST_CAP;     // entries of one warp's candidate list (a multiple of 32, > 64)
 constexpr int kListWords = kListCap / 32;
 constexpr int kBlock = (kWarps + kHistoryWarps + kClosers) * 32;
-constexpr uint32_t kDefaultPolls = 1u << 20;
-constexpr uint32_t kNapNanoseconds = 2000;      // longest sleep inside one poll of an mbarrier
+constexpr uint32_t kDefaultPolls = 1u << 21;    // polls before a wait gives up: a second or two
+constexpr uint32_t kNapNanoseconds = 400;       // sleep between two polls of a wait that may be long
 constexpr uint32_t kHugeBits = 0x6b000000u;     // |x| >= 2^87: a repetition factor <= 2^40 may reach inf
 constexpr uint32_t kSharedLimit = 227u * 1024u; // shared memory one CTA may ask for
 
@@ -117,7 +117,7 @@ struct Params {
     const uint64_t *history_offsets;
     uint32_t history_max;
     uint32_t bitmap_words;          // 0: the batch has no history
-    uint32_t bitmap_buffers;        // 2: the next row's bitmap is built ahead; 1: no room for that
+    uint32_t bitmap_buffers;        // 3 or 2: the next rows' bitmaps are built ahead; 1: no room for that
     const SamplerConfig *configs;   // device copy when config_count > 1
     SamplerConfig config0;
     uint32_t config_count;
@@ -126,6 +126,7 @@ struct Params {
     float *shard_scores;
     uint32_t *shard_ids;
     uint32_t shard_stride;          // elements between consecutive candidates (2: interleaved pairs)
+    PushTargets push;               // ranks != 0: candidates go straight to every rank's window
     // Work is dealt out in 4 KB tiles: CTA c takes tiles [c * tiles_per_cta, (c + 1) *
     // tiles_per_cta) of the batch's tile sequence (row after row), so a row may be shared
     // by several CTAs.  Each leaves its part's k best in `parts`; the last to finish
@@ -209,6 +210,7 @@ struct alignas(16) Lists {
     unsigned long long bound;               // the admission bound T (only ever rises)
     uint32_t first_key;                     // smallest of the warps' first-tile keys
     uint32_t first_count;                   // warps that have published theirs
+    uint32_t warp_kth[kWarps];              // each warp's j-th best exact score so far, as a key (0: none yet)
     uint32_t bad_history;
     uint32_t pad_;
 };
@@ -220,8 +222,9 @@ struct Shared {
     alignas(8) uint64_t full[kWarps][kStages];  // "the tile has landed"
     alignas(8) uint64_t ready[2];            // "every consumer warp is through with the unit"
     alignas(8) uint64_t vacant[2];           // "the closing warp is done with the lists"
-    alignas(8) uint64_t bitmap_ready[2];     // "the unit's history bitmap is complete"
-    uint32_t history_bad[2];                 // status a broken history earns the unit, by bitmap buffer
+    alignas(8) uint64_t bitmap_ready[3];     // "the unit's history bitmap is complete"
+    alignas(8) uint64_t bitmap_free[3];      // "every consumer warp is through with the bitmap buffer"
+    uint32_t history_bad[3];                 // status a broken history earns the unit, by bitmap buffer
     uint32_t ring_error;                     // a bounded wait ran out
 };
 
@@ -250,14 +253,15 @@ __device__ __forceinline__ void poke(uint32_t *word, uint32_t value) {
     *reinterpret_cast<volatile uint32_t *>(word) = value;
 }
 
-// Waits for a phase of an mbarrier, at most `polls` polls that may sleep 2 us each, and
+// Waits for a phase of an mbarrier, at most `polls` polls with a short sleep between them, and
 // not at all once another wait of the CTA has run out.  A wait that runs out raises
 // ring_error: the CTA's rows then end with FG_ERR_LIMIT and every later wait returns at
 // once, so the kernel always comes back.
 __device__ __forceinline__ bool bounded_wait(Shared &sh, uint64_t *barrier, uint32_t parity, uint32_t polls) {
     for (uint32_t i = 0; i < polls; i++) {
-        if (mbarrier_try_wait_sleeping(barrier, parity, kNapNanoseconds)) return true;
+        if (mbarrier_try_wait(barrier, parity)) return true;
         if (peek(&sh.ring_error) != 0) return false;
+        __nanosleep(kNapNanoseconds);  // (the warps that stream need the issue slots)
     }
     poke(&sh.ring_error, 1u);
     return false;
@@ -598,7 +602,7 @@ __device__ __noinline__ uint64_t first_bound(Shared &sh, Lists &L, const Row r, 
             poke(&sh.ring_error, 1u);
             break;
         }
-        __nanosleep(32);
+        __nanosleep(100);
     }
     __threadfence_block();
     return (uint64_t)peek(&L.first_key) << 32;
@@ -646,16 +650,24 @@ __device__ __noinline__ uint32_t refine(Lists &L, const Row r, const uint32_t *b
 // and round, so the list's length lives in registers and no atomic is needed.  A list that
 // cannot take a round is refined, and cut to its k best if that was not enough, which also
 // lifts the bound.  All lanes call; returns the bound the warp knows afterwards.
+// What a consumer warp knows about its list and the bound; handed to and from collect() by
+// value, so that it stays in registers.
+struct Progress {
+    uint64_t bound;
+    uint32_t count, refined;  // entries on the list; how many of them refine() has seen
+};
+
 template <typename T, bool kGreedy>
-__device__ __noinline__ uint64_t collect(Lists &L, const Row r, const uint32_t *bitmap, const unsigned char *tile,
+__device__ __noinline__ Progress collect(Lists &L, const Row r, const uint32_t *bitmap, const unsigned char *tile,
                                          uint32_t column0, uint32_t valid_vectors, uint32_t w, uint32_t hot,
-                                         uint64_t bound, uint32_t *refined_io, uint32_t *count_io) {
+                                         const Progress in) {
     using V = Lanes<T>;
     constexpr int kPer = V::kPer;
     const uint32_t lane = lane_id();
     const uint4 *vectors = reinterpret_cast<const uint4 *>(tile);
+    uint64_t bound = in.bound;
     const float tau = key_to_float((uint32_t)(bound >> 32));
-    uint32_t count = *count_io, refined = *refined_io;
+    uint32_t count = in.count, refined = in.refined;
     uint64_t take = 0;  // bit u * kPer + j: element j of this lane's vector u
     for (uint32_t rest = hot; rest != 0; rest &= rest - 1) {  // bit u: vector u of this lane is worth a look
         {
@@ -699,9 +711,46 @@ __device__ __noinline__ uint64_t collect(Lists &L, const Row r, const uint32_t *
         }
         count += round;
     }
-    *count_io = count;
-    *refined_io = refined;
-    return bound;
+    Progress out;
+    out.bound = bound;
+    out.count = count;
+    out.refined = refined;
+    return out;
+}
+
+// The j-th largest exact score on the warp's list, as a key (0 when it holds fewer than j
+// exact entries): j rounds of "the largest that is left".  Every warp publishes its own; the
+// smallest over the warps of a unit has j entries at or above it in every one of them, k in
+// all, and so bounds the row -- more tightly the further the row has been read.
+__device__ __noinline__ uint32_t jth_best(const Lists &L, uint32_t w, uint32_t count, uint32_t j) {
+    const uint32_t lane = lane_id();
+    uint32_t key[kListWords];
+#pragma unroll
+    for (int q = 0; q < kListWords; q++) {
+        const uint32_t i = q * 32 + lane;
+        const bool exact = i < count && ((L.deferred[w][q] >> lane) & 1u) == 0 && L.id[w][i] != kPaddingId;
+        key[q] = exact ? float_key(L.score[w][i]) : 0u;
+    }
+    uint32_t found = 0;
+    for (uint32_t round = 0; round < j; round++) {
+        uint32_t mine = 0;
+#pragma unroll
+        for (int q = 0; q < kListWords; q++) mine = max(mine, key[q]);
+        found = __reduce_max_sync(kFullMask, mine);
+        if (found == 0) break;
+        const uint32_t owners = __ballot_sync(kFullMask, mine == found);
+        if ((int)lane == __ffs(owners) - 1) {
+            bool gone = false;
+#pragma unroll
+            for (int q = 0; q < kListWords; q++) {
+                if (!gone && key[q] == found) {
+                    key[q] = 0;
+                    gone = true;
+                }
+            }
+        }
+    }
+    return found;
 }
 
 // The row as the warps see it; *bad_history is the status a broken history earns the
@@ -799,7 +848,7 @@ struct Feeder {
 // list.  Per tile and lane: the 128-bit vectors of the tile, a maximum of each, the largest of
 // those against the bound's score.  Returns the number of tiles it has looked at.
 template <typename T, bool kGreedy>
-__device__ __noinline__ uint32_t consume_unit(const Params &p, Shared &sh, Lists &L, const Row r, const Unit u,
+__device__ __forceinline__ uint32_t consume_unit(const Params &p, Shared &sh, Lists &L, const Row r, const Unit u,
                                               const uint32_t *bitmap, unsigned char *stages, Feeder &feeder,
                                               uint32_t consumed, uint32_t w, uint32_t tiles, uint32_t row_bytes,
                                               bool shard_mode, uint64_t policy, uint32_t polls
@@ -814,8 +863,10 @@ __device__ __noinline__ uint32_t consume_unit(const Params &p, Shared &sh, Lists
     const uint32_t whole = tile_bytes<T>() / 16u;
     const uint32_t last_vectors = (row_bytes - (tiles - 1) * tile_bytes<T>()) / 16u;
     const uint32_t participants = min((uint32_t)kWarps, u.end - u.first);
+    const uint32_t per_warp = (r.k + participants - 1) / participants;  // j of jth_best()
     uint64_t bound = 0;
     uint32_t count = 0, refined = 0;  // entries on this warp's list; how many of them refine() has seen
+    uint32_t done = 0, published = 0; // tiles of this unit so far; the j-th best this warp has published
     bool first = true;
     for (uint32_t t = u.first + w; t < u.end; t += kWarps) {
         const uint32_t stage = consumed % kStages;
@@ -863,18 +914,36 @@ __device__ __noinline__ uint32_t consume_unit(const Params &p, Shared &sh, Lists
             }
         }
         if (__any_sync(kFullMask, hot != 0)) {
-            bound = collect<T, kGreedy>(L, r, bitmap, tile, column0, valid_vectors, w, hot, bound, &refined, &count);
-            if (r.k == 1u && count != refined) {
-                // one candidate bounds a row that wants one: the best exact value so far is
-                // the bound, and most later tiles are then not worth a second look
-                uint64_t best = 0;
-                count = refine<kGreedy>(L, r, bitmap, w, refined, count, bound, &best);
+            Progress state;
+            state.bound = bound;
+            state.count = count;
+            state.refined = refined;
+            state = collect<T, kGreedy>(L, r, bitmap, tile, column0, valid_vectors, w, hot, state);
+            bound = state.bound;
+            count = state.count;
+            refined = state.refined;
+        }
+        // The bound tightens as the row is read: after its 1st, 2nd, 4th, 8th ... tile (always
+        // when the row wants one candidate) the warp gives its new entries their exact values
+        // and publishes its j-th best; the smallest published by the unit's warps bounds k
+        // elements.  Nobody waits: a warp that has published nothing yet keeps it at zero.
+        done++;
+        if (per_warp <= 32u && count != 0 &&
+            (r.k == 1u ? count != refined : (done & (done - 1u)) == 0u)) {
+            if (count != refined) {
+                count = refine<kGreedy>(L, r, bitmap, w, refined, count, bound, nullptr);
                 refined = count;
-                if (best > bound) {
-                    bound = best;
-                    if (lane == 0) atomicMax(&L.bound, (unsigned long long)best);
-                }
             }
+            const uint32_t mine = jth_best(L, w, count, per_warp);
+            if (mine > published) {
+                published = mine;
+                if (lane == 0) poke(&L.warp_kth[w], mine);
+            }
+        }
+        if (published != 0) {
+            const uint32_t theirs = lane < participants ? peek(&L.warp_kth[lane]) : 0xffffffffu;
+            const uint64_t pooled = (uint64_t)__reduce_min_sync(kFullMask, theirs) << 32;
+            bound = max(bound, pooled);
         }
         __syncwarp();
         FGK_PTICK(3);
@@ -1123,8 +1192,19 @@ __device__ __noinline__ void close_unit(Shared &sh, uint32_t closer, Lists &L, c
                 score = __uint_as_float(wild_bits);
                 id = wild_id;
             }
-            p.shard_scores[at] = score;
-            p.shard_ids[at] = id;
+            if (p.push.ranks != 0) {
+                // the fused exchange: the block lands in every rank's window, this one's too
+                for (uint32_t t = 0; t < p.push.ranks; t++)
+                    *p.push.pair(t, row, r.k, i) = make_uint2(__float_as_uint(score), id);
+            } else {
+                p.shard_scores[at] = score;
+                p.shard_ids[at] = id;
+            }
+        }
+        if (p.push.ranks != 0) {
+            __threadfence_system();  // the pairs are visible on the peers before the arrivals are
+            __syncwarp();
+            if (lane < p.push.ranks) atomicAdd_system(p.push.arrived(lane, row), 1u);
         }
         if (lane == 0) {
             p.out.row_status[row] = bad_history;
@@ -1189,15 +1269,19 @@ __global__ void __launch_bounds__(kBlock, 1) persistent_select_kernel(const __gr
     if (tid == 0) {
         for (int w = 0; w < kWarps; w++)
             for (int s = 0; s < kStages; s++) mbarrier_init(&sh.full[w][s], 1);
+        for (int b = 0; b < 3; b++) {
+            mbarrier_init(&sh.bitmap_ready[b], kHistoryWarps);
+            mbarrier_init(&sh.bitmap_free[b], kWarps);
+            sh.history_bad[b] = 0;
+        }
         for (int b = 0; b < 2; b++) {
             mbarrier_init(&sh.ready[b], kWarps);
             mbarrier_init(&sh.vacant[b], 1);
-            mbarrier_init(&sh.bitmap_ready[b], kHistoryWarps);
-            sh.history_bad[b] = 0;
             lists[b].bound = 0;
             lists[b].first_key = 0xffffffffu;
             lists[b].first_count = 0;
             lists[b].bad_history = 0;
+            for (int w = 0; w < kWarps; w++) lists[b].warp_kth[w] = 0;
         }
         mbarrier_fence_init();
         sh.ring_error = 0;
@@ -1227,7 +1311,11 @@ __global__ void __launch_bounds__(kBlock, 1) persistent_select_kernel(const __gr
             __syncwarp();
             close_unit(sh, closer, L, p, u, r, cfg, shard_mode, row_status);
             __syncwarp();
-            if (lane == 0) {  // the lists' shared words, clean for the unit after next
+            // the lists' shared words, clean for the unit after next (a warp that is ahead of
+            // the others must not meet what they published for another row)
+            if (lane < (uint32_t)kWarps) L.warp_kth[lane] = 0;
+            __syncwarp();
+            if (lane == 0) {
                 L.bound = 0;
                 L.first_key = 0xffffffffu;
                 L.first_count = 0;
@@ -1254,10 +1342,9 @@ __global__ void __launch_bounds__(kBlock, 1) persistent_select_kernel(const __gr
             uint32_t row_status;
             const Row r = make_row(p, cfg, u.row, shard_mode, &row_status);
             const uint32_t slot = served % buffers;
-            if (served >= buffers) {  // the consumers must be through with the unit that used the buffer
-                const uint32_t before = served - buffers;
-                bounded_wait(sh, &sh.ready[before & 1u], (before >> 1) & 1u, polls);
-            }
+            // the consumers must be through with the unit that used the buffer last (each buffer
+            // has a barrier of its own: one phase per use, however far the consumers have got)
+            if (served >= buffers) bounded_wait(sh, &sh.bitmap_free[slot], (served / buffers - 1u) & 1u, polls);
             if (helper == 0 && lane == 0) sh.history_bad[slot] = 0;
             if (r.seen_any) {
                 uint32_t *bitmap = bitmaps + (size_t)slot * bitmap_stride;
@@ -1352,7 +1439,10 @@ __global__ void __launch_bounds__(kBlock, 1) persistent_select_kernel(const __gr
                                                      row_bytes, shard_mode, policy, polls FGK_CLOCK_ARGS);
         __threadfence_block();
         __syncwarp();
-        if (lane == 0) mbarrier_arrive(&sh.ready[b]);
+        if (lane == 0) {
+            mbarrier_arrive(&sh.ready[b]);
+            mbarrier_arrive(&sh.bitmap_free[slot]);
+        }
         served++;
         FGK_PTICK(5);
     }
@@ -1364,8 +1454,10 @@ __global__ void __launch_bounds__(kBlock, 1) persistent_select_kernel(const __gr
     // CTA's shared memory: see them land, bounded, before the CTA may go away
     while (consumed < feeder.issued) {
         const uint32_t stage = consumed % kStages;
-        for (uint32_t i = 0; i < polls; i++)
-            if (mbarrier_try_wait_sleeping(&sh.full[w][stage], (consumed / kStages) & 1u, kNapNanoseconds)) break;
+        for (uint32_t i = 0; i < polls; i++) {
+            if (mbarrier_try_wait(&sh.full[w][stage], (consumed / kStages) & 1u)) break;
+            __nanosleep(kNapNanoseconds);
+        }
         consumed++;
     }
 }
@@ -1410,6 +1502,12 @@ static persist::Params to_persist_params(const fgk_stream_launch *l) {
     p.shard_scores = l->shard_scores;
     p.shard_ids = l->shard_ids;
     p.shard_stride = l->shard_stride ? l->shard_stride : 1u;
+    for (int t = 0; t < 16; t++) p.push.window[t] = static_cast<unsigned char *>(l->push.window[t]);
+    p.push.ranks = l->push.ranks;
+    p.push.rank = l->push.rank;
+    p.push.half = l->push.half;
+    p.push.pair_capacity = l->push.pair_capacity;
+    p.push.row_capacity = l->push.row_capacity;
     p.tiles_per_cta = l->split_len;  /* reused: tiles per CTA */
     p.max_parts = l->splits;         /* reused: most CTAs per row */
     p.part_scores = l->part_scores;
@@ -1436,14 +1534,14 @@ static persist::Params to_persist_params(const fgk_stream_launch *l) {
 }
 
 // Dynamic shared memory for a history bitmap of `bitmap_words` words: the stages, the two
-// sets of lists and two bitmap buffers -- or one, when two do not fit.  0: not even one.
+// sets of lists and as many bitmap buffers as fit, three at most.  0: not even one.
 extern "C" uint64_t fgk_persistent_dynamic_smem(uint32_t bitmap_words, uint32_t *bitmap_buffers) {
     const uint64_t fixed = (uint64_t)persist::kWarps * persist::kStages * persist::kStageBytes +
                            2u * sizeof(persist::Lists);
     const uint64_t bitmap = (((uint64_t)bitmap_words + 3u) / 4u) * 16u;
     const uint64_t room = persist::kSharedLimit - sizeof(persist::Shared) - 256u;
-    uint32_t buffers = 2;
-    if (fixed + 2u * bitmap > room) buffers = 1;
+    uint32_t buffers = 3;
+    while (buffers > 1u && fixed + buffers * bitmap > room) buffers--;
     if (fixed + buffers * bitmap > room) return 0;
     if (bitmap_buffers) *bitmap_buffers = buffers;
     return fixed + buffers * bitmap;

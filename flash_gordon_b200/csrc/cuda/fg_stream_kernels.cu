@@ -54,6 +54,7 @@ struct StreamParams {
     float *shard_scores;
     uint32_t *shard_ids;
     uint32_t shard_stride;          // elements between consecutive candidates (2: interleaved pairs)
+    PushTargets push;               // ranks != 0: candidates go straight to every rank's window
     float *part_scores;             // [rows][splits][64]
     uint32_t *part_ids;
     PartMeta *part_meta;            // [rows][splits]
@@ -643,8 +644,19 @@ __device__ __noinline__ void finish_split(const StreamParams &p, StreamShared &s
                 score = __uint_as_float(wild_bits);
                 id = wild_id;
             }
-            p.shard_scores[at] = score;
-            p.shard_ids[at] = id;
+            if (p.push.ranks != 0) {
+                // the fused exchange: the block lands in every rank's window, this one's too
+                for (uint32_t t = 0; t < p.push.ranks; t++)
+                    *p.push.pair(t, row, k, tid) = make_uint2(__float_as_uint(score), id);
+            } else {
+                p.shard_scores[at] = score;
+                p.shard_ids[at] = id;
+            }
+        }
+        if (p.push.ranks != 0) {
+            __threadfence_system();  // the pairs are visible on the peers before the arrivals are
+            __syncthreads();
+            if (tid < p.push.ranks) atomicAdd_system(p.push.arrived(tid, row), 1u);
         }
         if (tid == 0) {
             p.out.row_status[row] = bad_history;
@@ -993,6 +1005,9 @@ struct MergeParams {
     const uint32_t *ids;
     uint32_t rows, shards, k_shard;
     uint32_t stride;                // elements between consecutive candidates (2: interleaved (value, id) pairs)
+    uint64_t shard_pitch;           // candidates between consecutive shards' blocks
+    uint32_t *arrived;              // fused exchange: per-row arrival counters of this rank's window
+    uint32_t arrival_target, wait_polls;
     uint32_t check_spans;           // sharded merge: range-check ids, a NaN/Inf finalist is an error
     uint32_t span_first[16], span_width[16];
     const SamplerConfig *configs;
@@ -1013,12 +1028,37 @@ __global__ void __launch_bounds__(kThreads) merge_select_kernel(const MergeParam
         sh.bad_history = 0;
         sh.wild_id = kPaddingId;
         sh.wild_bits = 0;
+        sh.is_last = 1;
+        if (p.arrived != nullptr) {
+            // The fused exchange: every rank's shard kernel stores its block of this row into
+            // this rank's window and then counts itself in.  Wait for all of them -- bounded:
+            // a rank that never comes fails the row instead of hanging the GPU.
+            const uint32_t polls = p.wait_polls ? p.wait_polls : (1u << 21);
+            uint32_t seen = 0;
+            for (uint32_t i = 0; i < polls; i++) {
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(p.arrived + row) : "memory");
+                if (seen >= p.arrival_target) break;
+                __nanosleep(1000);
+            }
+            if (seen < p.arrival_target) sh.is_last = 0;
+            // all are in: the counter starts from zero again for the call after next, which is
+            // the earliest any rank can store into this half of the window again
+            else p.arrived[row] = 0;
+        }
     }
     __syncthreads();
+    if (!sh.is_last) {  // not every rank's candidates came: FG_ERR_LIMIT, as a partial that misses its deadline
+        if (tid == 0) {
+            report_row(p.out, row, kErrLimit, kPaddingId, 0.0f);
+            atomicMin(p.out.first_error + 1, 1ull);
+            if (p.out.dbg_count) p.out.dbg_count[row] = 0;
+        }
+        return;
+    }
     const uint32_t total = p.shards * p.k_shard;  // <= kCandCap, checked by the host
     for (uint32_t i = tid; i < total; i += kThreads) {
         const uint32_t shard = i / p.k_shard, within = i % p.k_shard;
-        const size_t at = (((size_t)shard * p.rows + row) * p.k_shard + within) * p.stride;
+        const size_t at = ((size_t)shard * p.shard_pitch + (size_t)row * p.k_shard + within) * p.stride;
         const float score = p.scores[at];
         const uint32_t id = p.ids[at];
         if (id == kPaddingId && p.check_spans) continue;  // padding of a short shard
@@ -1036,7 +1076,7 @@ __global__ void __launch_bounds__(kThreads) merge_select_kernel(const MergeParam
     if (greedy && sh.wild_id != kPaddingId) {
         for (uint32_t i = tid; i < total; i += kThreads) {
             const uint32_t shard = i / p.k_shard, within = i % p.k_shard;
-            const size_t at = (((size_t)shard * p.rows + row) * p.k_shard + within) * p.stride;
+            const size_t at = ((size_t)shard * p.shard_pitch + (size_t)row * p.k_shard + within) * p.stride;
             if (p.ids[at] == sh.wild_id && is_nonfinite(p.scores[at]))
                 sh.wild_bits = __float_as_uint(p.scores[at]);
         }
@@ -1163,6 +1203,12 @@ static StreamParams to_stream_params(const fgk_stream_launch *l) {
     p.shard_scores = l->shard_scores;
     p.shard_ids = l->shard_ids;
     p.shard_stride = l->shard_stride ? l->shard_stride : 1u;
+    for (int t = 0; t < 16; t++) p.push.window[t] = static_cast<unsigned char *>(l->push.window[t]);
+    p.push.ranks = l->push.ranks;
+    p.push.rank = l->push.rank;
+    p.push.half = l->push.half;
+    p.push.pair_capacity = l->push.pair_capacity;
+    p.push.row_capacity = l->push.row_capacity;
     p.part_scores = l->part_scores;
     p.part_ids = l->part_ids;
     p.part_meta = reinterpret_cast<PartMeta *>(l->part_meta);
@@ -1205,6 +1251,10 @@ extern "C" int fgk_launch_merge_select(const fgk_merge_launch *l, void *stream) 
     p.shards = l->shards;
     p.k_shard = l->k_shard;
     p.stride = l->stride ? l->stride : 1u;
+    p.shard_pitch = l->shard_pitch ? l->shard_pitch : (uint64_t)l->rows * l->k_shard;
+    p.arrived = l->arrived;
+    p.arrival_target = l->arrival_target;
+    p.wait_polls = l->wait_polls;
     p.check_spans = l->check_spans;
     for (int i = 0; i < 16; i++) {
         p.span_first[i] = l->span_first[i];

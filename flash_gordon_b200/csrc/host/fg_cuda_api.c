@@ -695,6 +695,7 @@ static fg_status run_stream(fg_cuda_context *c, const fg_cuda_sample_args *a,
     l.shard_scores = shard_scores;
     l.shard_ids = shard_ids;
     l.shard_stride = shard_stride;
+    if (c->push) l.push = *c->push;
     l.tickets = c->tickets;
     l.bitmap_words = plan.bitmap_words;
     l.count_capacity = plan.count_capacity;
@@ -895,7 +896,7 @@ fg_status fg_cuda_shard_topk_layout(fg_cuda_context *c, const fg_cuda_sample_arg
     batch_traits traits;
     fg_status status = check_batch(c, a, true, &traits, err);
     if (status != FG_OK) return status;
-    if (k_shard < 1u || k_shard > 64u || !candidate_scores || !candidate_ids ||
+    if (k_shard < 1u || k_shard > 64u || ((!candidate_scores || !candidate_ids) && !c->push) ||
         (uint64_t)vocab_offset + a->vocab > vocab_total) {
         fg_error_set(err, FG_ERR_ARGUMENT, "invalid vocabulary shard arguments");
         return FG_ERR_ARGUMENT;
@@ -924,7 +925,7 @@ fg_status fg_cuda_merge_select_layout(fg_cuda_context *c, const fg_cuda_sample_a
                                       const float *candidate_scores, const uint32_t *candidate_ids,
                                       uint32_t stride, uint32_t shards, uint32_t k_shard,
                                       const uint32_t *shard_first, const uint32_t *shard_width,
-                                      bool keep_errors, fg_error *err) {
+                                      bool keep_errors, const fg_cuda_arrivals *arrivals, fg_error *err) {
     if (!c || !a || !a->rows || !a->configs || (a->config_count != 1u && a->config_count != a->rows) ||
         !a->tokens || !a->token_logits || !a->row_status || !candidate_scores || !candidate_ids ||
         !shards || shards > 16u || k_shard < 1u || k_shard > 64u || !shard_first || !shard_width) {
@@ -964,6 +965,12 @@ fg_status fg_cuda_merge_select_layout(fg_cuda_context *c, const fg_cuda_sample_a
     l.shards = shards;
     l.k_shard = k_shard;
     l.stride = stride;
+    if (arrivals) {
+        l.shard_pitch = arrivals->shard_pitch;
+        l.arrived = arrivals->arrived;
+        l.arrival_target = arrivals->target;
+        l.wait_polls = arrivals->wait_polls;
+    }
     l.check_spans = 1u;
     for (uint32_t s = 0; s < shards; s++) {
         l.span_first[s] = shard_first[s];
@@ -984,7 +991,7 @@ fg_status fg_cuda_merge_select(fg_cuda_context *c, const fg_cuda_sample_args *a,
                                uint32_t shards, uint32_t k_shard, const uint32_t *shard_first,
                                const uint32_t *shard_width, fg_error *err) {
     const fg_status status = fg_cuda_merge_select_layout(c, a, candidate_scores, candidate_ids, 1u, shards,
-                                                         k_shard, shard_first, shard_width, false, err);
+                                                         k_shard, shard_first, shard_width, false, NULL, err);
     if (status != FG_OK || (a->flags & FG_CUDA_SAMPLE_ASYNC)) return status;
     return collect_status(c, err);
 }

@@ -23,6 +23,13 @@ struct fg_dist {
     size_t send_bytes;
     void *gathered;        /* [rank][rows][k] pairs after the exchange */
     size_t gathered_bytes;
+    /* the fused exchange: this rank's window and every rank's, as mapped into this process */
+    void *window;
+    size_t window_bytes;
+    void *peer_window[16];
+    uint32_t pair_capacity, row_capacity;
+    uint32_t calls;        /* fused calls so far: the half alternates */
+    void *handles;         /* device staging for the handle exchange */
 };
 
 static fg_status nccl_status(fg_dist *d, int code, const char *what, fg_error *err) {
@@ -46,6 +53,16 @@ static fg_status nccl_status(fg_dist *d, int code, const char *what, fg_error *e
         return FG_ERR_IO;
     }
     return fg_cuda_fail(err, code, what);
+}
+
+static void close_windows(fg_dist *d) {
+    for (uint32_t r = 0; r < d->ranks; r++) {
+        if (d->peer_window[r] && r != d->rank) fgk_ipc_close(d->peer_window[r]);
+        d->peer_window[r] = NULL;
+    }
+    if (d->window) fgk_free(d->window);
+    d->window = NULL;
+    d->window_bytes = 0;
 }
 
 fg_status fg_dist_unique_id(void *id, fg_error *err) {
@@ -91,6 +108,8 @@ void fg_dist_destroy(fg_dist *d) {
         if (d->comm) fgk_nccl_destroy(d->comm);
         if (d->send) fgk_free(d->send);
         if (d->gathered) fgk_free(d->gathered);
+        close_windows(d);
+        if (d->handles) fgk_free(d->handles);
     }
     free(d);
 }
@@ -151,9 +170,113 @@ fg_status fg_dist_sample_vocab_sharded(fg_dist *d, const fg_cuda_sample_args *a,
     if (status != FG_OK) return status;
     /* 3. span check, merge under (value desc, global id asc), select -- on every rank */
     status = fg_cuda_merge_select_layout(c, a, (const float *)d->gathered, (const uint32_t *)d->gathered + 1,
-                                         2u, d->ranks, k_shard, first, width, true, err);
+                                         2u, d->ranks, k_shard, first, width, true, NULL, err);
     if (status != FG_OK || (a->flags & FG_CUDA_SAMPLE_ASYNC)) return status;
     return finish(d, "vocabulary-sharded sampling", err);
+}
+
+/* Makes sure every rank has a window that takes `rows` rows of k pairs from every rank, and
+ * that this process can store into all of them.  Collective: every rank calls it with the
+ * same sizes (they sample the same rows), so all grow together. */
+static fg_status ensure_windows(fg_dist *d, uint32_t rows, uint32_t k, fg_error *err) {
+    const uint64_t pairs = (uint64_t)rows * k;
+    if (d->window && pairs <= d->pair_capacity && rows <= d->row_capacity) return FG_OK;
+    fg_cuda_context *c = d->context;
+    int e = fgk_stream_synchronize(c->stream);
+    if (e) return fg_cuda_fail(err, e, "draining the stream");
+    close_windows(d);
+    d->pair_capacity = (uint32_t)(pairs + pairs / 4u);
+    d->row_capacity = rows + rows / 4u;
+    const size_t bytes = (size_t)2u * d->ranks * d->pair_capacity * 8u + (size_t)2u * d->row_capacity * 4u;
+    e = fgk_malloc(&d->window, bytes);
+    if (!e) e = fgk_memset_async(d->window, 0, bytes, c->stream);
+    if (!e && !d->handles) e = fgk_malloc(&d->handles, (size_t)(d->ranks + 1u) * FGK_IPC_HANDLE_BYTES);
+    if (e) return fg_cuda_fail(err, e, "allocating the exchange window");
+    d->window_bytes = bytes;
+    d->calls = 0;
+    d->peer_window[d->rank] = d->window;
+    if (d->ranks > 1u) {
+        /* every rank's handle to every rank: one small all-gather through device memory */
+        unsigned char mine[FGK_IPC_HANDLE_BYTES], all[16 * FGK_IPC_HANDLE_BYTES];
+        e = fgk_ipc_handle(d->window, mine);
+        unsigned char *send = (unsigned char *)d->handles + (size_t)d->ranks * FGK_IPC_HANDLE_BYTES;
+        if (!e) e = fgk_copy_to_device_async(send, mine, FGK_IPC_HANDLE_BYTES, c->stream);
+        if (e) return fg_cuda_fail(err, e, "exporting the exchange window");
+        fg_status status = nccl_status(d, fgk_nccl_all_gather(d->comm, send, d->handles, FGK_IPC_HANDLE_BYTES,
+                                                              c->stream, d->timeout_ms),
+                                       "exchanging the window handles", err);
+        if (status != FG_OK) return status;
+        e = fgk_copy_to_host_async(all, d->handles, (size_t)d->ranks * FGK_IPC_HANDLE_BYTES, c->stream);
+        if (e) return fg_cuda_fail(err, e, "reading the window handles");
+        const int waited = fgk_stream_wait_deadline(c->stream, d->timeout_ms);
+        if (waited) return nccl_status(d, waited, "exchanging the window handles", err);
+        for (uint32_t r = 0; r < d->ranks; r++) {
+            if (r == d->rank) continue;
+            e = fgk_ipc_open(all + (size_t)r * FGK_IPC_HANDLE_BYTES, &d->peer_window[r]);
+            if (e) return fg_cuda_fail(err, e, "mapping a peer's exchange window");
+        }
+    } else {
+        e = fgk_stream_synchronize(c->stream);
+        if (e) return fg_cuda_fail(err, e, "clearing the exchange window");
+    }
+    return FG_OK;
+}
+
+fg_status fg_dist_sample_vocab_sharded_fused(fg_dist *d, const fg_cuda_sample_args *a, uint32_t vocab_total,
+                                             uint32_t k_shard, fg_error *err) {
+    if (!d || !a || k_shard < 1u || k_shard > 64u || !a->rows) {
+        fg_error_set(err, FG_ERR_ARGUMENT, "invalid sharded sampling arguments");
+        return FG_ERR_ARGUMENT;
+    }
+    if (!d->comm) {
+        fg_error_set(err, FG_ERR_UNAVAILABLE, "the communicator was aborted after a rank failed to join");
+        return FG_ERR_UNAVAILABLE;
+    }
+    uint32_t first[16], width[16];
+    for (uint32_t s = 0; s < d->ranks; s++) fg_dist_shard_span(vocab_total, d->ranks, s, &first[s], &width[s]);
+    if (a->vocab != width[d->rank]) {
+        fg_error_set(err, FG_ERR_ARGUMENT, "rank %u holds %u columns, its span of %u has %u", d->rank,
+                     a->vocab, vocab_total, width[d->rank]);
+        return FG_ERR_ARGUMENT;
+    }
+    fg_cuda_context *c = d->context;
+    fg_status status = fg_cuda_enter(c, err);
+    if (status == FG_OK) status = ensure_windows(d, a->rows, k_shard, err);
+    if (status != FG_OK) return status;
+    /* Alternate calls use alternate halves of the windows: a rank can be one call ahead of
+     * another (it cannot start the call after, whose merge needs this one's blocks from
+     * everybody), so what it stores never lands on what a slower rank still reads. */
+    const uint32_t half = d->calls & 1u;
+    fgk_push push;
+    memset(&push, 0, sizeof(push));
+    for (uint32_t r = 0; r < d->ranks; r++) push.window[r] = d->peer_window[r];
+    push.ranks = d->ranks;
+    push.rank = d->rank;
+    push.half = half;
+    push.pair_capacity = d->pair_capacity;
+    push.row_capacity = d->row_capacity;
+    /* 1. this rank's columns -> k_shard pairs per row, stored into every rank's window */
+    c->push = &push;
+    status = fg_cuda_shard_topk_layout(c, a, first[d->rank], vocab_total, k_shard, NULL, NULL, 2u, err);
+    c->push = NULL;
+    if (status != FG_OK) return status;
+    d->calls++;
+    /* 2. merge what has landed here: a row is read once all ranks have counted themselves in
+     * (the merge sets the row's counter back to zero) */
+    unsigned char *mine = d->window;
+    const unsigned char *pairs = mine + (size_t)half * d->ranks * d->pair_capacity * 8u;
+    uint32_t *counters = (uint32_t *)(mine + (size_t)2u * d->ranks * d->pair_capacity * 8u) +
+                         (size_t)half * d->row_capacity;
+    fg_cuda_arrivals arrivals = {d->pair_capacity, counters, d->ranks, 0u};
+    status = fg_cuda_merge_select_layout(c, a, (const float *)pairs, (const uint32_t *)pairs + 1, 2u, d->ranks,
+                                         k_shard, first, width, true, &arrivals, err);
+    if (status != FG_OK || (a->flags & FG_CUDA_SAMPLE_ASYNC)) return status;
+    status = finish(d, "vocabulary-sharded sampling (fused exchange)", err);
+    if (status == FG_ERR_LIMIT && d->comm) {  /* a rank never stored its blocks: the counters are out of step for good */
+        fgk_nccl_abort(d->comm);
+        d->comm = NULL;
+    }
+    return status;
 }
 
 fg_status fg_dist_gather_rows(fg_dist *d, const uint32_t *tokens, const float *token_logits,

@@ -25,6 +25,10 @@ struct fg_cuda_context {
     const uint32_t *session_rows;
     uint32_t session_bitmap_words;
 
+    /* Set by the multi-GPU layer around a shard step whose candidates go straight to the
+     * ranks' windows (the fused exchange) instead of to a local buffer. */
+    const fgk_push *push;
+
     /* device scratch, grown on demand and then reused (no allocation on a warm call) */
     void *parts;            /* candidate hand-off between the splits of a row */
     size_t parts_bytes;
@@ -72,11 +76,19 @@ fg_status fg_cuda_shard_topk_layout(fg_cuda_context *context, const fg_cuda_samp
                                     uint32_t vocab_offset, uint32_t vocab_total, uint32_t k_shard,
                                     float *candidate_scores, uint32_t *candidate_ids, uint32_t stride,
                                     fg_error *err);
+/* the merge step of the fused exchange: where the shards' blocks lie in this rank's window,
+ * and the arrival counters it waits on (bounded) before it reads a row */
+typedef struct fg_cuda_arrivals {
+    uint64_t shard_pitch;     /* candidates between consecutive shards' blocks */
+    uint32_t *arrived;        /* one counter per row; set back to zero by the merge */
+    uint32_t target;          /* a row is complete at this count */
+    uint32_t wait_polls;      /* 0: about two seconds */
+} fg_cuda_arrivals;
 fg_status fg_cuda_merge_select_layout(fg_cuda_context *context, const fg_cuda_sample_args *args,
                                       const float *candidate_scores, const uint32_t *candidate_ids,
                                       uint32_t stride, uint32_t shards, uint32_t k_shard,
                                       const uint32_t *shard_first, const uint32_t *shard_width,
-                                      bool keep_errors, fg_error *err);
+                                      bool keep_errors, const fg_cuda_arrivals *arrivals, fg_error *err);
 /* Waits for the context's stream and turns the device's error word into a status. */
 fg_status fg_cuda_collect(fg_cuda_context *context, fg_error *err);
 /* fg_sampler_config_validate with the optional "top_k == 0" extension. */

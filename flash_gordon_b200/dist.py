@@ -194,8 +194,10 @@ class Communicator:
 
     def sample_vocab_sharded(self, logits_shard: torch.Tensor, configs, uniforms: torch.Tensor,
                              vocab_total: int, k_shard: int = 64, history_tokens=None, history_offsets=None,
-                             history_max: int = 0, out=None, asynchronous: bool = False):
-        """fg_dist_sample_vocab_sharded: shard top-k, one all-gather, merge and select."""
+                             history_max: int = 0, out=None, asynchronous: bool = False, fused: bool = False):
+        """fg_dist_sample_vocab_sharded: shard top-k, one all-gather, merge and select.  `fused`:
+        fg_dist_sample_vocab_sharded_fused, where the shard kernel stores its candidates straight
+        into every rank's window and the merge kernel waits for them (no collective kernel)."""
         import ctypes
         from . import FG_CUDA_SAMPLE_ASYNC, FgError
         from .api import SampleResult
@@ -208,8 +210,8 @@ class Communicator:
         args, keep = self.context._args(logits_shard, configs, uniforms, history_tokens, history_offsets,
                                         history_max, None, FG_CUDA_SAMPLE_ASYNC if asynchronous else 0, out, None)
         err = FgError()
-        status = self.lib.fg_dist_sample_vocab_sharded(self.handle, ctypes.byref(args), vocab_total, k_shard,
-                                                       ctypes.byref(err))
+        call = self.lib.fg_dist_sample_vocab_sharded_fused if fused else self.lib.fg_dist_sample_vocab_sharded
+        status = call(self.handle, ctypes.byref(args), vocab_total, k_shard, ctypes.byref(err))
         del keep
         return SampleResult(out[0], out[1], out[2], status, err.text(), None)
 

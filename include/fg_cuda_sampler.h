@@ -364,6 +364,18 @@ void fg_dist_shard_span(uint32_t vocab_total, uint32_t shards, uint32_t shard, u
 fg_status fg_dist_sample_vocab_sharded(fg_dist *dist, const fg_cuda_sample_args *args,
                                        uint32_t vocab_total, uint32_t k_shard, fg_error *err);
 
+/* The same call with the exchange fused into the two kernels: the shard kernel stores every
+ * row's block of pairs straight into every rank's window over NVLink (plain stores on peer
+ * pointers, then one system-scope add on the row's arrival counter there), and the merge
+ * kernel waits -- bounded -- until all ranks have counted themselves in for a row before it
+ * reads its own window.  Two launches per call and no collective kernel; results are
+ * identical.  The windows are mapped with CUDA IPC on first use (all ranks on one machine),
+ * and the first call and any call with more rows than before is collective.  A rank that
+ * never stores its blocks fails the rows with FG_ERR_LIMIT after about two seconds and the
+ * communicator is closed, as above. */
+fg_status fg_dist_sample_vocab_sharded_fused(fg_dist *dist, const fg_cuda_sample_args *args,
+                                             uint32_t vocab_total, uint32_t k_shard, fg_error *err);
+
 /* Row partition, optional: all ranks' results on every rank.  Every rank passes `rows`
  * results (device arrays; the same count on every rank) and gets ranks * rows back in
  * rank order.  Waits for completion. */

@@ -43,6 +43,13 @@ def _worker(rank, world, port, failures):
         assert out.status == want[0] == 0, out.message
         assert np.array_equal(out.tokens.cpu().numpy().view(np.uint32), want[1])
         assert np.array_equal(out.token_logits.cpu().numpy().view(np.uint32), want[2].view(np.uint32))
+        # the same with the exchange fused into the kernels (stores into the peers' windows), three
+        # times over so that both halves of the windows and a second use of one are exercised
+        for attempt in range(3):
+            fused = communicator.sample_vocab_sharded(mine, w.configs, w.uniforms.cuda(), w.vocab, 64, fused=True)
+            assert fused.status == 0, fused.message
+            assert np.array_equal(fused.tokens.cpu().numpy().view(np.uint32), want[1]), attempt
+            assert np.array_equal(fused.token_logits.cpu().numpy().view(np.uint32), want[2].view(np.uint32))
         # with penalties and a history: ids are global, every shard filters the history to its span
         w2 = synth.config2(rows=16, history=256)
         want2 = run_oracle(w2, threads=4)
@@ -111,6 +118,14 @@ def test_one_rank_runs_the_whole_sharded_call(context):
             want = run_oracle(w)
             # (a greedy row with a NaN/Inf is rejected as the split head does: MISMATCH, as unsharded)
             assert_rows_equal(result, want, w.name)
+            # and with the exchange fused into the two kernels: the shard kernel stores into the
+            # (one) rank's window and counts itself in, the merge kernel waits for the counters
+            for attempt in range(3):
+                fused = communicator.sample_vocab_sharded(wd.logits, wd.configs, wd.uniforms, w.vocab, 64,
+                                                          wd.history_tokens, wd.history_offsets, wd.history_max,
+                                                          fused=True)
+                torch.cuda.synchronize()
+                assert_rows_equal(fused, want, f"{w.name}, fused exchange, call {attempt}")
         wd = synth.config4(rows=4, vocab=8_000).to("cuda")
         short = communicator.sample_vocab_sharded(wd.logits[:, :4000].contiguous(), wd.configs, wd.uniforms,
                                                   8_000, 64)
