@@ -280,7 +280,8 @@ __device__ __forceinline__ bool tile_wait(Shared &sh, uint64_t *barrier, uint32_
 #ifdef FGK_PHASE_CLOCKS
 // Build with -DFGK_PHASE_CLOCKS to learn where the consumer warps' cycles go: slot 0 waits
 // for the lists and the bitmap, 1 waits for tiles, 2 first bound (with its wait for the
-// other warps), 3 tiles against the bound, 4 asking for the next tile, 5 end of unit.
+// other warps), 3 tiles against the bound, 4 asking for the next tile, 5 end of unit,
+// 6 candidates onto the list, 7 exact values and the warp's j-th best.
 __device__ unsigned long long fgk_persist_clocks[8];
 #define FGK_PTICK(slot)                          \
     do {                                          \
@@ -913,6 +914,7 @@ __device__ __forceinline__ uint32_t consume_unit(const Params &p, Shared &sh, Li
                 hot |= (largest(v) >= tau && (uint32_t)(v8 * 32) + lane < valid_vectors ? 1u : 0u) << v8;
             }
         }
+        FGK_PTICK(3);
         if (__any_sync(kFullMask, hot != 0)) {
             Progress state;
             state.bound = bound;
@@ -923,11 +925,13 @@ __device__ __forceinline__ uint32_t consume_unit(const Params &p, Shared &sh, Li
             count = state.count;
             refined = state.refined;
         }
+        FGK_PTICK(6);
         // The bound tightens as the row is read: after its 1st, 2nd, 4th, 8th ... tile (always
         // when the row wants one candidate) the warp gives its new entries their exact values
         // and publishes its j-th best; the smallest published by the unit's warps bounds k
         // elements.  Nobody waits: a warp that has published nothing yet keeps it at zero.
         done++;
+#ifndef FGK_X_NO_ADAPT
         if (per_warp <= 32u && count != 0 &&
             (r.k == 1u ? count != refined : (done & (done - 1u)) == 0u)) {
             if (count != refined) {
@@ -945,8 +949,9 @@ __device__ __forceinline__ uint32_t consume_unit(const Params &p, Shared &sh, Li
             const uint64_t pooled = (uint64_t)__reduce_min_sync(kFullMask, theirs) << 32;
             bound = max(bound, pooled);
         }
+#endif
         __syncwarp();
-        FGK_PTICK(3);
+        FGK_PTICK(7);
         consumed++;
         feeder.template issue<T>(p, stages + (size_t)stage * kStageBytes, &sh.full[w][stage], row_bytes, w,
                                  shard_mode, policy);
@@ -1403,7 +1408,7 @@ __global__ void __launch_bounds__(kBlock, 1) persistent_select_kernel(const __gr
     uint32_t consumed = 0;  // tiles of this warp so far
     uint32_t served = 0;    // units before this one
 #ifdef FGK_PHASE_CLOCKS
-    unsigned long long phase[6] = {0, 0, 0, 0, 0, 0};
+    unsigned long long phase[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     long long tick = clock64();
 #endif
     UnitWalk walk(p, tiles);
@@ -1448,7 +1453,7 @@ __global__ void __launch_bounds__(kBlock, 1) persistent_select_kernel(const __gr
     }
 #ifdef FGK_PHASE_CLOCKS
     if (lane == 0)
-        for (int i = 0; i < 6; i++) atomicAdd(&fgk_persist_clocks[i], phase[i]);
+        for (int i = 0; i < 8; i++) atomicAdd(&fgk_persist_clocks[i], phase[i]);
 #endif
     // copies asked for but never looked at (only after a wait ran out) still write into this
     // CTA's shared memory: see them land, bounded, before the CTA may go away

@@ -203,7 +203,10 @@ fg_status fg_sampler_select(const fg_sampler_config *config, const float *scores
             } else if (!any_finite) {
                 fg_error_set(err, status, "sampler received no finite candidates");
             } else {
-                fg_error_set(err, status, "sampler softmax failed");
+                /* src/sampler.c:102 cannot be what failed: the un-tempered sum holds
+                 * exp(0) for the best finite candidate and at most 63 terms in (0, 1],
+                 * so it is finite and positive; what is left is src/sampler.c:111 */
+                fg_error_set(err, status, "sampler temperature softmax failed");
             }
         }
     }
