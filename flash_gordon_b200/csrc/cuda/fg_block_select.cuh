@@ -207,6 +207,44 @@ __device__ __forceinline__ void report_row(const SelectOutput &out, uint32_t row
         atomicMin(out.first_error, ((unsigned long long)row << 8) | (unsigned long long)status);
 }
 
+// x[0] + x[1] + ... + x[n-1] added from the left, one rounding per addition, as the C loops
+// of src/sampler.c:99-111 do; the loads of four terms go ahead of their additions.
+__device__ __forceinline__ double ordered_sum(const double *x, uint32_t n) {
+    double sum = 0.0;
+    uint32_t i = 0;
+    for (; i + 4 <= n; i += 4) {
+        const double a = x[i], b = x[i + 1], c = x[i + 2], d = x[i + 3];
+        sum += a;
+        sum += b;
+        sum += c;
+        sum += d;
+    }
+    for (; i < n; i++) sum += x[i];
+    return sum;
+}
+
+// The first i whose running sum x[0] + ... + x[i] (added from the left) satisfies
+// `sum >= limit` (kStrictlyAbove: `limit < sum`); n when none does.
+template <bool kStrictlyAbove>
+__device__ __forceinline__ uint32_t ordered_reach(const double *x, uint32_t n, double limit) {
+    double sum = 0.0;
+    uint32_t i = 0;
+    for (; i + 4 <= n; i += 4) {
+        const double a = x[i], b = x[i + 1], c = x[i + 2], d = x[i + 3];
+        const double s0 = sum + a, s1 = s0 + b, s2 = s1 + c, s3 = s2 + d;
+        if (kStrictlyAbove ? limit < s0 : s0 >= limit) return i;
+        if (kStrictlyAbove ? limit < s1 : s1 >= limit) return i + 1;
+        if (kStrictlyAbove ? limit < s2 : s2 >= limit) return i + 2;
+        if (kStrictlyAbove ? limit < s3 : s3 >= limit) return i + 3;
+        sum = s3;
+    }
+    for (; i < n; i++) {
+        sum += x[i];
+        if (kStrictlyAbove ? limit < sum : sum >= limit) return i;
+    }
+    return n;
+}
+
 // Final step for one row; called by warp 0 of the CTA (all 32 lanes) with the
 // candidates already in sampling order in fin.score/id[0..n), n = min(top_k,
 // #finite).  Greedy rows never come here.
@@ -226,8 +264,7 @@ __device__ inline void finish_select(FinishBuffer &fin, uint32_t n, const Sample
     // the sums run left to right on one lane, as the C code's loops do; the divisions
     // are independent of one another and spread over the warp
     double raw_sum = 0.0;
-    if (lane == 0)
-        for (uint32_t i = 0; i < n; i++) raw_sum += fin.raw[i];
+    if (lane == 0) raw_sum = ordered_sum(fin.raw, n);
     raw_sum = __shfl_sync(kFullMask, raw_sum, 0);
     const bool raw_ok = raw_sum > 0.0 && !isinf(raw_sum) && !isnan(raw_sum);
     if (raw_ok)
@@ -235,17 +272,7 @@ __device__ inline void finish_select(FinishBuffer &fin, uint32_t n, const Sample
     __syncwarp();
     if (lane == 0) {
         uint32_t cutoff = n;
-        if (raw_ok) {
-            double mass = 0.0;
-            const double top_p = (double)cfg.top_p;
-            for (uint32_t i = 0; i < n; i++) {
-                mass += fin.raw[i];
-                if (mass >= top_p) {
-                    cutoff = i + 1;
-                    break;
-                }
-            }
-        }
+        if (raw_ok) cutoff = min(n, ordered_reach<false>(fin.raw, n, (double)cfg.top_p) + 1u);
         fin.cutoff = cutoff;
         fin.status = raw_ok ? kOk : kErrFormat;  // "sampler raw softmax failed"
     }
@@ -264,8 +291,7 @@ __device__ inline void finish_select(FinishBuffer &fin, uint32_t n, const Sample
         fin.tempered[i] = i < cutoff ? exp((double)fin.score[i] / temperature - top_tempered) : 0.0;
     __syncwarp();
     if (lane == 0) {
-        double weight_sum = 0.0;
-        for (uint32_t i = 0; i < cutoff; i++) weight_sum += fin.tempered[i];
+        const double weight_sum = ordered_sum(fin.tempered, cutoff);
         if (!(weight_sum > 0.0) || isinf(weight_sum) || isnan(weight_sum)) {
             fin.status = kErrFormat;  // "sampler temperature softmax failed"
         } else {
@@ -273,16 +299,7 @@ __device__ inline void finish_select(FinishBuffer &fin, uint32_t n, const Sample
             if (is_nonfinite(u) || u < 0.0f) u = 0.0f;
             if (u >= 1.0f) u = __uint_as_float(0x3f7fffffu);  // nextafterf(1, 0)
             const double draw = (double)u * weight_sum;
-            uint32_t pick = cutoff - 1;
-            double walked = 0.0;
-            for (uint32_t i = 0; i < cutoff; i++) {
-                walked += fin.tempered[i];
-                if (draw < walked) {
-                    pick = i;
-                    break;
-                }
-            }
-            fin.picked = pick;
+            fin.picked = min(cutoff - 1u, ordered_reach<true>(fin.tempered, cutoff, draw));
             if (out.dbg_tempered)
                 for (uint32_t i = 0; i < cutoff; i++) fin.tempered[i] = fin.tempered[i] / weight_sum;
         }

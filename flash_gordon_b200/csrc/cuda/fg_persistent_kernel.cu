@@ -62,6 +62,7 @@ constexpr uint32_t kStageBytes = kTileLogits * 4;  // a stage holds a tile of th
 #endif
 constexpr int kListCap = FGK_RING_LIST_CAP;     // entries of one warp's candidate list (a multiple of 32, > 64)
 constexpr int kListWords = kListCap / 32;
+constexpr int kTallyBins = 256;                 // bins of the per-unit score tally (eight per lane)
 constexpr int kBlock = (kWarps + kHistoryWarps + kClosers) * 32;
 constexpr uint32_t kDefaultPolls = 1u << 21;    // polls before a wait gives up: a second or two
 constexpr uint32_t kNapNanoseconds = 400;       // sleep between two polls of a wait that may be long
@@ -210,9 +211,9 @@ struct alignas(16) Lists {
     unsigned long long bound;               // the admission bound T (only ever rises)
     uint32_t first_key;                     // smallest of the warps' first-tile keys
     uint32_t first_count;                   // warps that have published theirs
-    uint32_t warp_kth[kWarps];              // each warp's j-th best exact score so far, as a key (0: none yet)
+    uint32_t first_top;                     // largest score of the first tiles, as a key
     uint32_t bad_history;
-    uint32_t pad_;
+    uint32_t tally[kTallyBins];             // exact entries by score, see Tally
 };
 
 struct Shared {
@@ -282,7 +283,16 @@ __device__ __forceinline__ bool tile_wait(Shared &sh, uint64_t *barrier, uint32_
 // for the lists and the bitmap, 1 waits for tiles, 2 first bound (with its wait for the
 // other warps), 3 tiles against the bound, 4 asking for the next tile, 5 end of unit,
 // 6 candidates onto the list, 7 exact values and the warp's j-th best.
-__device__ unsigned long long fgk_persist_clocks[8];
+__device__ unsigned long long fgk_persist_clocks[16];
+// closing warps: 8 waiting for a unit, 9 threshold selection, 10 counting occurrences,
+// 11 gather and sort, 12 the rest of a unit's close
+#define FGK_CTICK(slot)                                                            \
+    do {                                                                            \
+        const long long now_ = clock64();                                           \
+        if (lane_id() == 0) atomicAdd(&fgk_persist_clocks[slot], (unsigned long long)(now_ - ctick)); \
+        ctick = now_;                                                               \
+    } while (0)
+#define FGK_CTICK_BEGIN long long ctick = clock64()
 #define FGK_PTICK(slot)                          \
     do {                                          \
         const long long now = clock64();          \
@@ -291,6 +301,8 @@ __device__ unsigned long long fgk_persist_clocks[8];
     } while (0)
 #else
 #define FGK_PTICK(slot) do { } while (0)
+#define FGK_CTICK(slot) do { } while (0)
+#define FGK_CTICK_BEGIN do { } while (0)
 #endif
 
 __device__ __forceinline__ uint64_t warp_max_u64(uint64_t v) {
@@ -416,6 +428,19 @@ __device__ __forceinline__ uint32_t classify(Lists &L, const Row &r, uint32_t w,
     return select_key(x, id) >= bound ? 1u : 0u;
 }
 
+// The same out of line, for the few elements of a tile that need it.
+struct Classified {
+    uint32_t kind;
+    float value;
+};
+template <bool kGreedy>
+__device__ __noinline__ Classified classify_apart(Lists &L, const Row r, uint32_t w, float x, uint32_t id, bool seen,
+                                                  uint64_t bound) {
+    Classified c;
+    c.kind = classify<kGreedy>(L, r, w, x, id, seen, bound, &c.value);
+    return c;
+}
+
 // Counts the occurrences of the not-yet-counted entries of warp w's list whose upper bound
 // reaches `bound`, and gives them their exact value (src/sampler.c:52-58).  An entry the
 // penalty turns into NaN/Inf dies (greedy rows note it).  All lanes call; returns how many
@@ -537,6 +562,23 @@ __device__ __noinline__ uint64_t local_cut(Lists &L, const Row r, uint32_t w) {
     return threshold;
 }
 
+// Where the exact entries of a unit lie, by score: bin b counts those whose score key is at
+// least base + (b << shift), the last bin everything above.  Once the bins from the top down
+// to b hold k entries, the lower edge of bin b bounds the row -- more tightly the further the
+// row has been read.  base and top come from the warps' first tiles.
+struct Tally {
+    uint32_t base;   // score key of the first bound (bin 0 starts here)
+    uint32_t shift;
+    __device__ __forceinline__ void span(uint32_t low, uint32_t high) {
+        base = low;
+        const uint32_t range = high > low ? high - low : 0u;
+        shift = range < (uint32_t)kTallyBins - 1u ? 0u : 25u - (uint32_t)__clz(range);  // (range >> shift) < 255
+    }
+    __device__ __forceinline__ uint32_t bin(uint32_t key) const {
+        return min((key - base) >> shift, (uint32_t)kTallyBins - 1u);
+    }
+};
+
 // The first bound of a unit.  Each warp that has a tile publishes the j-th largest of its
 // lanes' maxima, j = ceil(k / warps with a tile); a lane whose maximum is not finite, or
 // belongs to an id the history has seen (whose value the penalty will lower), publishes
@@ -544,11 +586,16 @@ __device__ __noinline__ uint64_t local_cut(Lists &L, const Row r, uint32_t w) {
 // their value, so the smallest of the published keys bounds k elements.  (A warp with fewer
 // than j such lanes publishes "no bound"; everything finite is then a candidate until some
 // list is cut.)  The warp waits until all have published -- a tile's worth of skew at most,
-// with the next tiles already on their way.  Returns the bound as a key.
+// with the next tiles already on their way.  Returns the bound and the largest score of the
+// first tiles, between which the tally is laid out.
+struct FirstBound {
+    uint32_t key;  // score key of the bound (0: none)
+    uint32_t top;  // largest score of the first tiles, as a key
+};
 template <typename T>
-__device__ __noinline__ uint64_t first_bound(Shared &sh, Lists &L, const Row r, const uint32_t *bitmap,
-                                             const unsigned char *tile, uint32_t column0,
-                                             uint32_t valid_vectors, uint32_t participants, uint32_t polls) {
+__device__ __noinline__ FirstBound first_bound(Shared &sh, Lists &L, const Row r, const uint32_t *bitmap,
+                                               const unsigned char *tile, uint32_t column0,
+                                               uint32_t valid_vectors, uint32_t participants, uint32_t polls) {
     using V = Lanes<T>;
     constexpr int kPer = V::kPer;
     constexpr int kVectors = tile_vectors<T>();
@@ -582,8 +629,9 @@ __device__ __noinline__ uint64_t first_bound(Shared &sh, Lists &L, const Row r, 
         if (!seen) key = float_key(best);
     }
     const uint32_t per_warp = (r.k + participants - 1) / participants;
-    uint32_t kth = 0;
-    if (per_warp <= 32u) {
+    const uint32_t top = __reduce_max_sync(kFullMask, key);
+    uint32_t kth = per_warp == 1u ? top : 0u;
+    if (per_warp > 1u && per_warp <= 32u) {
         for (uint32_t i = 0; i < per_warp; i++) {
             kth = __reduce_max_sync(kFullMask, key);
             if (kth == 0) break;
@@ -593,6 +641,9 @@ __device__ __noinline__ uint64_t first_bound(Shared &sh, Lists &L, const Row r, 
     }
     if (lane == 0) {
         atomicMin(&L.first_key, kth);
+        atomicMax(&L.first_top, top);
+        // a row that wants one candidate is bounded by the best any warp has seen
+        if (r.k == 1u && top != 0) atomicMax(&L.bound, (unsigned long long)top << 32);
         __threadfence_block();
         atomicAdd(&L.first_count, 1u);
     }
@@ -606,152 +657,134 @@ __device__ __noinline__ uint64_t first_bound(Shared &sh, Lists &L, const Row r, 
         __nanosleep(100);
     }
     __threadfence_block();
-    return (uint64_t)peek(&L.first_key) << 32;
+    FirstBound first;
+    first.key = peek(&L.first_key);
+    first.top = peek(&L.first_top);
+    return first;
 }
 
-// Entries [from, count) of the warp's list are raw: (logit, id) as they were streamed.
-// Here every lane takes one of them at a time and gives it its place: the penalty of a seen
-// id (src/sampler.c:52-58), or the mark "occurrences not counted yet"; what cannot be among
-// the k best under the bound as it stands now is dropped, the rest moves up.  Greedy rows
-// note a NaN/Inf on the way.  All lanes call; returns the new count.
-template <bool kGreedy>
-__device__ __noinline__ uint32_t refine(Lists &L, const Row r, const uint32_t *bitmap, uint32_t w, uint32_t from,
-                                        uint32_t count, uint64_t bound, uint64_t *best_exact) {
+// The bound the tally allows: the lower edge of the highest bin such that it and the bins above
+// it hold k entries.  All lanes call; lane 0 lifts the unit's bound.
+__device__ __noinline__ void raise_bound(Lists &L, const Tally tally, uint32_t k) {
     const uint32_t lane = lane_id();
-    uint32_t out = from;
-    uint64_t best = 0;  // the largest key among the entries kept with their exact value
-    for (uint32_t base = from; base < count; base += 32) {
-        const uint32_t i = base + lane;
-        const bool valid = i < count;
-        const float x = valid ? L.score[w][i] : 0.0f;
-        const uint32_t id = valid ? L.id[w][i] : kPaddingId;
-        const uint32_t column = id - r.id_base;
-        const bool seen = valid && r.seen_any && ((bitmap[column >> 5] >> (column & 31u)) & 1u);
-        float value = x;
-        const uint32_t kind = valid ? classify<kGreedy>(L, r, w, x, id, seen, bound, &value) : 0u;
-        const uint32_t keeping = __ballot_sync(kFullMask, kind != 0u);  // (every lane has read its entry)
-        if (kind != 0u) {
-            const uint32_t at = out + __popc(keeping & ((1u << lane) - 1u));
-            L.score[w][at] = kind == 2u ? x : value;
-            L.id[w][at] = id;
-            if (kind == 2u) atomicOr(&L.deferred[w][at >> 5], 1u << (at & 31u));
-            else best = max(best, select_key(value, id));
-        }
-        out += __popc(keeping);
-        __syncwarp();
+    // lane l owns bins 255-8l .. 248-8l, walked from the top
+    uint32_t bins[8];
+    uint32_t mine = 0;
+#pragma unroll
+    for (int b = 0; b < 8; b++) {
+        bins[b] = peek(&L.tally[kTallyBins - 1 - 8 * lane - b]);
+        mine += bins[b];
     }
-    if (best_exact) *best_exact = warp_max_u64(best);
-    return out;
+    uint32_t incl = mine;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const uint32_t up = __shfl_up_sync(kFullMask, incl, d);
+        if (lane >= (uint32_t)d) incl += up;
+    }
+    const unsigned reached = __ballot_sync(kFullMask, incl >= k);
+    if (reached == 0) return;
+    if ((int)lane == __ffs(reached) - 1) {
+        uint32_t over = incl - mine;
+        uint32_t bin = kTallyBins - 1 - 8 * lane;
+#pragma unroll
+        for (int b = 0; b < 8; b++) {
+            over += bins[b];
+            if (over >= k) break;
+            bin--;
+        }
+        const uint64_t edge = (uint64_t)tally.base + ((uint64_t)bin << tally.shift);
+        // (an edge below every finite score is no bound, and its key no number)
+        if (edge >= 0x00800000ull && edge <= 0xff7fffffull) atomicMax(&L.bound, (unsigned long long)(edge << 32));
+    }
 }
 
-// The elements of a tile that reach the bound's score go on the warp's list as they are,
-// (logit, id); refine() deals with them later, a whole warp's worth at a time.  Only lanes
-// that hold such an element look for it, in the vectors the scan marked (`hot`, a bit per
-// vector of the lane), element by element.  Slots are handed out by ballot, one element per lane
-// and round, so the list's length lives in registers and no atomic is needed.  A list that
-// cannot take a round is refined, and cut to its k best if that was not enough, which also
-// lifts the bound.  All lanes call; returns the bound the warp knows afterwards.
-// What a consumer warp knows about its list and the bound; handed to and from collect() by
-// value, so that it stays in registers.
-struct Progress {
-    uint64_t bound;
-    uint32_t count, refined;  // entries on the list; how many of them refine() has seen
-};
-
+// The elements of a tile that reach the bound go on the warp's list.  Only lanes that hold such
+// an element look for it, in the vectors the scan marked (`hot`, a bit per vector of the lane),
+// and note where (`take`, a bit per element of the lane); then all of them put one element each
+// on the list at a time.  An id the history has seen, or a NaN/Inf of a greedy row, is classified
+// first; every entry that goes on the list with its exact value lifts the bound (a row that wants
+// one candidate) or is counted in the tally.  A list that is full is cut to its k best, which
+// lifts the bound too, and the lanes go on where they stopped.  All lanes call; returns the bound
+// the warp knows afterwards.
 template <typename T, bool kGreedy>
-__device__ __noinline__ Progress collect(Lists &L, const Row r, const uint32_t *bitmap, const unsigned char *tile,
+__device__ __noinline__ uint64_t collect(Lists &L, const Row r, const uint32_t *bitmap, const unsigned char *tile,
                                          uint32_t column0, uint32_t valid_vectors, uint32_t w, uint32_t hot,
-                                         const Progress in) {
+                                         uint64_t bound, const Tally tally) {
     using V = Lanes<T>;
     constexpr int kPer = V::kPer;
     const uint32_t lane = lane_id();
     const uint4 *vectors = reinterpret_cast<const uint4 *>(tile);
-    uint64_t bound = in.bound;
-    const float tau = key_to_float((uint32_t)(bound >> 32));
-    uint32_t count = in.count, refined = in.refined;
+    float tau = key_to_float((uint32_t)(bound >> 32));
     uint64_t take = 0;  // bit u * kPer + j: element j of this lane's vector u
-    for (uint32_t rest = hot; rest != 0; rest &= rest - 1) {  // bit u: vector u of this lane is worth a look
-        {
-            const uint32_t u = __ffs(rest) - 1;
-            const uint32_t g = u * 32 + lane;
-            if (g >= valid_vectors) break;
-            float v[kPer];
-            V::unpack(vectors[g], v);
-            uint32_t bits = 0;
+    for (; hot != 0; hot &= hot - 1) {
+        const uint32_t u = __ffs(hot) - 1;
+        const uint32_t g = u * 32 + lane;
+        if (g >= valid_vectors) break;
+        float v[kPer];
+        V::unpack(vectors[g], v);
+        uint32_t bits = 0;
 #pragma unroll
-            for (int j = 0; j < kPer; j++) {
-                const bool wild = kGreedy && (__float_as_uint(v[j]) & 0x7fffffffu) >= kHugeBits;
-                bits |= (v[j] >= tau || wild ? 1u : 0u) << j;
-            }
-            take |= (uint64_t)bits << (u * kPer);
+        for (int j = 0; j < kPer; j++) {
+            const bool wild = kGreedy && (__float_as_uint(v[j]) & 0x7fffffffu) >= kHugeBits;
+            bits |= (v[j] >= tau || wild ? 1u : 0u) << j;
         }
+        take |= (uint64_t)bits << (u * kPer);
     }
+#ifdef FGK_PHASE_CLOCKS
+    if (lane == 0) atomicAdd(&fgk_persist_clocks[14], 1ull);
+#endif
     for (;;) {
-        const uint32_t offering = __ballot_sync(kFullMask, take != 0);
-        if (offering == 0) break;
-        const uint32_t round = __popc(offering);
-        if (count + round > (uint32_t)kListCap) {
-            count = refine<kGreedy>(L, r, bitmap, w, refined, count, bound, nullptr);
-            refined = count;
-            if (count + round > (uint32_t)kListCap) {
-                if (lane == 0) L.count[w] = count;
-                __syncwarp();
-                const uint64_t mine = local_cut(L, r, w);
-                bound = max(bound, mine);
-                count = refined = L.count[w];
-            }
-            bound = max(bound, (uint64_t)peek64(&L.bound));
-        }
-        if (take != 0) {
+        bool stuck = false;
+        while (take != 0 && !stuck) {
             const uint32_t e = __ffsll((long long)take) - 1;
-            take &= take - 1;
             const uint32_t position = ((e / kPer) * 32 + lane) * kPer + (e % kPer);
-            const uint32_t slot = count + __popc(offering & ((1u << lane) - 1u));
-            L.score[w][slot] = tile_element<T>(tile, position);
-            L.id[w][slot] = r.id_base + column0 + position;
-        }
-        count += round;
-    }
-    Progress out;
-    out.bound = bound;
-    out.count = count;
-    out.refined = refined;
-    return out;
-}
-
-// The j-th largest exact score on the warp's list, as a key (0 when it holds fewer than j
-// exact entries): j rounds of "the largest that is left".  Every warp publishes its own; the
-// smallest over the warps of a unit has j entries at or above it in every one of them, k in
-// all, and so bounds the row -- more tightly the further the row has been read.
-__device__ __noinline__ uint32_t jth_best(const Lists &L, uint32_t w, uint32_t count, uint32_t j) {
-    const uint32_t lane = lane_id();
-    uint32_t key[kListWords];
-#pragma unroll
-    for (int q = 0; q < kListWords; q++) {
-        const uint32_t i = q * 32 + lane;
-        const bool exact = i < count && ((L.deferred[w][q] >> lane) & 1u) == 0 && L.id[w][i] != kPaddingId;
-        key[q] = exact ? float_key(L.score[w][i]) : 0u;
-    }
-    uint32_t found = 0;
-    for (uint32_t round = 0; round < j; round++) {
-        uint32_t mine = 0;
-#pragma unroll
-        for (int q = 0; q < kListWords; q++) mine = max(mine, key[q]);
-        found = __reduce_max_sync(kFullMask, mine);
-        if (found == 0) break;
-        const uint32_t owners = __ballot_sync(kFullMask, mine == found);
-        if ((int)lane == __ffs(owners) - 1) {
-            bool gone = false;
-#pragma unroll
-            for (int q = 0; q < kListWords; q++) {
-                if (!gone && key[q] == found) {
-                    key[q] = 0;
-                    gone = true;
+            const float x = tile_element<T>(tile, position);
+            const uint32_t column = column0 + position;
+            const uint32_t id = r.id_base + column;
+            const bool wild = kGreedy && (__float_as_uint(x) & 0x7fffffffu) >= kHugeBits;
+            const bool seen = r.seen_any && ((bitmap[column >> 5] >> (column & 31u)) & 1u);
+            float value = x;
+            uint32_t kind;
+            if (seen || wild) {
+                const Classified c = classify_apart<kGreedy>(L, r, w, x, id, seen, bound);
+                kind = c.kind;
+                value = c.value;
+            } else {
+                // (an infinity is nobody's candidate; equal scores: the smaller id)
+                kind = !is_nonfinite(x) && x >= tau && select_key(x, id) >= bound ? 1u : 0u;
+            }
+            if (kind != 0u) {
+                const uint32_t slot = atomicAdd(&L.count[w], 1u);
+                if (slot >= (uint32_t)kListCap) {
+                    stuck = true;  // (the element stays in `take`)
+                    continue;
+                }
+                L.score[w][slot] = kind == 2u ? x : value;
+                L.id[w][slot] = id;
+#ifdef FGK_PHASE_CLOCKS
+                atomicAdd(&fgk_persist_clocks[13], 1ull);
+#endif
+                if (kind == 2u) {
+                    atomicOr(&L.deferred[w][slot >> 5], 1u << (slot & 31u));
+                } else if (r.k == 1u) {
+                    atomicMax(&L.bound, (unsigned long long)select_key(value, id));
+                } else {
+                    const uint32_t key = float_key(value);
+                    if (key >= tally.base) atomicAdd(&L.tally[tally.bin(key)], 1u);
                 }
             }
+            take &= take - 1;
         }
+        if (!__any_sync(kFullMask, stuck)) break;
+        __syncwarp();
+#ifdef FGK_PHASE_CLOCKS
+        if (lane == 0) atomicAdd(&fgk_persist_clocks[15], 1ull);
+#endif
+        bound = max(bound, local_cut(L, r, w));
+        bound = max(bound, (uint64_t)peek64(&L.bound));
+        tau = key_to_float((uint32_t)(bound >> 32));
     }
-    return found;
+    return bound;
 }
 
 // The row as the warps see it; *bad_history is the status a broken history earns the
@@ -846,8 +879,8 @@ struct Feeder {
 };
 
 // One consumer warp's share of one unit: its tiles against the bound, candidates onto its
-// list.  Per tile and lane: the 128-bit vectors of the tile, a maximum of each, the largest of
-// those against the bound's score.  Returns the number of tiles it has looked at.
+// list.  Per tile and lane: the 128-bit vectors of the tile, a maximum of each against the
+// bound's score.  Returns the number of tiles it has looked at.
 template <typename T, bool kGreedy>
 __device__ __forceinline__ uint32_t consume_unit(const Params &p, Shared &sh, Lists &L, const Row r, const Unit u,
                                               const uint32_t *bitmap, unsigned char *stages, Feeder &feeder,
@@ -864,11 +897,12 @@ __device__ __forceinline__ uint32_t consume_unit(const Params &p, Shared &sh, Li
     const uint32_t whole = tile_bytes<T>() / 16u;
     const uint32_t last_vectors = (row_bytes - (tiles - 1) * tile_bytes<T>()) / 16u;
     const uint32_t participants = min((uint32_t)kWarps, u.end - u.first);
-    const uint32_t per_warp = (r.k + participants - 1) / participants;  // j of jth_best()
     uint64_t bound = 0;
-    uint32_t count = 0, refined = 0;  // entries on this warp's list; how many of them refine() has seen
-    uint32_t done = 0, published = 0; // tiles of this unit so far; the j-th best this warp has published
-    bool first = true;
+    Tally tally;
+    tally.base = 0;
+    tally.shift = 24;
+    uint32_t done = 0;  // tiles of this unit so far
+    uint32_t turn = w;  // after which of them it is this warp's turn to lift the bound
     for (uint32_t t = u.first + w; t < u.end; t += kWarps) {
         const uint32_t stage = consumed % kStages;
         tile_wait(sh, &sh.full[w][stage], (consumed / kStages) & 1u, polls);
@@ -876,9 +910,11 @@ __device__ __forceinline__ uint32_t consume_unit(const Params &p, Shared &sh, Li
         const unsigned char *tile = stages + (size_t)stage * kStageBytes;
         const uint32_t valid_vectors = t + 1 == tiles ? last_vectors : whole;
         const uint32_t column0 = t * kTileLogits;
-        if (first) {
-            bound = first_bound<T>(sh, L, r, bitmap, tile, column0, valid_vectors, participants, polls);
-            first = false;
+        if (done == 0) {
+            const FirstBound first =
+                first_bound<T>(sh, L, r, bitmap, tile, column0, valid_vectors, participants, polls);
+            bound = (uint64_t)first.key << 32;
+            tally.span(first.key, first.top);
             FGK_PTICK(2);
         }
         bound = max(bound, (uint64_t)peek64(&L.bound));
@@ -886,70 +922,38 @@ __device__ __forceinline__ uint32_t consume_unit(const Params &p, Shared &sh, Li
         const uint4 *vectors = reinterpret_cast<const uint4 *>(tile);
         // which of the lane's vectors hold something at or above the bound's score (a NaN never
         // wins a maximum).  Greedy rows: the argmax order must also see NaN, both infinities
-        // and magnitudes a repetition factor of at most 2^40 could push there -- the lane's
-        // NaN-keeping maximum and its minimum tell, and then all its vectors are looked at.
+        // and magnitudes a repetition factor of at most 2^40 could push there -- a maximum that
+        // keeps NaN and a minimum tell.  (Beyond the row's end: stale bytes, masked.)
         uint32_t hot = 0;
-        if (kGreedy) {
-            float top = __uint_as_float(0xff800000u), low = __uint_as_float(0x7f800000u);
-            for (uint32_t g = lane; g < valid_vectors; g += 32) {
-                float v[kPer];
-                V::unpack(vectors[g], v);
-                top = propagating_max(top, v);
-                low = fminf(low, smallest(v));
-            }
-            // (`top` is NaN when the lane holds one, and NaN is not below anything)
-            if (!(top < tau) || low <= -__uint_as_float(kHugeBits)) hot = 0xffffffffu;
-        } else if (valid_vectors == whole) {
 #pragma unroll
-            for (int v8 = 0; v8 < kVectors; v8++) {
-                float v[kPer];
-                V::unpack(vectors[v8 * 32 + lane], v);
-                hot |= (largest(v) >= tau ? 1u : 0u) << v8;
+        for (int v8 = 0; v8 < kVectors; v8++) {
+            float v[kPer];
+            V::unpack(vectors[v8 * 32 + lane], v);
+            bool look;
+            if (kGreedy) {
+                const float top = propagating_max(v[0], v);
+                look = !(top < tau) || smallest(v) <= -__uint_as_float(kHugeBits);  // (NaN is not below anything)
+            } else {
+                look = largest(v) >= tau;
             }
-        } else {
+            hot |= (look ? 1u : 0u) << v8;
+        }
+        if (valid_vectors != whole) {
 #pragma unroll
-            for (int v8 = 0; v8 < kVectors; v8++) {
-                float v[kPer];
-                V::unpack(vectors[v8 * 32 + lane], v);  // (beyond the row's end: stale bytes, masked)
-                hot |= (largest(v) >= tau && (uint32_t)(v8 * 32) + lane < valid_vectors ? 1u : 0u) << v8;
-            }
+            for (int v8 = 0; v8 < kVectors; v8++)
+                if ((uint32_t)(v8 * 32) + lane >= valid_vectors) hot &= ~(1u << v8);
         }
         FGK_PTICK(3);
-        if (__any_sync(kFullMask, hot != 0)) {
-            Progress state;
-            state.bound = bound;
-            state.count = count;
-            state.refined = refined;
-            state = collect<T, kGreedy>(L, r, bitmap, tile, column0, valid_vectors, w, hot, state);
-            bound = state.bound;
-            count = state.count;
-            refined = state.refined;
-        }
+        if (__any_sync(kFullMask, hot != 0))
+            bound = collect<T, kGreedy>(L, r, bitmap, tile, column0, valid_vectors, w, hot, bound, tally);
         FGK_PTICK(6);
-        // The bound tightens as the row is read: after its 1st, 2nd, 4th, 8th ... tile (always
-        // when the row wants one candidate) the warp gives its new entries their exact values
-        // and publishes its j-th best; the smallest published by the unit's warps bounds k
-        // elements.  Nobody waits: a warp that has published nothing yet keeps it at zero.
+        // The bound tightens as the row is read: the warps take turns, one after every round of
+        // tiles, to see what the tally of all the warps' exact entries allows.  Nobody waits.
+        if (r.k > 1u && done == turn) {
+            raise_bound(L, tally, r.k);
+            turn += participants;
+        }
         done++;
-#ifndef FGK_X_NO_ADAPT
-        if (per_warp <= 32u && count != 0 &&
-            (r.k == 1u ? count != refined : (done & (done - 1u)) == 0u)) {
-            if (count != refined) {
-                count = refine<kGreedy>(L, r, bitmap, w, refined, count, bound, nullptr);
-                refined = count;
-            }
-            const uint32_t mine = jth_best(L, w, count, per_warp);
-            if (mine > published) {
-                published = mine;
-                if (lane == 0) poke(&L.warp_kth[w], mine);
-            }
-        }
-        if (published != 0) {
-            const uint32_t theirs = lane < participants ? peek(&L.warp_kth[lane]) : 0xffffffffu;
-            const uint64_t pooled = (uint64_t)__reduce_min_sync(kFullMask, theirs) << 32;
-            bound = max(bound, pooled);
-        }
-#endif
         __syncwarp();
         FGK_PTICK(7);
         consumed++;
@@ -957,11 +961,6 @@ __device__ __forceinline__ uint32_t consume_unit(const Params &p, Shared &sh, Li
                                  shard_mode, policy);
         FGK_PTICK(4);
     }
-    if (count != refined) {
-        bound = max(bound, (uint64_t)peek64(&L.bound));
-        count = refine<kGreedy>(L, r, bitmap, w, refined, count, bound, nullptr);
-    }
-    if (lane == 0) L.count[w] = count;
     return consumed;
 }
 
@@ -1046,13 +1045,16 @@ __device__ __noinline__ uint64_t select_threshold(uint32_t *hist, const Lists &L
     return low;
 }
 
-// The exact k best of a set of lists, in sampling order, into `fin`; returns how many.
-__device__ __noinline__ uint32_t settle_lists(FinishBuffer &fin, uint32_t *hist, uint32_t *gathered, Lists &L,
-                                             const Row r) {
+// The exact k best of a set of lists, in sampling order, into `fin`; returns how many.  The
+// long way: for lists that hold many more entries at or above the bound than a row wants.
+__device__ __noinline__ uint32_t settle_wide(FinishBuffer &fin, uint32_t *hist, uint32_t *gathered, Lists &L,
+                                            const Row r) {
     const uint32_t lane = lane_id();
     uint64_t threshold;
+    FGK_CTICK_BEGIN;
     for (;;) {
         threshold = select_threshold(hist, L, r);
+        FGK_CTICK(9);
         // entries not counted yet whose upper bound reaches the k best are settled, then the
         // selection is done again
         uint32_t any = 0;
@@ -1063,6 +1065,7 @@ __device__ __noinline__ uint32_t settle_lists(FinishBuffer &fin, uint32_t *hist,
         uint32_t with = __ballot_sync(kFullMask, any != 0);
         uint32_t settled = 0;
         for (; with != 0; with &= with - 1) settled += resolve_above(L, r, __ffs(with) - 1, threshold);
+        FGK_CTICK(10);
         if (settled == 0) break;
     }
     // unsorted survivors go to the far end of the work arrays, the sort brings them forward
@@ -1108,7 +1111,86 @@ __device__ __noinline__ uint32_t settle_lists(FinishBuffer &fin, uint32_t *hist,
         }
     }
     __syncwarp();
+    FGK_CTICK(11);
     return kept;
+}
+
+// The same, the short way.  Everything that can be among the k best lies at or above the
+// unit's bound, and by the time a unit is closed that is little more than k entries: they are
+// gathered densely (entries whose occurrences are not counted yet are settled first, if the
+// most they can be worth reaches the bound), and every entry finds its place by counting the
+// keys above its own.  Keys are distinct, so the places are a permutation.
+constexpr uint32_t kDense = 128;  // keys the short way takes: the closer's 256-word table
+__device__ __noinline__ uint32_t settle_lists(FinishBuffer &fin, uint32_t *hist, uint32_t *gathered, Lists &L,
+                                             const Row r) {
+    const uint32_t lane = lane_id();
+    FGK_CTICK_BEGIN;
+    const uint64_t bound = peek64(&L.bound);
+    {
+        uint32_t any = 0;
+        if (lane < (uint32_t)kWarps) {
+#pragma unroll
+            for (int j = 0; j < kListWords; j++) any |= L.deferred[lane][j];
+        }
+        for (uint32_t with = __ballot_sync(kFullMask, any != 0); with != 0; with &= with - 1)
+            resolve_above(L, r, __ffs(with) - 1, bound);
+    }
+    FGK_CTICK(10);
+    uint64_t *dense = reinterpret_cast<uint64_t *>(hist);
+    uint16_t *where = reinterpret_cast<uint16_t *>(fin.raw);  // list * kListCap + entry
+    static_assert(kDense * sizeof(uint64_t) <= 256 * sizeof(uint32_t), "the dense keys fit the closer's table");
+    static_assert(kWarps * kListCap <= 65536, "an entry's place fits 16 bits");
+    uint32_t n = 0;
+    for (uint32_t w = 0; w < (uint32_t)kWarps; w++) {
+        const uint32_t count = min(L.count[w], (uint32_t)kListCap);
+        for (uint32_t base = 0; base < count; base += 32) {
+            const uint32_t i = base + lane;
+            const bool exact = i < count && ((L.deferred[w][i >> 5] >> (i & 31u)) & 1u) == 0;
+            const uint64_t key = exact ? entry_key(L, r, w, i, false) : 0ull;
+            const bool take = key != 0 && key >= bound;
+            const uint32_t takers = __ballot_sync(kFullMask, take);
+            const uint32_t at = n + __popc(takers & ((1u << lane) - 1u));
+            if (take && at < kDense) {
+                dense[at] = key;
+                where[at] = (uint16_t)(w * kListCap + i);
+            }
+            n += __popc(takers);
+        }
+    }
+    __syncwarp();
+    if (n > kDense) return settle_wide(fin, hist, gathered, L, r);
+    constexpr int kOwned = kDense / 32;
+    uint64_t mine[kOwned];
+    uint32_t place[kOwned];
+#pragma unroll
+    for (int h = 0; h < kOwned; h++) {
+        const uint32_t e = lane + 32 * h;
+        mine[h] = e < n ? dense[e] : ~0ull;
+        place[h] = 0;
+    }
+    const uint32_t owned = (n + 31u) / 32u;
+#pragma unroll 4
+    for (uint32_t j = 0; j < n; j++) {
+        const uint64_t other = dense[j];
+#pragma unroll
+        for (int h = 0; h < kOwned; h++)
+            if ((uint32_t)h < owned) place[h] += other > mine[h] ? 1u : 0u;
+    }
+    __syncwarp();
+    const float *flat_score = &L.score[0][0];
+    const uint32_t *flat_id = &L.id[0][0];
+#pragma unroll
+    for (int h = 0; h < kOwned; h++) {
+        const uint32_t e = lane + 32 * h;
+        if (e < n && place[h] < r.k) {
+            const uint32_t from = where[e];
+            fin.score[place[h]] = flat_score[from];
+            fin.id[place[h]] = flat_id[from];
+        }
+    }
+    __syncwarp();
+    FGK_CTICK(11);
+    return min(n, r.k);
 }
 
 // A unit's lists become its part of the row's result; the CTA that finishes a row's last
@@ -1285,8 +1367,9 @@ __global__ void __launch_bounds__(kBlock, 1) persistent_select_kernel(const __gr
             lists[b].bound = 0;
             lists[b].first_key = 0xffffffffu;
             lists[b].first_count = 0;
+            lists[b].first_top = 0;
             lists[b].bad_history = 0;
-            for (int w = 0; w < kWarps; w++) lists[b].warp_kth[w] = 0;
+            for (int i = 0; i < kTallyBins; i++) lists[b].tally[i] = 0;
         }
         mbarrier_fence_init();
         sh.ring_error = 0;
@@ -1298,6 +1381,7 @@ __global__ void __launch_bounds__(kBlock, 1) persistent_select_kernel(const __gr
         // Closer c takes the units that use list set c: every other unit.
         const uint32_t closer = warp - (kWarps + kHistoryWarps);
         uint32_t served = 0;
+        FGK_CTICK_BEGIN;
         UnitWalk walk(p, tiles);
         Unit u;
         while (walk.next(u)) {
@@ -1314,16 +1398,19 @@ __global__ void __launch_bounds__(kBlock, 1) persistent_select_kernel(const __gr
             // (a wait that runs out leaves garbage lists: the row is failed through ring_error)
             bounded_wait(sh, &sh.ready[b], (served >> 1) & 1u, polls);
             __syncwarp();
+            FGK_CTICK(8);
             close_unit(sh, closer, L, p, u, r, cfg, shard_mode, row_status);
             __syncwarp();
+            FGK_CTICK(12);
             // the lists' shared words, clean for the unit after next (a warp that is ahead of
             // the others must not meet what they published for another row)
-            if (lane < (uint32_t)kWarps) L.warp_kth[lane] = 0;
+            for (uint32_t i = lane; i < (uint32_t)kTallyBins; i += 32) L.tally[i] = 0;
             __syncwarp();
             if (lane == 0) {
                 L.bound = 0;
                 L.first_key = 0xffffffffu;
                 L.first_count = 0;
+                L.first_top = 0;
                 L.bad_history = 0;
                 mbarrier_arrive(&sh.vacant[b]);
             }
@@ -1474,9 +1561,9 @@ __global__ void __launch_bounds__(kBlock, 1) persistent_select_kernel(const __gr
 
 #ifdef FGK_PHASE_CLOCKS
 extern "C" int fgk_read_persist_clocks(unsigned long long *out, int reset) {
-    cudaError_t e = cudaMemcpyFromSymbol(out, fgk::persist::fgk_persist_clocks, sizeof(unsigned long long) * 8);
+    cudaError_t e = cudaMemcpyFromSymbol(out, fgk::persist::fgk_persist_clocks, sizeof(unsigned long long) * 16);
     if (e == cudaSuccess && reset) {
-        unsigned long long zero[8] = {0};
+        unsigned long long zero[16] = {0};
         e = cudaMemcpyToSymbol(fgk::persist::fgk_persist_clocks, zero, sizeof(zero));
     }
     return (int)e;
