@@ -58,10 +58,14 @@ constexpr int kStages = FGK_RING_STAGES;        // tiles in flight per consumer 
 constexpr uint32_t kTileLogits = FGK_RING_TILE_LOGITS;  // logits per tile: at most 64 per lane, a bit each in a mask
 constexpr uint32_t kStageBytes = kTileLogits * 4;  // a stage holds a tile of the widest type
 #ifndef FGK_RING_LIST_CAP
-#define FGK_RING_LIST_CAP 256
+#define FGK_RING_LIST_CAP 128
 #endif
 constexpr int kListCap = FGK_RING_LIST_CAP;     // entries of one warp's candidate list (a multiple of 32, > 64)
 constexpr int kListWords = kListCap / 32;
+#ifndef FGK_X_SETS
+#define FGK_X_SETS 3
+#endif
+constexpr int kListSets = FGK_X_SETS;           // units whose lists exist at a time: one being filled, the others being closed
 constexpr int kTallyBins = 256;                 // bins of the per-unit score tally (eight per lane)
 constexpr int kBlock = (kWarps + kHistoryWarps + kClosers) * 32;
 constexpr uint32_t kDefaultPolls = 1u << 21;    // polls before a wait gives up: a second or two
@@ -221,8 +225,8 @@ struct Shared {
     uint32_t hist[kClosers][256];
     uint32_t gathered[kClosers];
     alignas(8) uint64_t full[kWarps][kStages];  // "the tile has landed"
-    alignas(8) uint64_t ready[2];            // "every consumer warp is through with the unit"
-    alignas(8) uint64_t vacant[2];           // "the closing warp is done with the lists"
+    alignas(8) uint64_t ready[kListSets];    // "every consumer warp is through with the unit"
+    alignas(8) uint64_t vacant[kListSets];   // "the closing warp is done with the lists"
     alignas(8) uint64_t bitmap_ready[3];     // "the unit's history bitmap is complete"
     alignas(8) uint64_t bitmap_free[3];      // "every consumer warp is through with the bitmap buffer"
     uint32_t history_bad[3];                 // status a broken history earns the unit, by bitmap buffer
@@ -944,12 +948,20 @@ __device__ __forceinline__ uint32_t consume_unit(const Params &p, Shared &sh, Li
                 if ((uint32_t)(v8 * 32) + lane >= valid_vectors) hot &= ~(1u << v8);
         }
         FGK_PTICK(3);
+#ifdef FGK_X_NO_COLLECT
+        if (__any_sync(kFullMask, hot == 0xdeadbeefu))
+#else
         if (__any_sync(kFullMask, hot != 0))
+#endif
             bound = collect<T, kGreedy>(L, r, bitmap, tile, column0, valid_vectors, w, hot, bound, tally);
         FGK_PTICK(6);
         // The bound tightens as the row is read: the warps take turns, one after every round of
         // tiles, to see what the tally of all the warps' exact entries allows.  Nobody waits.
+#ifdef FGK_X_NO_RAISE
+        if (r.k > 1000u && done == turn) {
+#else
         if (r.k > 1u && done == turn) {
+#endif
             raise_bound(L, tally, r.k);
             turn += participants;
         }
@@ -1200,6 +1212,10 @@ __device__ __noinline__ void close_unit(Shared &sh, uint32_t closer, Lists &L, c
     const uint32_t lane = lane_id();
     const uint32_t row = u.row;
     FinishBuffer &fin = sh.fin[closer];
+#ifdef FGK_X_NO_CLOSE
+    if (lane_id() == 0) report_row(p.out, u.row, kOk, 0u, 0.0f);
+    return;
+#endif
     uint32_t kept = settle_lists(fin, sh.hist[closer], &sh.gathered[closer], L, r);
     uint32_t bad_history = row_status ? row_status : L.bad_history;
     if (peek(&sh.ring_error)) {  // a tile never landed, or a warp never came
@@ -1337,13 +1353,69 @@ __device__ __noinline__ void close_unit(Shared &sh, uint32_t closer, Lists &L, c
     finish_select(fin, kept, cfg, p.uniforms[row], row, p.out);
 }
 
+// One warp's share (`part` of `parts`) of a unit's history bitmap.  First the words of the
+// unit's columns are cleared, or fetched from the session's bitmap; once all the warps that
+// share the work have met (`meet`), the tokens are marked.  A token outside the vocabulary
+// leaves its status in *bad.
+template <class Meet>
+__device__ __forceinline__ void build_bitmap(const Params &p, const Row &r, const Unit &u, uint32_t *bitmap,
+                                             uint32_t part, uint32_t parts, uint32_t *bad_word, Meet meet) {
+    const uint32_t lane = lane_id();
+    const uint32_t column_begin = u.first * kTileLogits;
+    const uint32_t column_end = min(p.vocab, u.end * kTileLogits);
+    uint4 *wide = reinterpret_cast<uint4 *>(bitmap);
+    const uint32_t quad_end = (column_end + 127u) / 128u;
+    if (r.table_bitmap != nullptr) {  // the session keeps its bitmap: fetch the unit's part of it
+        const uint4 *kept = reinterpret_cast<const uint4 *>(r.table_bitmap);
+        for (uint32_t q = column_begin / 128u + part * 32 + lane; q < quad_end; q += 32 * parts)
+            wide[q] = __ldg(&kept[q]);
+    } else {
+        for (uint32_t q = column_begin / 128u + part * 32 + lane; q < quad_end; q += 32 * parts)
+            wide[q] = make_uint4(0, 0, 0, 0);
+    }
+    meet();
+    constexpr int kBatch = 16;  // tokens per lane and trip, loaded before any is used
+    uint32_t bad = 0;
+    for (uint32_t base = part * kBatch * 32; base < r.history_len; base += parts * kBatch * 32) {
+        uint32_t token[kBatch];
+#pragma unroll
+        for (int q = 0; q < kBatch; q++) {
+            const uint32_t at = base + q * 32 + lane;
+            token[q] = at < r.history_len ? r.tokens[at] : p.vocab_offset + column_end;
+        }
+#pragma unroll
+        for (int q = 0; q < kBatch; q++) {
+            if (base + q * 32 + lane >= r.history_len) continue;
+            if (token[q] >= p.vocab_total) bad = kErrFormat;
+            const uint32_t local = token[q] - p.vocab_offset;  // wraps for ids below the span
+            if (local >= column_begin && local < column_end) {
+                const uint32_t bit = 1u << (local & 31u);
+                if ((bitmap[local >> 5] & bit) == 0) atomicOr(&bitmap[local >> 5], bit);
+            }
+        }
+    }
+    if (__any_sync(kFullMask, bad != 0) && lane == 0) atomicOr(bad_word, kErrFormat);
+}
+// Where the warps that share a bitmap's work meet: the history warps among themselves, or --
+// for a CTA's first unit, when the consumer warps have nothing to read yet -- all of them.
+struct HistoryWarpsMeet {
+    __device__ __forceinline__ void operator()() const {
+        asm volatile("bar.sync 2, %0;" ::"n"(kHistoryWarps * 32) : "memory");
+    }
+};
+struct EverybodyMeets {
+    __device__ __forceinline__ void operator()() const {
+        asm volatile("bar.sync 3, %0;" ::"n"((kWarps + kHistoryWarps) * 32) : "memory");
+    }
+};
+
 template <typename T>
 __global__ void __launch_bounds__(kBlock, 1) persistent_select_kernel(const __grid_constant__ Params p) {
     extern __shared__ __align__(128) unsigned char dynamic[];
     __shared__ Shared sh;
     unsigned char *ring = dynamic;
     Lists *lists = reinterpret_cast<Lists *>(dynamic + (size_t)kWarps * kStages * kStageBytes);
-    uint32_t *bitmaps = reinterpret_cast<uint32_t *>(dynamic + (size_t)kWarps * kStages * kStageBytes + 2 * sizeof(Lists));
+    uint32_t *bitmaps = reinterpret_cast<uint32_t *>(dynamic + (size_t)kWarps * kStages * kStageBytes + kListSets * sizeof(Lists));
     const uint32_t bitmap_stride = ((p.bitmap_words + 3u) / 4u) * 4u;  // words, a whole number of uint4
 
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
@@ -1361,7 +1433,7 @@ __global__ void __launch_bounds__(kBlock, 1) persistent_select_kernel(const __gr
             mbarrier_init(&sh.bitmap_free[b], kWarps);
             sh.history_bad[b] = 0;
         }
-        for (int b = 0; b < 2; b++) {
+        for (int b = 0; b < kListSets; b++) {
             mbarrier_init(&sh.ready[b], kWarps);
             mbarrier_init(&sh.vacant[b], 1);
             lists[b].bound = 0;
@@ -1387,16 +1459,16 @@ __global__ void __launch_bounds__(kBlock, 1) persistent_select_kernel(const __gr
         while (walk.next(u)) {
             const SamplerConfig cfg = row_config(p, u.row);
             if (!row_is_ours(cfg, shard_mode)) continue;
-            const uint32_t b = served & 1u;
-            if (b != closer) {
+            if ((served & 1u) != closer) {
                 served++;
                 continue;
             }
+            const uint32_t b = served % kListSets;
             uint32_t row_status;
             const Row r = make_row(p, cfg, u.row, shard_mode, &row_status);
             Lists &L = lists[b];
             // (a wait that runs out leaves garbage lists: the row is failed through ring_error)
-            bounded_wait(sh, &sh.ready[b], (served >> 1) & 1u, polls);
+            bounded_wait(sh, &sh.ready[b], (served / kListSets) & 1u, polls);
             __syncwarp();
             FGK_CTICK(8);
             close_unit(sh, closer, L, p, u, r, cfg, shard_mode, row_status);
@@ -1437,43 +1509,17 @@ __global__ void __launch_bounds__(kBlock, 1) persistent_select_kernel(const __gr
             // the consumers must be through with the unit that used the buffer last (each buffer
             // has a barrier of its own: one phase per use, however far the consumers have got)
             if (served >= buffers) bounded_wait(sh, &sh.bitmap_free[slot], (served / buffers - 1u) & 1u, polls);
-            if (helper == 0 && lane == 0) sh.history_bad[slot] = 0;
+            if (helper == 0 && lane == 0 && served != 0) sh.history_bad[slot] = 0;
             if (r.seen_any) {
                 uint32_t *bitmap = bitmaps + (size_t)slot * bitmap_stride;
-                const uint32_t column_begin = u.first * kTileLogits;
-                const uint32_t column_end = min(p.vocab, u.end * kTileLogits);
-                uint4 *wide = reinterpret_cast<uint4 *>(bitmap);
-                const uint32_t quad_end = (column_end + 127u) / 128u;
-                if (r.table_bitmap != nullptr) {  // the session keeps its bitmap: fetch the unit's part of it
-                    const uint4 *kept = reinterpret_cast<const uint4 *>(r.table_bitmap);
-                    for (uint32_t q = column_begin / 128u + helper * 32 + lane; q < quad_end; q += 32 * kHistoryWarps)
-                        wide[q] = __ldg(&kept[q]);
+                if (served == 0) {
+                    // the CTA's first unit: the consumer warps lend a hand (see below)
+                    build_bitmap(p, r, u, bitmap, kWarps + helper, kWarps + kHistoryWarps, &sh.history_bad[slot],
+                                 EverybodyMeets());
+                    EverybodyMeets()();  // everybody's marks are in
                 } else {
-                    for (uint32_t q = column_begin / 128u + helper * 32 + lane; q < quad_end; q += 32 * kHistoryWarps)
-                        wide[q] = make_uint4(0, 0, 0, 0);
+                    build_bitmap(p, r, u, bitmap, helper, kHistoryWarps, &sh.history_bad[slot], HistoryWarpsMeet());
                 }
-                asm volatile("bar.sync 2, %0;" ::"n"(kHistoryWarps * 32) : "memory");
-                constexpr int kBatch = 16;  // tokens per lane and trip, loaded before any is used
-                uint32_t bad = 0;
-                for (uint32_t base = helper * kBatch * 32; base < r.history_len; base += kHistoryWarps * kBatch * 32) {
-                    uint32_t token[kBatch];
-#pragma unroll
-                    for (int q = 0; q < kBatch; q++) {
-                        const uint32_t at = base + q * 32 + lane;
-                        token[q] = at < r.history_len ? r.tokens[at] : p.vocab_offset + column_end;
-                    }
-#pragma unroll
-                    for (int q = 0; q < kBatch; q++) {
-                        if (base + q * 32 + lane >= r.history_len) continue;
-                        if (token[q] >= p.vocab_total) bad = kErrFormat;
-                        const uint32_t local = token[q] - p.vocab_offset;  // wraps for ids below the span
-                        if (local >= column_begin && local < column_end) {
-                            const uint32_t bit = 1u << (local & 31u);
-                            if ((bitmap[local >> 5] & bit) == 0) atomicOr(&bitmap[local >> 5], bit);
-                        }
-                    }
-                }
-                if (__any_sync(kFullMask, bad != 0) && lane == 0) atomicOr(&sh.history_bad[slot], kErrFormat);
             }
             __threadfence_block();
             __syncwarp();
@@ -1492,6 +1538,22 @@ __global__ void __launch_bounds__(kBlock, 1) persistent_select_kernel(const __gr
 #pragma unroll
     for (int s = 0; s < kStages; s++)
         feeder.template issue<T>(p, stages + (size_t)s * kStageBytes, &sh.full[w][s], row_bytes, w, shard_mode, policy);
+    {
+        // The CTA's first unit: nothing has landed yet, so the consumer warps help the history
+        // warps with its bitmap (every warp comes to the same decision from the same inputs).
+        UnitWalk ahead(p, tiles);
+        Unit u0;
+        bool found = false;
+        while (!found && ahead.next(u0)) found = row_is_ours(row_config(p, u0.row), shard_mode);
+        if (found) {
+            uint32_t ignored;
+            const Row r0 = make_row(p, row_config(p, u0.row), u0.row, shard_mode, &ignored);
+            if (r0.seen_any) {
+                build_bitmap(p, r0, u0, bitmaps, w, kWarps + kHistoryWarps, &sh.history_bad[0], EverybodyMeets());
+                EverybodyMeets()();
+            }
+        }
+    }
     uint32_t consumed = 0;  // tiles of this warp so far
     uint32_t served = 0;    // units before this one
 #ifdef FGK_PHASE_CLOCKS
@@ -1505,12 +1567,12 @@ __global__ void __launch_bounds__(kBlock, 1) persistent_select_kernel(const __gr
         if (!row_is_ours(cfg, shard_mode)) continue;
         uint32_t row_status;
         const Row r = make_row(p, cfg, u.row, shard_mode, &row_status);
-        const uint32_t b = served & 1u;
+        const uint32_t b = served % kListSets;
         Lists &L = lists[b];
         const uint32_t slot = served % buffers;
         const uint32_t *bitmap = bitmaps + (size_t)slot * bitmap_stride;
         // the closing warp must be done with these lists (it had them two units ago)
-        if (served >= 2u) bounded_wait(sh, &sh.vacant[b], ((served >> 1) - 1u) & 1u, polls);
+        if (served >= (uint32_t)kListSets) bounded_wait(sh, &sh.vacant[b], (served / kListSets - 1u) & 1u, polls);
         if (lane < (uint32_t)kListWords) L.deferred[w][lane] = 0;
         if (lane == 0) {
             L.count[w] = 0;
@@ -1629,7 +1691,7 @@ static persist::Params to_persist_params(const fgk_stream_launch *l) {
 // sets of lists and as many bitmap buffers as fit, three at most.  0: not even one.
 extern "C" uint64_t fgk_persistent_dynamic_smem(uint32_t bitmap_words, uint32_t *bitmap_buffers) {
     const uint64_t fixed = (uint64_t)persist::kWarps * persist::kStages * persist::kStageBytes +
-                           2u * sizeof(persist::Lists);
+                           persist::kListSets * sizeof(persist::Lists);
     const uint64_t bitmap = (((uint64_t)bitmap_words + 3u) / 4u) * 16u;
     const uint64_t room = persist::kSharedLimit - sizeof(persist::Shared) - 256u;
     uint32_t buffers = 3;
