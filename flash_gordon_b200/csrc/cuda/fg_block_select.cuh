@@ -258,8 +258,21 @@ __device__ inline void finish_select(FinishBuffer &fin, uint32_t n, const Sample
         }
         return;
     }
+    // Every lane has at most two candidates (n <= 64).  Their four exponentials -- the raw
+    // and the tempered weight of each, the latter wanted only below the top-p cut, which is not
+    // known yet -- do not wait for one another, so they are all started here.
+    static_assert(kMaxK <= 64, "two candidates per lane");
     const double top_raw = (double)fin.score[0];
-    for (uint32_t i = lane; i < n; i += 32) fin.raw[i] = exp((double)fin.score[i] - top_raw);
+    const double temperature = (double)cfg.temperature;
+    const double top_tempered = (double)fin.score[0] / temperature;
+    const uint32_t i0 = lane, i1 = lane + 32;
+    const double s0 = i0 < n ? (double)fin.score[i0] : top_raw;
+    const double s1 = i1 < n ? (double)fin.score[i1] : top_raw;
+    double raw0 = exp(s0 - top_raw), raw1 = exp(s1 - top_raw);
+    const double tempered0 = exp(s0 / temperature - top_tempered);
+    const double tempered1 = exp(s1 / temperature - top_tempered);
+    if (i0 < n) fin.raw[i0] = raw0;
+    if (i1 < n) fin.raw[i1] = raw1;
     __syncwarp();
     // the sums run left to right on one lane, as the C code's loops do; the divisions
     // are independent of one another and spread over the warp
@@ -267,8 +280,12 @@ __device__ inline void finish_select(FinishBuffer &fin, uint32_t n, const Sample
     if (lane == 0) raw_sum = ordered_sum(fin.raw, n);
     raw_sum = __shfl_sync(kFullMask, raw_sum, 0);
     const bool raw_ok = raw_sum > 0.0 && !isinf(raw_sum) && !isnan(raw_sum);
-    if (raw_ok)
-        for (uint32_t i = lane; i < n; i += 32) fin.raw[i] = fin.raw[i] / raw_sum;
+    if (raw_ok) {
+        raw0 = raw0 / raw_sum;
+        raw1 = raw1 / raw_sum;
+        if (i0 < n) fin.raw[i0] = raw0;
+        if (i1 < n) fin.raw[i1] = raw1;
+    }
     __syncwarp();
     if (lane == 0) {
         uint32_t cutoff = n;
@@ -285,10 +302,8 @@ __device__ inline void finish_select(FinishBuffer &fin, uint32_t n, const Sample
         return;
     }
     const uint32_t cutoff = fin.cutoff;
-    const double temperature = (double)cfg.temperature;
-    const double top_tempered = (double)fin.score[0] / temperature;
-    for (uint32_t i = lane; i < n; i += 32)
-        fin.tempered[i] = i < cutoff ? exp((double)fin.score[i] / temperature - top_tempered) : 0.0;
+    if (i0 < n) fin.tempered[i0] = i0 < cutoff ? tempered0 : 0.0;
+    if (i1 < n) fin.tempered[i1] = i1 < cutoff ? tempered1 : 0.0;
     __syncwarp();
     if (lane == 0) {
         const double weight_sum = ordered_sum(fin.tempered, cutoff);

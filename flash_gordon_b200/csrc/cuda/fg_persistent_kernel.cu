@@ -734,9 +734,6 @@ __device__ __noinline__ uint64_t collect(Lists &L, const Row r, const uint32_t *
         }
         take |= (uint64_t)bits << (u * kPer);
     }
-#ifdef FGK_PHASE_CLOCKS
-    if (lane == 0) atomicAdd(&fgk_persist_clocks[14], 1ull);
-#endif
     for (;;) {
         bool stuck = false;
         while (take != 0 && !stuck) {
@@ -765,9 +762,6 @@ __device__ __noinline__ uint64_t collect(Lists &L, const Row r, const uint32_t *
                 }
                 L.score[w][slot] = kind == 2u ? x : value;
                 L.id[w][slot] = id;
-#ifdef FGK_PHASE_CLOCKS
-                atomicAdd(&fgk_persist_clocks[13], 1ull);
-#endif
                 if (kind == 2u) {
                     atomicOr(&L.deferred[w][slot >> 5], 1u << (slot & 31u));
                 } else if (r.k == 1u) {
@@ -1350,7 +1344,11 @@ __device__ __noinline__ void close_unit(Shared &sh, uint32_t closer, Lists &L, c
         }
         return;
     }
+#ifdef FGK_PHASE_CLOCKS
+    long long ctick = clock64();
+#endif
     finish_select(fin, kept, cfg, p.uniforms[row], row, p.out);
+    FGK_CTICK(13);
 }
 
 // One warp's share (`part` of `parts`) of a unit's history bitmap.  First the words of the
