@@ -23,19 +23,6 @@
 
 namespace fgk {
 
-#ifdef FGK_PHASE_CLOCKS
-__device__ unsigned long long fgk_nucleus_clocks[8];
-#define FGK_NTICK(slot)                                                            \
-    do {                                                                            \
-        if (threadIdx.x == 0) {                                                     \
-            const long long now = clock64();                                        \
-            atomicAdd(&fgk_nucleus_clocks[slot], (unsigned long long)(now - tick)); \
-            tick = now;                                                             \
-        }                                                                           \
-    } while (0)
-#else
-#define FGK_NTICK(slot) do { } while (0)
-#endif
 
 constexpr int kNucleusThreads = 1024;
 constexpr int kBuckets = 4096;
@@ -449,9 +436,6 @@ __device__ Position locate(NucleusShared &sh, NucleusList &list, const float *va
     const uint32_t tid = threadIdx.x;
     Position found;
     found.ok = false;
-#ifdef FGK_PHASE_CLOCKS
-    const long long entered = clock64();
-#endif
     clear_histogram(sh, kBuckets);
     walk_row(values, vocab, [&](float v, uint32_t i) {
         if (is_nonfinite(v) || !inside.holds(float_key(v), i)) return;
@@ -461,10 +445,6 @@ __device__ Position locate(NucleusShared &sh, NucleusList &list, const float *va
         atomicAdd(&sh.count[b], 1u);
     });
     __syncthreads();
-#ifdef FGK_PHASE_CLOCKS
-    long long tick = clock64();
-    if (threadIdx.x == 0) atomicAdd(&fgk_nucleus_clocks[4], (unsigned long long)(tick - entered));
-#endif
     const unsigned long long target = find_crossing_up(sh, target_of, strict);
     found.total = sh.total_mass;
     bool clipped = false;
@@ -511,7 +491,6 @@ __device__ Position locate(NucleusShared &sh, NucleusList &list, const float *va
         list.id[slot] = i;
     });
     __syncthreads();
-    FGK_NTICK(5);
     // order them: rank by counting, (value descending, id ascending); -0.0 and +0.0 tie
     for (uint32_t a = tid; a < members; a += kNucleusThreads) {
         const float v = list.value[a];
@@ -561,10 +540,6 @@ __device__ Position locate(NucleusShared &sh, NucleusList &list, const float *va
     found.rank = rank_before + at + 1;
     found.ok = true;
     __syncthreads();
-    FGK_NTICK(6);
-#ifdef FGK_PHASE_CLOCKS
-    if (threadIdx.x == 0) atomicAdd(&fgk_nucleus_clocks[7], (unsigned long long)members);
-#endif
     return found;
 }
 
@@ -582,13 +557,9 @@ __global__ void __launch_bounds__(kNucleusThreads, 1) nucleus_select_kernel(cons
     NucleusList &list = *reinterpret_cast<NucleusList *>(histogram_memory + kNucleusHistogramBytes);
     __syncthreads();
 
-#ifdef FGK_PHASE_CLOCKS
-    long long tick = clock64();
-#endif
     for (uint32_t row = blockIdx.x; row < p.rows; row += gridDim.x) {
         const SamplerConfig cfg = p.config_count > 1 ? p.configs[row] : p.config0;
         if (cfg.temperature == 0.0f || cfg.top_k != 0) continue;  // the streaming kernel's rows
-        FGK_NTICK(0);
 
         // ---- pass 1: HBM -> penalised fp32 row in scratch, maximum on the way ----
         const T *columns = static_cast<const T *>(p.logits) + (size_t)row * p.row_stride;
@@ -695,7 +666,6 @@ __global__ void __launch_bounds__(kNucleusThreads, 1) nucleus_select_kernel(cons
             continue;
         }
 
-        FGK_NTICK(1);
         // ---- top-p on the un-tempered softmax: where does the mass reach top_p? ----
         Nucleus all;
         all.everything = true;
@@ -736,7 +706,6 @@ __global__ void __launch_bounds__(kNucleusThreads, 1) nucleus_select_kernel(cons
                     &nucleus.id, &mass_at_cut, &size);
         }
 
-        FGK_NTICK(2);
         // ---- temperature weights of the nucleus, then the draw ----
         const double inv_t = 1.0 / (double)cfg.temperature;
         float u = p.uniforms[row];
@@ -773,7 +742,6 @@ __global__ void __launch_bounds__(kNucleusThreads, 1) nucleus_select_kernel(cons
             descend(sh, values, p.vocab, inv_t, (double)best, nucleus, draw_target(weight_sum), true,
                     &picked_key, &picked_id, &picked_mass, &picked_rank);
         }
-        FGK_NTICK(3);
         if (tid == 0) {
             if (weight_sum == 0 || raw_sum == 0 || picked_id >= p.vocab) {
                 report_row(p.out, row, kErrFormat, kPaddingId, 0.0f);
@@ -790,16 +758,6 @@ __global__ void __launch_bounds__(kNucleusThreads, 1) nucleus_select_kernel(cons
 
 using namespace fgk;
 
-#ifdef FGK_PHASE_CLOCKS
-extern "C" int fgk_read_nucleus_clocks(unsigned long long *out, int reset) {
-    cudaError_t e = cudaMemcpyFromSymbol(out, fgk::fgk_nucleus_clocks, sizeof(unsigned long long) * 8);
-    if (e == cudaSuccess && reset) {
-        unsigned long long zero[8] = {0};
-        e = cudaMemcpyToSymbol(fgk::fgk_nucleus_clocks, zero, sizeof(zero));
-    }
-    return (int)e;
-}
-#endif
 
 static constexpr size_t kNucleusDynamic = kNucleusHistogramBytes + sizeof(NucleusList);
 

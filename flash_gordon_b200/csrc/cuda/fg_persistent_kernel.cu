@@ -6,34 +6,39 @@
 //                       the copy engine itself (cp.async.bulk + mbarrier) for every 8th
 //                       2048-logit tile of the row: as soon as a stage has been looked at
 //                       it is asked to fetch the warp's next tile -- of this row or the
-//                       next -- so 128 KB are always on their way to the SM and no warp ever
+//                       next -- so 64 KB are always on their way to the SM and no warp ever
 //                       waits for another one's tile.  Per tile and lane: sixteen 128-bit
 //                       shared loads, a maximum and one compare per vector; single elements
-//                       are looked at only above the admission bound and go to the warp's
-//                       own candidate list (slots handed out by ballot, no atomics).
-//   2 history warps     build the bitmap of the NEXT row's token history in the other of
-//                       two bitmap buffers while the consumers stream the current row.
+//                       are looked at only at or above the admission bound and go to the
+//                       warp's own candidate list.
+//   2 history warps     build the bitmaps of the next rows' token histories, up to three rows
+//                       ahead, while the consumers stream the current row.  (A CTA's first
+//                       bitmap is everybody's work: the consumers have nothing to read yet.)
 //   2 closing warps     turn the lists of a finished row into its result (exact k best, the
 //                       select step of src/sampler.c:80-122), taking rows in turn, while
-//                       the consumers fill the other set of lists with the next row.
+//                       the consumers fill another of the three sets of lists.
 //
 // The warps of a row share one number, the admission bound: a 64-bit (score, ~id) key T
 // such that at least k elements of the row are known to have a key >= T.  It starts from
 // the warps' first tiles (each publishes the j-th largest of its lanes' maxima over ids
-// the history has not seen, j = ceil(k / warps); the smallest of them bounds k elements)
-// and rises whenever a warp whose list is full keeps its own k best.  A stale bound is
-// still a bound, so nobody waits for anybody after the first tile.
+// the history has not seen, j = ceil(k / warps); the smallest of them bounds k elements).
+// From then on every entry that goes on a list with its exact value is counted in a tally
+// by score (256 bins between the first bound and the largest score of the first tiles); after
+// every round of tiles one warp reads the tally and lifts the bound to the lower edge of the
+// highest bin that, with the bins above it, holds k entries.  A row that wants a single
+// candidate lifts the bound to every better candidate directly.  A stale bound is still a
+// bound, so nobody waits for anybody after the first tile.
 //
 // The kernel takes rows whose penalties can only lower a logit (presence >= 0,
 // frequency >= 0, repetition >= 1, or no penalties / no history at all).  Then a raw
 // value below the bound stays below, so the history matters only for the few values
-// above it.  An id that was seen is charged  frequency * count + presence
+// at or above it.  An id that was seen is charged  frequency * count + presence
 // (src/sampler.c:52-58); the count is not tabulated per row (src/output.c:601-617 keeps a
 // vocabulary-wide table per session): the entry keeps its raw logit, is ordered by the
 // charge for count = 1 -- an upper bound of its value -- and its occurrences are counted
-// in the token list only if that upper bound reaches the k best.  Everything else
-// (penalties that can raise a logit, rows that are not 16-byte aligned, column splits)
-// stays with stream_select_kernel.
+// in the token list only if that upper bound reaches the bound the row ends with.
+// Everything else (penalties that can raise a logit, rows that are not 16-byte aligned,
+// column splits) stays with stream_select_kernel.
 #include <cstring>
 
 #include "fg_block_select.cuh"
@@ -42,30 +47,15 @@
 namespace fgk {
 namespace persist {
 
-#ifndef FGK_RING_WARPS
-#define FGK_RING_WARPS 8
-#endif
-#ifndef FGK_RING_STAGES
-#define FGK_RING_STAGES 2
-#endif
-constexpr int kWarps = FGK_RING_WARPS;          // consumer warps
+constexpr int kWarps = 8;                       // consumer warps
 constexpr int kHistoryWarps = 2;
 constexpr int kClosers = 2;
-constexpr int kStages = FGK_RING_STAGES;        // tiles in flight per consumer warp
-#ifndef FGK_RING_TILE_LOGITS
-#define FGK_RING_TILE_LOGITS 2048
-#endif
-constexpr uint32_t kTileLogits = FGK_RING_TILE_LOGITS;  // logits per tile: at most 64 per lane, a bit each in a mask
+constexpr int kStages = 2;                      // stages per consumer warp: one tile being looked at, one on its way
+constexpr uint32_t kTileLogits = 2048;          // logits per tile: at most 64 per lane, a bit each in a mask
 constexpr uint32_t kStageBytes = kTileLogits * 4;  // a stage holds a tile of the widest type
-#ifndef FGK_RING_LIST_CAP
-#define FGK_RING_LIST_CAP 128
-#endif
-constexpr int kListCap = FGK_RING_LIST_CAP;     // entries of one warp's candidate list (a multiple of 32, > 64)
+constexpr int kListCap = 128;                   // entries of one warp's candidate list (a multiple of 32, > 64)
 constexpr int kListWords = kListCap / 32;
-#ifndef FGK_X_SETS
-#define FGK_X_SETS 3
-#endif
-constexpr int kListSets = FGK_X_SETS;           // units whose lists exist at a time: one being filled, the others being closed
+constexpr int kListSets = 3;                    // units whose lists exist at a time: one being filled, two being closed
 constexpr int kTallyBins = 256;                 // bins of the per-unit score tally (eight per lane)
 constexpr int kBlock = (kWarps + kHistoryWarps + kClosers) * 32;
 constexpr uint32_t kDefaultPolls = 1u << 21;    // polls before a wait gives up: a second or two
@@ -201,8 +191,8 @@ struct UnitWalk {
     }
 };
 
-// What the consumers collect for one unit: one private list per warp.  There are two of
-// these: while the closing warp turns one into a result the consumers fill the other.
+// What the consumers collect for one unit: one private list per warp.  There are three of
+// these: while the closing warps turn two into results the consumers fill the third.
 // An entry is (score, id); when its bit in `deferred` is up the score is the RAW logit of
 // an id the history has seen, whose occurrences have not been counted yet.  An entry whose
 // id is the padding id is dead.
@@ -282,32 +272,6 @@ __device__ __forceinline__ bool tile_wait(Shared &sh, uint64_t *barrier, uint32_
     return false;
 }
 
-#ifdef FGK_PHASE_CLOCKS
-// Build with -DFGK_PHASE_CLOCKS to learn where the consumer warps' cycles go: slot 0 waits
-// for the lists and the bitmap, 1 waits for tiles, 2 first bound (with its wait for the
-// other warps), 3 tiles against the bound, 4 asking for the next tile, 5 end of unit,
-// 6 candidates onto the list, 7 exact values and the warp's j-th best.
-__device__ unsigned long long fgk_persist_clocks[16];
-// closing warps: 8 waiting for a unit, 9 threshold selection, 10 counting occurrences,
-// 11 gather and sort, 12 the rest of a unit's close
-#define FGK_CTICK(slot)                                                            \
-    do {                                                                            \
-        const long long now_ = clock64();                                           \
-        if (lane_id() == 0) atomicAdd(&fgk_persist_clocks[slot], (unsigned long long)(now_ - ctick)); \
-        ctick = now_;                                                               \
-    } while (0)
-#define FGK_CTICK_BEGIN long long ctick = clock64()
-#define FGK_PTICK(slot)                          \
-    do {                                          \
-        const long long now = clock64();          \
-        phase[slot] += (unsigned long long)(now - tick); \
-        tick = now;                               \
-    } while (0)
-#else
-#define FGK_PTICK(slot) do { } while (0)
-#define FGK_CTICK(slot) do { } while (0)
-#define FGK_CTICK_BEGIN do { } while (0)
-#endif
 
 __device__ __forceinline__ uint64_t warp_max_u64(uint64_t v) {
 #pragma unroll
@@ -775,9 +739,6 @@ __device__ __noinline__ uint64_t collect(Lists &L, const Row r, const uint32_t *
         }
         if (!__any_sync(kFullMask, stuck)) break;
         __syncwarp();
-#ifdef FGK_PHASE_CLOCKS
-        if (lane == 0) atomicAdd(&fgk_persist_clocks[15], 1ull);
-#endif
         bound = max(bound, local_cut(L, r, w));
         bound = max(bound, (uint64_t)peek64(&L.bound));
         tau = key_to_float((uint32_t)(bound >> 32));
@@ -884,9 +845,6 @@ __device__ __forceinline__ uint32_t consume_unit(const Params &p, Shared &sh, Li
                                               const uint32_t *bitmap, unsigned char *stages, Feeder &feeder,
                                               uint32_t consumed, uint32_t w, uint32_t tiles, uint32_t row_bytes,
                                               bool shard_mode, uint64_t policy, uint32_t polls
-#ifdef FGK_PHASE_CLOCKS
-                                              , unsigned long long *phase, long long &tick
-#endif
 ) {
     using V = Lanes<T>;
     constexpr int kPer = V::kPer;
@@ -904,7 +862,6 @@ __device__ __forceinline__ uint32_t consume_unit(const Params &p, Shared &sh, Li
     for (uint32_t t = u.first + w; t < u.end; t += kWarps) {
         const uint32_t stage = consumed % kStages;
         tile_wait(sh, &sh.full[w][stage], (consumed / kStages) & 1u, polls);
-        FGK_PTICK(1);
         const unsigned char *tile = stages + (size_t)stage * kStageBytes;
         const uint32_t valid_vectors = t + 1 == tiles ? last_vectors : whole;
         const uint32_t column0 = t * kTileLogits;
@@ -913,7 +870,6 @@ __device__ __forceinline__ uint32_t consume_unit(const Params &p, Shared &sh, Li
                 first_bound<T>(sh, L, r, bitmap, tile, column0, valid_vectors, participants, polls);
             bound = (uint64_t)first.key << 32;
             tally.span(first.key, first.top);
-            FGK_PTICK(2);
         }
         bound = max(bound, (uint64_t)peek64(&L.bound));
         const float tau = key_to_float((uint32_t)(bound >> 32));
@@ -941,38 +897,26 @@ __device__ __forceinline__ uint32_t consume_unit(const Params &p, Shared &sh, Li
             for (int v8 = 0; v8 < kVectors; v8++)
                 if ((uint32_t)(v8 * 32) + lane >= valid_vectors) hot &= ~(1u << v8);
         }
-        FGK_PTICK(3);
-#ifdef FGK_X_NO_COLLECT
-        if (__any_sync(kFullMask, hot == 0xdeadbeefu))
-#else
         if (__any_sync(kFullMask, hot != 0))
-#endif
             bound = collect<T, kGreedy>(L, r, bitmap, tile, column0, valid_vectors, w, hot, bound, tally);
-        FGK_PTICK(6);
         // The bound tightens as the row is read: the warps take turns, one after every round of
         // tiles, to see what the tally of all the warps' exact entries allows.  Nobody waits.
-#ifdef FGK_X_NO_RAISE
-        if (r.k > 1000u && done == turn) {
-#else
         if (r.k > 1u && done == turn) {
-#endif
             raise_bound(L, tally, r.k);
             turn += participants;
         }
         done++;
         __syncwarp();
-        FGK_PTICK(7);
         consumed++;
         feeder.template issue<T>(p, stages + (size_t)stage * kStageBytes, &sh.full[w][stage], row_bytes, w,
                                  shard_mode, policy);
-        FGK_PTICK(4);
     }
     return consumed;
 }
 
 // ------------------------------------------------------------------ closing warp
 
-// The key such that exactly k exact entries of the sixteen lists lie at or above it
+// The key such that exactly k exact entries of the lists lie at or above it
 // (0: there are at most k).  256-bin histogram passes over the range the k-th best can
 // still lie in; each narrows the range to one bin.
 __device__ __noinline__ uint64_t select_threshold(uint32_t *hist, const Lists &L, const Row r) {
@@ -1057,10 +1001,8 @@ __device__ __noinline__ uint32_t settle_wide(FinishBuffer &fin, uint32_t *hist, 
                                             const Row r) {
     const uint32_t lane = lane_id();
     uint64_t threshold;
-    FGK_CTICK_BEGIN;
     for (;;) {
         threshold = select_threshold(hist, L, r);
-        FGK_CTICK(9);
         // entries not counted yet whose upper bound reaches the k best are settled, then the
         // selection is done again
         uint32_t any = 0;
@@ -1071,7 +1013,6 @@ __device__ __noinline__ uint32_t settle_wide(FinishBuffer &fin, uint32_t *hist, 
         uint32_t with = __ballot_sync(kFullMask, any != 0);
         uint32_t settled = 0;
         for (; with != 0; with &= with - 1) settled += resolve_above(L, r, __ffs(with) - 1, threshold);
-        FGK_CTICK(10);
         if (settled == 0) break;
     }
     // unsorted survivors go to the far end of the work arrays, the sort brings them forward
@@ -1117,7 +1058,6 @@ __device__ __noinline__ uint32_t settle_wide(FinishBuffer &fin, uint32_t *hist, 
         }
     }
     __syncwarp();
-    FGK_CTICK(11);
     return kept;
 }
 
@@ -1130,7 +1070,6 @@ constexpr uint32_t kDense = 128;  // keys the short way takes: the closer's 256-
 __device__ __noinline__ uint32_t settle_lists(FinishBuffer &fin, uint32_t *hist, uint32_t *gathered, Lists &L,
                                              const Row r) {
     const uint32_t lane = lane_id();
-    FGK_CTICK_BEGIN;
     const uint64_t bound = peek64(&L.bound);
     {
         uint32_t any = 0;
@@ -1141,7 +1080,6 @@ __device__ __noinline__ uint32_t settle_lists(FinishBuffer &fin, uint32_t *hist,
         for (uint32_t with = __ballot_sync(kFullMask, any != 0); with != 0; with &= with - 1)
             resolve_above(L, r, __ffs(with) - 1, bound);
     }
-    FGK_CTICK(10);
     uint64_t *dense = reinterpret_cast<uint64_t *>(hist);
     uint16_t *where = reinterpret_cast<uint16_t *>(fin.raw);  // list * kListCap + entry
     static_assert(kDense * sizeof(uint64_t) <= 256 * sizeof(uint32_t), "the dense keys fit the closer's table");
@@ -1195,7 +1133,6 @@ __device__ __noinline__ uint32_t settle_lists(FinishBuffer &fin, uint32_t *hist,
         }
     }
     __syncwarp();
-    FGK_CTICK(11);
     return min(n, r.k);
 }
 
@@ -1206,10 +1143,6 @@ __device__ __noinline__ void close_unit(Shared &sh, uint32_t closer, Lists &L, c
     const uint32_t lane = lane_id();
     const uint32_t row = u.row;
     FinishBuffer &fin = sh.fin[closer];
-#ifdef FGK_X_NO_CLOSE
-    if (lane_id() == 0) report_row(p.out, u.row, kOk, 0u, 0.0f);
-    return;
-#endif
     uint32_t kept = settle_lists(fin, sh.hist[closer], &sh.gathered[closer], L, r);
     uint32_t bad_history = row_status ? row_status : L.bad_history;
     if (peek(&sh.ring_error)) {  // a tile never landed, or a warp never came
@@ -1344,11 +1277,7 @@ __device__ __noinline__ void close_unit(Shared &sh, uint32_t closer, Lists &L, c
         }
         return;
     }
-#ifdef FGK_PHASE_CLOCKS
-    long long ctick = clock64();
-#endif
     finish_select(fin, kept, cfg, p.uniforms[row], row, p.out);
-    FGK_CTICK(13);
 }
 
 // One warp's share (`part` of `parts`) of a unit's history bitmap.  First the words of the
@@ -1451,7 +1380,6 @@ __global__ void __launch_bounds__(kBlock, 1) persistent_select_kernel(const __gr
         // Closer c takes the units that use list set c: every other unit.
         const uint32_t closer = warp - (kWarps + kHistoryWarps);
         uint32_t served = 0;
-        FGK_CTICK_BEGIN;
         UnitWalk walk(p, tiles);
         Unit u;
         while (walk.next(u)) {
@@ -1468,10 +1396,8 @@ __global__ void __launch_bounds__(kBlock, 1) persistent_select_kernel(const __gr
             // (a wait that runs out leaves garbage lists: the row is failed through ring_error)
             bounded_wait(sh, &sh.ready[b], (served / kListSets) & 1u, polls);
             __syncwarp();
-            FGK_CTICK(8);
             close_unit(sh, closer, L, p, u, r, cfg, shard_mode, row_status);
             __syncwarp();
-            FGK_CTICK(12);
             // the lists' shared words, clean for the unit after next (a warp that is ahead of
             // the others must not meet what they published for another row)
             for (uint32_t i = lane; i < (uint32_t)kTallyBins; i += 32) L.tally[i] = 0;
@@ -1491,9 +1417,10 @@ __global__ void __launch_bounds__(kBlock, 1) persistent_select_kernel(const __gr
     }
     if (warp >= (uint32_t)kWarps) {
         // ------------------------------------------------------------ history warps
-        // The bitmap of the history ids that fall into the unit's columns, built one unit
-        // ahead of the consumers (two buffers) or as soon as they are through with the
-        // previous unit (one).  A token outside the vocabulary leaves its status behind.
+        // The bitmap of the history ids that fall into the unit's columns, built ahead of the
+        // consumers by as many units as there are spare buffers (two, one) or as soon as they
+        // are through with the previous unit (none).  A token outside the vocabulary leaves
+        // its status behind.
         const uint32_t helper = warp - kWarps;
         uint32_t served = 0;
         UnitWalk walk(p, tiles);
@@ -1554,10 +1481,6 @@ __global__ void __launch_bounds__(kBlock, 1) persistent_select_kernel(const __gr
     }
     uint32_t consumed = 0;  // tiles of this warp so far
     uint32_t served = 0;    // units before this one
-#ifdef FGK_PHASE_CLOCKS
-    unsigned long long phase[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    long long tick = clock64();
-#endif
     UnitWalk walk(p, tiles);
     Unit u;
     while (walk.next(u)) {
@@ -1569,7 +1492,7 @@ __global__ void __launch_bounds__(kBlock, 1) persistent_select_kernel(const __gr
         Lists &L = lists[b];
         const uint32_t slot = served % buffers;
         const uint32_t *bitmap = bitmaps + (size_t)slot * bitmap_stride;
-        // the closing warp must be done with these lists (it had them two units ago)
+        // the closing warp must be done with these lists (it got them three units ago)
         if (served >= (uint32_t)kListSets) bounded_wait(sh, &sh.vacant[b], (served / kListSets - 1u) & 1u, polls);
         if (lane < (uint32_t)kListWords) L.deferred[w][lane] = 0;
         if (lane == 0) {
@@ -1579,16 +1502,10 @@ __global__ void __launch_bounds__(kBlock, 1) persistent_select_kernel(const __gr
         bounded_wait(sh, &sh.bitmap_ready[slot], (served / buffers) & 1u, polls);
         if (w == 0 && lane == 0) L.bad_history = sh.history_bad[slot];
         __syncwarp();
-        FGK_PTICK(0);
-#ifdef FGK_PHASE_CLOCKS
-#define FGK_CLOCK_ARGS , phase, tick
-#else
-#define FGK_CLOCK_ARGS
-#endif
         consumed = r.greedy ? consume_unit<T, true>(p, sh, L, r, u, bitmap, stages, feeder, consumed, w, tiles,
-                                                    row_bytes, shard_mode, policy, polls FGK_CLOCK_ARGS)
+                                                    row_bytes, shard_mode, policy, polls)
                             : consume_unit<T, false>(p, sh, L, r, u, bitmap, stages, feeder, consumed, w, tiles,
-                                                     row_bytes, shard_mode, policy, polls FGK_CLOCK_ARGS);
+                                                     row_bytes, shard_mode, policy, polls);
         __threadfence_block();
         __syncwarp();
         if (lane == 0) {
@@ -1596,12 +1513,7 @@ __global__ void __launch_bounds__(kBlock, 1) persistent_select_kernel(const __gr
             mbarrier_arrive(&sh.bitmap_free[slot]);
         }
         served++;
-        FGK_PTICK(5);
     }
-#ifdef FGK_PHASE_CLOCKS
-    if (lane == 0)
-        for (int i = 0; i < 8; i++) atomicAdd(&fgk_persist_clocks[i], phase[i]);
-#endif
     // copies asked for but never looked at (only after a wait ran out) still write into this
     // CTA's shared memory: see them land, bounded, before the CTA may go away
     while (consumed < feeder.issued) {
@@ -1619,16 +1531,6 @@ __global__ void __launch_bounds__(kBlock, 1) persistent_select_kernel(const __gr
 
 // ------------------------------------------------------------------ host side
 
-#ifdef FGK_PHASE_CLOCKS
-extern "C" int fgk_read_persist_clocks(unsigned long long *out, int reset) {
-    cudaError_t e = cudaMemcpyFromSymbol(out, fgk::persist::fgk_persist_clocks, sizeof(unsigned long long) * 16);
-    if (e == cudaSuccess && reset) {
-        unsigned long long zero[16] = {0};
-        e = cudaMemcpyToSymbol(fgk::persist::fgk_persist_clocks, zero, sizeof(zero));
-    }
-    return (int)e;
-}
-#endif
 
 using namespace fgk;
 
@@ -1685,7 +1587,7 @@ static persist::Params to_persist_params(const fgk_stream_launch *l) {
     return p;
 }
 
-// Dynamic shared memory for a history bitmap of `bitmap_words` words: the stages, the two
+// Dynamic shared memory for a history bitmap of `bitmap_words` words: the stages, the
 // sets of lists and as many bitmap buffers as fit, three at most.  0: not even one.
 extern "C" uint64_t fgk_persistent_dynamic_smem(uint32_t bitmap_words, uint32_t *bitmap_buffers) {
     const uint64_t fixed = (uint64_t)persist::kWarps * persist::kStages * persist::kStageBytes +

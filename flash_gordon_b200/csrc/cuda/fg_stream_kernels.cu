@@ -21,10 +21,6 @@
 
 namespace fgk {
 
-#ifndef FGK_STREAM_MIN_CTAS
-#define FGK_STREAM_MIN_CTAS 4
-#endif
-
 constexpr int kThreads = 256;
 constexpr int kElemsPerThread = 16;
 constexpr int kTile = kThreads * kElemsPerThread;  // 4096 logits per CTA iteration
@@ -836,22 +832,9 @@ __device__ __noinline__ uint32_t fast_tiles(const StreamParams &p, StreamShared 
     return full_tiles - 1;
 }
 
-#ifdef FGK_PHASE_CLOCKS
-__device__ unsigned long long fgk_phase_clocks[8];
-#define FGK_TICK(slot)                                                          \
-    do {                                                                         \
-        if (threadIdx.x == 0) {                                                  \
-            const long long now = clock64();                                     \
-            atomicAdd(&fgk_phase_clocks[slot], (unsigned long long)(now - tick)); \
-            tick = now;                                                          \
-        }                                                                        \
-    } while (0)
-#else
-#define FGK_TICK(slot) do { } while (0)
-#endif
 
 template <typename T>
-__global__ void __launch_bounds__(kThreads, FGK_STREAM_MIN_CTAS)
+__global__ void __launch_bounds__(kThreads, 4)
 stream_select_kernel(const __grid_constant__ StreamParams p) {
     using L = Loader<T>;
     extern __shared__ __align__(16) uint32_t dyn_smem[];
@@ -859,9 +842,6 @@ stream_select_kernel(const __grid_constant__ StreamParams p) {
 
     const uint32_t tid = threadIdx.x;
     const uint32_t split = blockIdx.x, row = blockIdx.y;
-#ifdef FGK_PHASE_CLOCKS
-    long long tick = clock64();
-#endif
     const SamplerConfig cfg = p.config_count > 1 ? p.configs[row] : p.config0;
     const bool shard_mode = p.shard_k != 0;
     // (a shard of a greedy row keeps k_shard candidates like any other, and on top of them
@@ -896,7 +876,6 @@ stream_select_kernel(const __grid_constant__ StreamParams p) {
 
     // ---- 1. history slice -> bitmap / running popcount / offsets ----
     state.flags = build_history(p, sh, dyn_smem, row, lo, state.n, cfg);
-    FGK_TICK(0);
 
     // ---- 2. stream the columns ----
     // Tiles 1 .. full-1 of a 16-byte aligned row take the fast loop below: 128-bit
@@ -907,7 +886,6 @@ stream_select_kernel(const __grid_constant__ StreamParams p) {
     const uint32_t tiles = (n + kTile - 1) / kTile;
     const uint32_t full_tiles = state.aligned ? n / kTile : 0;
     float tau = careful_tile<T>(p, sh, dyn_smem, columns, 0, state, __uint_as_float(0xff800000u));
-    FGK_TICK(1);
 
     // can the row's penalties only lower a logit?  (rows without history count as such)
     const bool lowering = !(state.flags & kSeenAny) ||
@@ -918,38 +896,21 @@ stream_select_kernel(const __grid_constant__ StreamParams p) {
             lowering ? fast_tiles<T, true>(p, sh, dyn_smem, columns, t, full_tiles, state, tau)
                      : fast_tiles<T, false>(p, sh, dyn_smem, columns, t, full_tiles, state, tau);
         t = (stopped & ~kNeedsAttention) + 1;
-        FGK_TICK(2);
         if (stopped & kNeedsAttention) {
             // a tile pushed more than the list holds: feed it again in pieces;
             // otherwise the list is merely long: cut it, which lifts the bound
             if (sh.overflow) tau = redo_tile<T>(p, sh, dyn_smem, columns, t - 1, state);
             else tau = cut_list(sh, state.k);
-            FGK_TICK(3);
-#ifdef FGK_PHASE_CLOCKS
-            if (tid == 0) atomicAdd(&fgk_phase_clocks[6], 1ull);
-#endif
         }
     }
     // the ragged end of an aligned row, or every further tile of an unaligned one
     for (uint32_t t = full_tiles > 1 ? full_tiles : 1; t < tiles; t++)
         tau = careful_tile<T>(p, sh, dyn_smem, columns, t, state, tau);
-    FGK_TICK(4);
 
     // ---- 3./4. this split's k best, the row's result ----
     finish_split(p, sh, row, split, state.k, greedy, shard_mode, cfg);
-    FGK_TICK(5);
 }
 
-#ifdef FGK_PHASE_CLOCKS
-extern "C" int fgk_read_phase_clocks(unsigned long long *out, int reset) {
-    cudaError_t e = cudaMemcpyFromSymbol(out, fgk_phase_clocks, sizeof(unsigned long long) * 8);
-    if (e == cudaSuccess && reset) {
-        unsigned long long zero[8] = {0};
-        e = cudaMemcpyToSymbol(fgk_phase_clocks, zero, sizeof(zero));
-    }
-    return (int)e;
-}
-#endif
 
 // ================================================================== history pass
 //
