@@ -326,21 +326,28 @@ def sharded_record(context, world, rank, device, steps, barrier, torch, dist):
             np.array_equal(result.token_logits.cpu().numpy().view(np.uint32), want[2].view(np.uint32)))
         record["oracle_kind"] = kind
 
-    def whole(i):
-        communicator.sample_vocab_sharded(mine[i % len(mine)], full.configs, uniforms, VOCAB, 64, out=out,
-                                          asynchronous=True)
+    def timed(fused):
+        """ms for `steps` asynchronous calls, one after the other, max over the ranks."""
+        calls = [communicator.prepared_sample_vocab_sharded(shard, full.configs, uniforms, VOCAB, 64, out,
+                                                            fused=fused) for shard in mine]
+        for i in range(5):
+            if calls[i % len(calls)]() != 0:
+                raise SystemExit("sharded step failed to enqueue")
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        start.record()
+        for i in range(steps):
+            calls[i % len(calls)]()
+        stop.record()
+        barrier()
+        if int(out[2].max()) != 0:
+            raise SystemExit("sharded rows failed: " + str(out[2].unique().tolist()))
+        span = torch.tensor([start.elapsed_time(stop)], dtype=torch.float64, device=device)
+        dist.all_reduce(span, op=dist.ReduceOp.MAX)
+        return span
 
-    for i in range(5):
-        whole(i)
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    start.record()
-    for i in range(steps):
-        whole(i)
-    stop.record()
-    barrier()
-    total = torch.tensor([start.elapsed_time(stop)], dtype=torch.float64, device=device)
-    dist.all_reduce(total, op=dist.ReduceOp.MAX)
+    total = timed(False)
+    fused_total = timed(True)
 
     # the two compute steps on their own (per-launch events); the exchange is the rest
     scores = torch.empty(256, 64, dtype=torch.float32, device=device)
@@ -365,6 +372,9 @@ def sharded_record(context, world, rank, device, steps, barrier, torch, dist):
                    "rows_per_sec": 256 * steps / (float(total[0]) * 1e-3),
                    "shard_kernel_us": shard_us, "merge_us": merge_us,
                    "exchange_us": max(0.0, us_per_step - shard_us - merge_us),
+                   "fused_us_per_step": 1e3 * float(fused_total[0]) / steps,
+                   "fused_exchange": "fg_dist_sample_vocab_sharded_fused: the shard kernel stores its pairs into "
+                                     "every rank's window (CUDA IPC), the merge kernel waits for them",
                    "bytes_sent_per_rank": 256 * 64 * 8, "bytes_gathered_per_rank": 256 * 64 * 8 * world})
     communicator.close()
     return record

@@ -215,6 +215,26 @@ class Communicator:
         del keep
         return SampleResult(out[0], out[1], out[2], status, err.text(), None)
 
+    def prepared_sample_vocab_sharded(self, logits_shard: torch.Tensor, configs, uniforms: torch.Tensor,
+                                      vocab_total: int, k_shard: int, out, history_tokens=None,
+                                      history_offsets=None, history_max: int = 0, fused: bool = False):
+        """Builds the argument block once; the returned callable re-issues the same asynchronous
+        fg_dist_sample_vocab_sharded(_fused) call and returns its status (decode loops call it
+        once per token)."""
+        import ctypes
+        from . import FG_CUDA_SAMPLE_ASYNC, FgError
+        args, keep = self.context._args(logits_shard, configs, uniforms, history_tokens, history_offsets,
+                                        history_max, None, FG_CUDA_SAMPLE_ASYNC, out, None)
+        err = FgError()
+        call = self.lib.fg_dist_sample_vocab_sharded_fused if fused else self.lib.fg_dist_sample_vocab_sharded
+        handle, args_ref, err_ref = self.handle, ctypes.byref(args), ctypes.byref(err)
+
+        def issue() -> int:
+            return call(handle, args_ref, vocab_total, k_shard, err_ref)
+
+        issue.keep = (keep, args, err, logits_shard, uniforms, out)
+        return issue
+
     def gather_rows(self, tokens: torch.Tensor, token_logits: torch.Tensor, row_status: torch.Tensor):
         """fg_dist_gather_rows: every rank's `rows` results on every rank, in rank order."""
         import ctypes
