@@ -26,7 +26,8 @@ namespace fgk {
 
 constexpr int kNucleusThreads = 1024;
 constexpr int kBuckets = 4096;
-constexpr size_t kNucleusHistogramBytes = kBuckets * (sizeof(unsigned long long) + sizeof(uint32_t));
+// per bucket: two masses (raw and tempered weights) and a count
+constexpr size_t kNucleusHistogramBytes = kBuckets * (2 * sizeof(unsigned long long) + sizeof(uint32_t));
 
 struct NucleusParams {
     const void *logits;
@@ -48,7 +49,8 @@ struct NucleusParams {
 };
 
 struct NucleusShared {
-    unsigned long long *mass;         // kBuckets entries, dynamic shared memory
+    unsigned long long *mass;         // kBuckets entries, dynamic shared memory: the masses a crossing search walks
+    unsigned long long *other_mass;   // kBuckets entries: the tempered masses while `mass` holds the raw ones
     uint32_t *count;                  // kBuckets entries
     double table[64];                 // 2^(j/64)
     unsigned long long scan_mass[32];
@@ -429,68 +431,38 @@ struct Position {
 // first element of the (value descending, id ascending) order at which the running
 // weight reaches target_of(total) (strict: exceeds it); if it never does, the last
 // element inside.  All threads call.
-template <typename TargetOf>
-__device__ Position locate(NucleusShared &sh, NucleusList &list, const float *values, uint32_t vocab,
-                           double inv_t, float top, const Nucleus inside, TargetOf target_of,
-                           bool strict) {
+// The members of one value bucket (restricted to `inside`), ordered exactly, and among them the
+// first at which the running weight -- `before` plus the weights exp((v - top) * inv_t) of the
+// members so far -- reaches `target` (strict: exceeds it); the last member when none does or
+// when `clipped`.  ok = false: the bucket is empty or holds more than the list takes.  With
+// `also_inv_t` != 0 the weights exp((v - top) * also_inv_t) of the members up to and including
+// the one found are summed into *also_sum.  All threads call.
+__device__ Position resolve_bucket(NucleusShared &sh, NucleusList &list, const float *values, uint32_t vocab,
+                                   double inv_t, float top, const Nucleus inside, uint32_t bucket,
+                                   uint32_t members, unsigned long long before, uint32_t rank_before,
+                                   unsigned long long target, bool strict, bool clipped, double also_inv_t,
+                                   unsigned long long *also_sum) {
     const uint32_t tid = threadIdx.x;
     Position found;
     found.ok = false;
-    clear_histogram(sh, kBuckets);
-    walk_row(values, vocab, [&](float v, uint32_t i) {
-        if (is_nonfinite(v) || !inside.holds(float_key(v), i)) return;
-        const unsigned long long w = exp_fixed(((double)v - (double)top) * inv_t, sh.table);
-        const uint32_t b = value_bucket(v, top);
-        atomicAdd(&sh.mass[b], w);
-        atomicAdd(&sh.count[b], 1u);
-    });
-    __syncthreads();
-    const unsigned long long target = find_crossing_up(sh, target_of, strict);
-    found.total = sh.total_mass;
-    bool clipped = false;
-    if (!sh.hit_found) {
-        // never reached (top_p = 1 or a draw rounded up to the total): the last element
-        // inside, i.e. the last member of the last non-empty bucket
-        clipped = true;
-        __syncthreads();
-        if (tid == 0) {
-            unsigned long long m = 0;
-            uint32_t c = 0, last = 0;
-            bool any = false;
-            for (uint32_t b = 0; b < kBuckets; b++) {
-                if (sh.count[b]) {
-                    if (any) {
-                        m += sh.mass[last];
-                        c += sh.count[last];
-                    }
-                    last = b;
-                    any = true;
-                }
-            }
-            sh.hit_bucket = last;
-            sh.hit_mass_before = m;
-            sh.hit_count_before = c;
-        }
-        __syncthreads();
-    }
-    const uint32_t bucket = sh.hit_bucket;
-    const unsigned long long before = sh.hit_mass_before;
-    const uint32_t rank_before = sh.hit_count_before;
-    const uint32_t members = sh.count[bucket];
-    __syncthreads();
+    found.total = 0;
     if (members == 0 || members > kListCap) return found;  // crowded bucket (heavy ties): generic path
-
-    // gather the bucket's members
     if (tid == 0) list.count = 0;
     __syncthreads();
     walk_row(values, vocab, [&](float v, uint32_t i) {
-        if (is_nonfinite(v) || !inside.holds(float_key(v), i)) return;
+        // (a NaN or an infinity has no bucket: the conversion below sends them to the last one or
+        // to bucket 0, so they are looked at, and dropped, only there)
         if (value_bucket(v, top) != bucket) return;
+        if (is_nonfinite(v) || !inside.holds(float_key(v), i)) return;
         const uint32_t slot = atomicAdd(&list.count, 1u);
-        list.value[slot] = v;
-        list.id[slot] = i;
+        if (slot < kListCap) {
+            list.value[slot] = v;
+            list.id[slot] = i;
+        }
     });
     __syncthreads();
+    members = min(list.count, kListCap);  // (inside may hold fewer of the bucket than the histogram counted)
+    if (members == 0) return found;
     // order them: rank by counting, (value descending, id ascending); -0.0 and +0.0 tie
     for (uint32_t a = tid; a < members; a += kNucleusThreads) {
         const float v = list.value[a];
@@ -540,7 +512,166 @@ __device__ Position locate(NucleusShared &sh, NucleusList &list, const float *va
     found.rank = rank_before + at + 1;
     found.ok = true;
     __syncthreads();
+    if (also_sum != nullptr) {
+        // the other weight of the members up to the one found (order does not matter: integers)
+        unsigned long long part = 0;
+        for (uint32_t a = tid; a <= at; a += kNucleusThreads)
+            part += exp_fixed(((double)list.sorted_value[a] - (double)top) * also_inv_t, sh.table);
+        const uint32_t lane = tid & 31u, warp = tid >> 5;
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) part += __shfl_xor_sync(kFullMask, part, d);
+        if (lane == 0) sh.scan_mass[warp] = part;
+        __syncthreads();
+        unsigned long long sum = 0;
+        for (int w = 0; w < kNucleusThreads / 32; w++) sum += sh.scan_mass[w];
+        *also_sum = sum;
+        __syncthreads();
+    }
     return found;
+}
+
+// After a crossing search: the bucket it stopped in, or -- when the total never reaches the
+// target (top_p = 1, a draw rounded up to the total) -- the last non-empty bucket.  Returns
+// whether it was clipped; all threads call.
+__device__ bool settle_crossing(NucleusShared &sh) {
+    if (sh.hit_found) return false;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        unsigned long long m = 0;
+        uint32_t c = 0, last = 0;
+        bool any = false;
+        for (uint32_t b = 0; b < kBuckets; b++) {
+            if (sh.count[b]) {
+                if (any) {
+                    m += sh.mass[last];
+                    c += sh.count[last];
+                }
+                last = b;
+                any = true;
+            }
+        }
+        sh.hit_bucket = last;
+        sh.hit_mass_before = m;
+        sh.hit_count_before = c;
+    }
+    __syncthreads();
+    return true;
+}
+
+// One phase: among the elements `inside`, weights exp((v - top) * inv_t), find the
+// first element of the (value descending, id ascending) order at which the running
+// weight reaches target_of(total) (strict: exceeds it); if it never does, the last
+// element inside.  All threads call.
+template <typename TargetOf>
+__device__ Position locate(NucleusShared &sh, NucleusList &list, const float *values, uint32_t vocab,
+                           double inv_t, float top, const Nucleus inside, TargetOf target_of,
+                           bool strict) {
+    clear_histogram(sh, kBuckets);
+    walk_row(values, vocab, [&](float v, uint32_t i) {
+        if (is_nonfinite(v) || !inside.holds(float_key(v), i)) return;
+        const unsigned long long w = exp_fixed(((double)v - (double)top) * inv_t, sh.table);
+        const uint32_t b = value_bucket(v, top);
+        atomicAdd(&sh.mass[b], w);
+        atomicAdd(&sh.count[b], 1u);
+    });
+    __syncthreads();
+    const unsigned long long target = find_crossing_up(sh, target_of, strict);
+    const unsigned long long total = sh.total_mass;
+    const bool clipped = settle_crossing(sh);
+    const uint32_t bucket = sh.hit_bucket;
+    const unsigned long long before = sh.hit_mass_before;
+    const uint32_t rank_before = sh.hit_count_before;
+    const uint32_t members = sh.count[bucket];
+    __syncthreads();
+    Position found = resolve_bucket(sh, list, values, vocab, inv_t, top, inside, bucket, members, before,
+                                    rank_before, target, strict, clipped, 0.0, nullptr);
+    found.total = total;
+    return found;
+}
+
+// exp(x) for |x| <= 1/64 by its series to the sixth power (the next term is below 1e-16).
+__device__ __forceinline__ double exp_small(double x) {
+    double p = fma(x, 1.0 / 720.0, 1.0 / 120.0);
+    p = fma(p, x, 1.0 / 24.0);
+    p = fma(p, x, 1.0 / 6.0);
+    p = fma(p, x, 0.5);
+    p = fma(p, x, 1.0);
+    return fma(p, x, 1.0);
+}
+
+// One pass over the row for both phases: per value bucket the count, the raw weights
+// exp(v - top) and the tempered weights exp((v - top) * inv_t) of its members.  A member's
+// weight is taken relative to the bucket's upper edge -- an argument of at most 1/256 (times
+// inv_t), a short series instead of a full exp() -- as 2^-32 fixed point, and summed in two
+// 16-bit halves with 32-bit shared-memory adds (a bucket of up to 65,535 members cannot
+// overflow them; integer sums do not depend on the order of arrival).  The rounding of one
+// member is 2^-33 of a member's weight; a whole row's worth stays below 1e-4 of one member's
+// weight, three orders of magnitude under the smallest distance to an edge of the cumulative
+// distribution that decides a row.  Afterwards every bucket's sums are scaled by the weight of
+// its edge, exp(-b/256) (and its power inv_t), into the row's 2^-40 fixed point.  The last
+// bucket (everything 16 below the maximum) and rows with inv_t > 4 take the full exp().
+// Returns false when a bucket holds too many members for its sums (heavy ties).
+__device__ bool fill_both(NucleusShared &sh, const float *values, uint32_t vocab, double inv_t, float top) {
+    const uint32_t tid = threadIdx.x;
+    // the two mass arrays, seen as four arrays of 32-bit sums
+    uint32_t *raw_low = reinterpret_cast<uint32_t *>(sh.mass), *raw_high = raw_low + kBuckets;
+    uint32_t *tempered_low = reinterpret_cast<uint32_t *>(sh.other_mass), *tempered_high = tempered_low + kBuckets;
+    for (uint32_t b = tid; b < kBuckets; b += kNucleusThreads) {
+        sh.mass[b] = 0;
+        sh.other_mass[b] = 0;
+        sh.count[b] = 0;
+    }
+    if (tid == 0) sh.hit_found = 0;
+    __syncthreads();
+    const bool series = inv_t <= 4.0;  // (1/256) * inv_t <= 1/64
+    const double top_d = (double)top;
+    constexpr double kOne = 4294967296.0;  // 2^32
+    walk_row(values, vocab, [&](float v, uint32_t i) {
+        if (is_nonfinite(v)) return;
+        const uint32_t b = value_bucket(v, top);
+        // v - (top - b/256): at most a bucket's width (and a rounding of the bucket's number) from 0
+        const double x = ((double)v - top_d) + (double)b * (1.0 / 256.0);
+        // (a weight of 1 and a rounding above it saturate at 2^32 - 1: half a unit, like any rounding)
+        uint32_t r, t;
+        if (series && b != (uint32_t)(kBuckets - 1)) {
+            r = (uint32_t)min(__double2ull_rn(exp_small(x) * kOne), 0xffffffffull);
+            t = (uint32_t)min(__double2ull_rn(exp_small(x * inv_t) * kOne), 0xffffffffull);
+        } else {
+            r = (uint32_t)min((exp_fixed(x, sh.table) + 128ull) >> 8, 0xffffffffull);
+            t = (uint32_t)min((exp_fixed(x * inv_t, sh.table) + 128ull) >> 8, 0xffffffffull);
+        }
+        atomicAdd(&raw_low[b], r & 0xffffu);
+        atomicAdd(&raw_high[b], r >> 16);
+        atomicAdd(&tempered_low[b], t & 0xffffu);
+        atomicAdd(&tempered_high[b], t >> 16);
+        atomicAdd(&sh.count[b], 1u);
+    });
+    __syncthreads();
+    // the halves back together (every thread reads the sums of its buckets before any of them is
+    // overwritten: the 64-bit masses take the place of the 32-bit sums), scaled by the edge's
+    // weight into the row's fixed point: 2^-32 -> 2^-40 is a factor 256
+    constexpr int kOwn = kBuckets / kNucleusThreads;
+    unsigned long long raw[kOwn], tempered[kOwn];
+#pragma unroll
+    for (int j = 0; j < kOwn; j++) {
+        const uint32_t b = j * kNucleusThreads + tid;
+        raw[j] = ((unsigned long long)raw_high[b] << 16) + raw_low[b];
+        tempered[j] = ((unsigned long long)tempered_high[b] << 16) + tempered_low[b];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < kOwn; j++) {
+        const uint32_t b = j * kNucleusThreads + tid;
+        const uint32_t members = sh.count[b];
+        if (members > 65535u) sh.hit_found = 1;  // (reused as "a bucket overflowed")
+        const double edge = -(double)b * (1.0 / 256.0);
+        sh.mass[b] = members ? __double2ull_rn((double)raw[j] * 256.0 * exp(edge)) : 0ull;
+        sh.other_mass[b] = members ? __double2ull_rn((double)tempered[j] * 256.0 * exp(edge * inv_t)) : 0ull;
+    }
+    __syncthreads();
+    const bool fits = sh.hit_found == 0;
+    __syncthreads();
+    return fits;
 }
 
 template <typename T>
@@ -550,7 +681,8 @@ __global__ void __launch_bounds__(kNucleusThreads, 1) nucleus_select_kernel(cons
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     if (tid == 0) {
         sh.mass = reinterpret_cast<unsigned long long *>(histogram_memory);
-        sh.count = reinterpret_cast<uint32_t *>(histogram_memory + kBuckets * sizeof(unsigned long long));
+        sh.other_mass = sh.mass + kBuckets;
+        sh.count = reinterpret_cast<uint32_t *>(histogram_memory + 2 * kBuckets * sizeof(unsigned long long));
     }
     if (tid < 64) sh.table[tid] = exp2((double)tid / 64.0);
     float *values = p.scratch + (size_t)blockIdx.x * p.scratch_stride;
@@ -681,6 +813,74 @@ __global__ void __launch_bounds__(kNucleusThreads, 1) nucleus_select_kernel(cons
         nucleus.everything = false;
         unsigned long long raw_sum, mass_at_cut;
         uint32_t size;
+        const double inv_t = 1.0 / (double)cfg.temperature;
+        float u = p.uniforms[row];
+        if (is_nonfinite(u) || u < 0.0f) u = 0.0f;
+        if (u >= 1.0f) u = __uint_as_float(0x3f7fffffu);
+        const double draw_at = (double)u;
+        // first element whose cumulative weight exceeds draw = u * sum
+        auto draw_target = [draw_at](unsigned long long total) {
+            return (unsigned long long)floor(draw_at * (double)total);
+        };
+        uint32_t picked_id = kPaddingId;
+        unsigned long long weight_sum = 0;
+
+        // ---- the usual way: one pass fills both histograms, each phase then looks into one bucket ----
+        bool done = false;
+        {
+            const bool filled = fill_both(sh, values, p.vocab, inv_t, best);
+            const unsigned long long cut_target = find_crossing_up(sh, mass_target, false);
+            raw_sum = sh.total_mass;
+            const bool cut_clipped = settle_crossing(sh);
+            const uint32_t cut_bucket = sh.hit_bucket;
+            const unsigned long long cut_before = sh.hit_mass_before;
+            const uint32_t cut_rank_before = sh.hit_count_before;
+            const uint32_t cut_members = sh.count[cut_bucket];
+            __syncthreads();
+            unsigned long long tempered_inside = 0;  // tempered weight of the bucket's members inside the nucleus
+            const Position cut = resolve_bucket(sh, list, values, p.vocab, 1.0, best, all, cut_bucket, cut_members,
+                                                cut_before, cut_rank_before, cut_target, false, cut_clipped, inv_t,
+                                                &tempered_inside);
+            if (filled && cut.ok) {
+                nucleus.key = cut.key;
+                nucleus.id = cut.id;
+                mass_at_cut = cut.mass;
+                size = cut.rank;
+                // the tempered masses of the nucleus: whole buckets above the cut's, that bucket as
+                // far as the nucleus reaches into it, nothing below
+                if (tid == 0) {
+                    unsigned long long *raw = sh.mass;
+                    sh.mass = sh.other_mass;
+                    sh.other_mass = raw;
+                }
+                __syncthreads();
+                for (uint32_t b = tid; b < kBuckets; b += kNucleusThreads) {
+                    if (b > cut_bucket) {
+                        sh.mass[b] = 0;
+                        sh.count[b] = 0;
+                    } else if (b == cut_bucket) {
+                        sh.mass[b] = tempered_inside;
+                    }
+                }
+                __syncthreads();
+                const unsigned long long pick_target = find_crossing_up(sh, draw_target, true);
+                weight_sum = sh.total_mass;
+                const bool pick_clipped = settle_crossing(sh);
+                const uint32_t pick_bucket = sh.hit_bucket;
+                const unsigned long long pick_before = sh.hit_mass_before;
+                const uint32_t pick_members = sh.count[pick_bucket];
+                __syncthreads();
+                const Position pick = resolve_bucket(sh, list, values, p.vocab, inv_t, best, nucleus, pick_bucket,
+                                                     pick_members, pick_before, 0u, pick_target, true, pick_clipped,
+                                                     0.0, nullptr);
+                if (pick.ok) {
+                    picked_id = pick.id;
+                    done = true;
+                }
+            }
+        }
+        if (!done) {
+        // ---- a bucket too crowded to order in shared memory: phase by phase, with the exact descent ----
         const Position cut = locate(sh, list, values, p.vocab, 1.0, best, all, mass_target, false);
         if (cut.ok) {
             nucleus.key = cut.key;
@@ -707,17 +907,6 @@ __global__ void __launch_bounds__(kNucleusThreads, 1) nucleus_select_kernel(cons
         }
 
         // ---- temperature weights of the nucleus, then the draw ----
-        const double inv_t = 1.0 / (double)cfg.temperature;
-        float u = p.uniforms[row];
-        if (is_nonfinite(u) || u < 0.0f) u = 0.0f;
-        if (u >= 1.0f) u = __uint_as_float(0x3f7fffffu);
-        const double draw_at = (double)u;
-        // first element whose cumulative weight exceeds draw = u * sum
-        auto draw_target = [draw_at](unsigned long long total) {
-            return (unsigned long long)floor(draw_at * (double)total);
-        };
-        uint32_t picked_id;
-        unsigned long long weight_sum;
         const Position pick = locate(sh, list, values, p.vocab, inv_t, best, nucleus, draw_target, true);
         if (pick.ok) {
             picked_id = pick.id;
@@ -741,6 +930,7 @@ __global__ void __launch_bounds__(kNucleusThreads, 1) nucleus_select_kernel(cons
             unsigned long long picked_mass;
             descend(sh, values, p.vocab, inv_t, (double)best, nucleus, draw_target(weight_sum), true,
                     &picked_key, &picked_id, &picked_mass, &picked_rank);
+        }
         }
         if (tid == 0) {
             if (weight_sum == 0 || raw_sum == 0 || picked_id >= p.vocab) {
