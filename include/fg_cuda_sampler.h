@@ -398,7 +398,10 @@ fg_status fg_dist_gather_rows(fg_dist *dist, const uint32_t *tokens, const float
  *     are in args->row_status after the caller synchronises the stream.
  *   - The first call on a device looks up the array's device address
  *     (cudaGetSymbolAddress, with that device made current); make that first
- *     call before starting any stream capture.
+ *     call before starting any stream capture.  With per-row configs
+ *     (config_count > 1) every call copies the caller's host array to the
+ *     device, so a captured graph would replay that copy from the same host
+ *     address: pass one config when capturing.
  *   - Limit: 256 + 4*rows (+ 40*rows with per-row configs) + 528*rows*splits
  *     bytes must fit 4 MiB; the split count is lowered to make it fit and
  *     FG_ERR_LIMIT names the sizes when even one CTA per row does not
