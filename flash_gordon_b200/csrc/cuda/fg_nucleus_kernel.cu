@@ -746,22 +746,65 @@ __global__ void __launch_bounds__(kNucleusThreads, 1) nucleus_select_kernel(cons
                     }
                     return v;
                 };
-                auto take4 = [&](float4 v, uint32_t q) {
+                // What the history says about the four columns of a quad (they share a bitmap word).
+                // The loads go out in two waves that wait for nothing but each other -- the word and
+                // the running count of ids before it, then the four occurrence counts -- instead of
+                // a chain of two loads per seen column.
+                struct Seen {
+                    uint32_t nibble;    // bit j: column 4q + j has been seen
+                    uint32_t times[4];  // how often (with a frequency penalty)
+                };
+                auto look_up = [&](uint32_t q) {
+                    Seen seen;
+                    seen.nibble = 0;
+                    seen.times[0] = seen.times[1] = seen.times[2] = seen.times[3] = 1u;
+                    if (!(flags & 1u)) return seen;
                     const uint32_t c = q * 4u;
-                    const uint32_t word = (flags & 1u) ? history.bitmap[c >> 5] : 0u;
-                    v.x = take(v.x, c, word);
-                    v.y = take(v.y, c + 1u, word);
-                    v.z = take(v.z, c + 2u, word);
-                    v.w = take(v.w, c + 3u, word);
+                    const uint32_t word = history.bitmap[c >> 5];
+                    seen.nibble = (word >> (c & 31u)) & 15u;
+                    if ((flags & 2u) && seen.nibble != 0) {
+                        const uint32_t before = history.running[c >> 5] + __popc(word & ((1u << (c & 31u)) - 1u));
+                        uint32_t at[4];
+                        at[0] = before;
+                        at[1] = at[0] + (seen.nibble & 1u);
+                        at[2] = at[1] + ((seen.nibble >> 1) & 1u);
+                        at[3] = at[2] + ((seen.nibble >> 2) & 1u);
+#pragma unroll
+                        for (int j = 0; j < 4; j++) {
+                            const uint32_t slot = min(at[j], history.capacity - 1u);
+                            seen.times[j] = history.wide ? static_cast<const uint32_t *>(history.dense)[slot]
+                                                         : static_cast<const uint16_t *>(history.dense)[slot];
+                        }
+                    }
+                    return seen;
+                };
+                auto settle = [&](float v, uint32_t j, const Seen &seen) {
+                    if ((seen.nibble >> j) & 1u) {
+                        float offset = flat_offset;
+                        if (flags & 2u) offset = penalty_offset(seen.times[j], cfg.presence_penalty, cfg.frequency_penalty);
+                        v = penalise_with_offset(v, offset, repetition);
+                    }
+                    if (!is_nonfinite(v)) {
+                        best = fmaxf(best, v);
+                        finite++;
+                    }
+                    return v;
+                };
+                auto take4 = [&](float4 v, uint32_t q, const Seen &seen) {
+                    v.x = settle(v.x, 0u, seen);
+                    v.y = settle(v.y, 1u, seen);
+                    v.z = settle(v.z, 2u, seen);
+                    v.w = settle(v.w, 3u, seen);
                     out[q] = v;
                 };
                 uint32_t q = tid;
                 for (; q + kNucleusThreads < quads; q += 2 * kNucleusThreads) {
                     const float4 a = load4(q), b = load4(q + kNucleusThreads);
-                    take4(a, q);
-                    take4(b, q + kNucleusThreads);
+                    const Seen seen_a = look_up(q), seen_b = look_up(q + kNucleusThreads);
+                    take4(a, q, seen_a);
+                    take4(b, q + kNucleusThreads, seen_b);
                 }
-                if (q < quads) take4(load4(q), q);
+                if (q < quads) take4(load4(q), q, look_up(q));
                 done = quads * 4u;
             }
             for (uint32_t c = done + tid; c < n; c += kNucleusThreads) {
