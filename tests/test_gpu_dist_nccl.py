@@ -126,6 +126,22 @@ def test_one_rank_runs_the_whole_sharded_call(context):
                                                           fused=True)
                 torch.cuda.synchronize()
                 assert_rows_equal(fused, want, f"{w.name}, fused exchange, call {attempt}")
+        # the prepared form (argument block built once, asynchronous calls back to back), both ways
+        w = synth.config4(rows=24, vocab=40_000)
+        wd = w.to("cuda")
+        want = run_oracle(w)
+        out = (torch.empty(24, dtype=torch.int32, device="cuda"), torch.empty(24, dtype=torch.float32, device="cuda"),
+               torch.empty(24, dtype=torch.int32, device="cuda"))
+        for fused in (False, True):
+            issue = communicator.prepared_sample_vocab_sharded(wd.logits, wd.configs, wd.uniforms, w.vocab, 64, out,
+                                                               fused=fused)
+            for _ in range(4):
+                out[0].fill_(-7)
+                assert issue() == FG_OK
+            torch.cuda.synchronize()
+            assert np.array_equal(out[0].cpu().numpy().view(np.uint32), want[1]), fused
+            assert np.array_equal(out[1].cpu().numpy().view(np.uint32), want[2].view(np.uint32)), fused
+            assert int(out[2].max()) == 0
         wd = synth.config4(rows=4, vocab=8_000).to("cuda")
         short = communicator.sample_vocab_sharded(wd.logits[:, :4000].contiguous(), wd.configs, wd.uniforms,
                                                   8_000, 64)
