@@ -212,3 +212,23 @@ def test_ring_refuses_what_it_cannot_take(context):
         assert result.status == FG_OK
     finally:
         context.set_path(PATH_RING)
+
+
+def test_shapes_the_planner_treats_differently(context):
+    """Through the automatic choice: a few rows of more than a million logits (dealt out in tiles
+    and merged), the same with a history (its bitmap does not fit beside the ring: the other
+    kernel), long rows in a small batch, many one-tile rows, a ragged one-tile row."""
+    context.set_path(PATH_AUTO)
+    try:
+        for rows, vocab, history, cfg in (
+                (3, 1_200_000, 0, SamplerConfig.make(0.9, 0.9, 50)),
+                (2, 1_200_004, 0, SamplerConfig.make(0.0, 1.0, 1)),
+                (5, 1_100_000, 300, SamplerConfig.make(0.8, 0.9, 40, presence=0.2, frequency=0.1)),
+                (40, 300_000, 500, SamplerConfig.make(0.8, 0.9, 64, presence=0.2, frequency=0.1, repetition=1.1)),
+                (600, 2048, 100, SamplerConfig.make(0.8, 0.9, 20, presence=0.2)),
+                (7, 2052, 0, SamplerConfig.make(1.0, 0.95, 64))):
+            w = random_workload(rows, vocab, history, [cfg], 4242 + rows, specials=1)
+            assert_rows_equal(run_gpu(context, w), run_oracle(w), f"{rows} x {vocab}")
+    finally:
+        context.set_path(PATH_RING)
+
