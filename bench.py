@@ -308,9 +308,15 @@ def sharded_record(context, world, rank, device, steps, barrier, torch, dist):
     uniforms = full.uniforms.to(device)
     out = (torch.empty(256, dtype=torch.int32, device=device), torch.empty(256, dtype=torch.float32, device=device),
            torch.empty(256, dtype=torch.int32, device=device))
+    def agree(failed: bool, what: str):
+        """Every rank leaves together when any of them failed (nobody is left in a collective)."""
+        flag = torch.tensor([1 if failed else 0], dtype=torch.int32, device=device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MAX)
+        if int(flag[0]) != 0:
+            raise RuntimeError(what)
+
     result = communicator.sample_vocab_sharded(mine[0], full.configs, uniforms, VOCAB, 64, out=out)
-    if result.status != 0:
-        raise SystemExit(f"sharded step failed: {result.message}")
+    agree(result.status != 0, f"sharded step failed: {result.message}")
     record = {"workload": "config4: batch 256 x vocab 151936 bf16 split by columns over the GPUs, "
                           "N(0,4^2), shard top-64, all-gather of (fp32 value, int32 id), merge, "
                           "T=0.8 top_p=0.9 top_k=64", "columns_per_gpu": width,
@@ -330,9 +336,10 @@ def sharded_record(context, world, rank, device, steps, barrier, torch, dist):
         """ms for `steps` asynchronous calls, one after the other, max over the ranks."""
         calls = [communicator.prepared_sample_vocab_sharded(shard, full.configs, uniforms, VOCAB, 64, out,
                                                             fused=fused) for shard in mine]
+        refused = False
         for i in range(5):
-            if calls[i % len(calls)]() != 0:
-                raise SystemExit("sharded step failed to enqueue")
+            refused = calls[i % len(calls)]() != 0 or refused
+        agree(refused, "a sharded step could not be enqueued" + (" (fused exchange)" if fused else ""))
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         barrier()
         start.record()
@@ -340,14 +347,16 @@ def sharded_record(context, world, rank, device, steps, barrier, torch, dist):
             calls[i % len(calls)]()
         stop.record()
         barrier()
-        if int(out[2].max()) != 0:
-            raise SystemExit("sharded rows failed: " + str(out[2].unique().tolist()))
+        agree(int(out[2].max()) != 0, "sharded rows failed" + (" (fused exchange)" if fused else ""))
         span = torch.tensor([start.elapsed_time(stop)], dtype=torch.float64, device=device)
         dist.all_reduce(span, op=dist.ReduceOp.MAX)
         return span
 
     total = timed(False)
-    fused_total = timed(True)
+    try:  # (every rank raises together, see agree(): the NCCL figures above stay)
+        fused_total, fused_error = timed(True), None
+    except RuntimeError as error:
+        fused_total, fused_error = None, str(error)
 
     # the two compute steps on their own (per-launch events); the exchange is the rest
     scores = torch.empty(256, 64, dtype=torch.float32, device=device)
@@ -372,7 +381,8 @@ def sharded_record(context, world, rank, device, steps, barrier, torch, dist):
                    "rows_per_sec": 256 * steps / (float(total[0]) * 1e-3),
                    "shard_kernel_us": shard_us, "merge_us": merge_us,
                    "exchange_us": max(0.0, us_per_step - shard_us - merge_us),
-                   "fused_us_per_step": 1e3 * float(fused_total[0]) / steps,
+                   "fused_us_per_step": None if fused_total is None else 1e3 * float(fused_total[0]) / steps,
+                   "fused_error": fused_error,
                    "fused_exchange": "fg_dist_sample_vocab_sharded_fused: the shard kernel stores its pairs into "
                                      "every rank's window (CUDA IPC), the merge kernel waits for them",
                    "bytes_sent_per_rank": 256 * 64 * 8, "bytes_gathered_per_rank": 256 * 64 * 8 * world})
